@@ -1,0 +1,393 @@
+// Prefill attention forward for sm_100a: bf16 in/out, float32 softmax and accumulation.
+//
+// One CTA owns 256 consecutive query rows of one (batch*head) as two 128-row tiles that
+// ping-pong: while the softmax warps of one tile work on their scores, the tensor core runs
+// the MMAs of the other tile.
+//
+//   warps 0-3   softmax + epilogue of tile 0 (one thread per query row, row state in registers)
+//   warps 4-7   softmax + epilogue of tile 1
+//   warp  8     MMA issue (one lane): S = Q K^T and O += P V with tcgen05.mma, accumulators in TMEM
+//   warp  9     TMA producer (one lane): Q once, then K and V tiles through a 2-stage ring
+//   warp 10     TMEM allocation / release
+//
+// Tensor memory (512 columns x 128 lanes of 32 bit): S0 [0,128) S1 [128,256) O0 [256,256+HD)
+// O1 [256+HD, 256+2HD). The bf16 probabilities P overwrite the first 64 columns of their S
+// and are read from there as the A operand of the PV MMA, so P never touches shared memory.
+// Softmax runs in the exp2 domain (scale*log2(e) folded into one FMA per score); the running
+// reference maximum is only moved, and O rescaled, when the row maximum grew by more than 2^8,
+// which after the first tiles is rare. Causal tiles above the diagonal are never loaded or
+// multiplied; only tiles crossed by the diagonal (or by the end of the key axis) pay for a mask.
+#include <math.h>
+
+#include "common.cuh"
+#include "kernels.cuh"
+#include "ptx.cuh"
+
+namespace ember {
+
+namespace {
+
+using namespace ptx;
+
+constexpr int FWD_THREADS = 384;
+constexpr float LOG2E_F = 1.4426950408889634f;
+constexpr float LN2_F = 0.6931471805599453f;
+constexpr float RESCALE_THRESHOLD = 8.0f;  // log2 units
+
+template <int HD>
+struct FwdCfg {
+    static constexpr int NSUB = HD / 64;                 // 64-column (128-byte) sub-tiles per tile
+    static constexpr int SUB_BYTES = 128 * 128;          // 128 rows x 128 bytes
+    static constexpr int TILE_BYTES = NSUB * SUB_BYTES;  // one 128 x HD bf16 tile
+    static constexpr int STAGES = HD == 128 ? 2 : 3;
+    static constexpr int OFF_Q = 0;
+    static constexpr int OFF_K = OFF_Q + 2 * TILE_BYTES;
+    static constexpr int OFF_V = OFF_K + STAGES * TILE_BYTES;
+    static constexpr int OFF_BAR = OFF_V + STAGES * TILE_BYTES;
+    static constexpr int NUM_BARS = 1 + 4 * STAGES + 6;
+    static constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;  // barriers + misc, + alignment slack
+    static constexpr int TMEM_S = 0;
+    static constexpr int TMEM_O = 256;
+};
+
+// Wait codes reported in the device status word.
+enum {
+    W_MMA_Q = 1, W_MMA_K, W_MMA_V, W_MMA_P, W_SM_S, W_SM_O, W_SM_OFINAL, W_TMA_KEMPTY, W_TMA_VEMPTY
+};
+
+struct FwdParams {
+    __nv_bfloat16 *out;
+    float *lse;
+    int lq, lk;
+    int causal;
+    float scale_log2;  // scale * log2(e)
+    DeviceStatus *status;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(FWD_THREADS, 1)
+    sm100_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                     const __grid_constant__ CUtensorMap tm_v, const FwdParams p)
+{
+    using C = FwdCfg<HD>;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+
+    const uint32_t bar0 = smem_base + C::OFF_BAR;
+    auto BAR = [&](int i) { return bar0 + 8u * (uint32_t)i; };
+    const int B_Q = 0;
+    const int B_KFULL = 1, B_KEMPTY = B_KFULL + C::STAGES, B_VFULL = B_KEMPTY + C::STAGES,
+              B_VEMPTY = B_VFULL + C::STAGES, B_S = B_VEMPTY + C::STAGES, B_P = B_S + 2, B_O = B_P + 2;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem_gen + C::OFF_BAR + 8 * C::NUM_BARS);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const int bh = blockIdx.x;
+    const int qblock = gridDim.y - 1 - blockIdx.y;  // heaviest (latest) causal rows first
+    const int q_base = qblock * 256;
+    const int off = p.lk - p.lq;
+
+    // number of key tiles each query tile visits
+    int n_t[2];
+#pragma unroll
+    for (int t = 0; t < 2; t++) {
+        const int qs = q_base + t * 128;
+        if (qs >= p.lq) {
+            n_t[t] = 0;
+        } else {
+            const int visible = p.causal ? min(p.lk, qs + 128 + off) : p.lk;
+            n_t[t] = (visible + 127) / 128;
+        }
+    }
+    const int n = max(n_t[0], n_t[1]);
+
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        mbar_init(BAR(B_Q), 1);
+        for (int s = 0; s < C::STAGES; s++) {
+            mbar_init(BAR(B_KFULL + s), 1);
+            mbar_init(BAR(B_KEMPTY + s), 1);
+            mbar_init(BAR(B_VFULL + s), 1);
+            mbar_init(BAR(B_VEMPTY + s), 1);
+        }
+        for (int t = 0; t < 2; t++) {
+            mbar_init(BAR(B_S + t), 1);
+            mbar_init(BAR(B_P + t), 128);
+            mbar_init(BAR(B_O + t), 1);
+        }
+        fence_mbar_init();
+    }
+    if (warp == 10) {
+        tmem_alloc(smem_u32(tmem_slot), 512);
+        tmem_relinquish();
+    }
+    if (warp == 9 && lane == 0) {
+        prefetch_tensormap(&tm_q);
+        prefetch_tensormap(&tm_k);
+        prefetch_tensormap(&tm_v);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp >= 8) {
+        reg_dealloc_40();
+        if (warp == 9 && lane == 0) {
+            // ------------------------------------------------------------ TMA producer
+            const int ntiles_q = (n_t[1] > 0) ? 2 : 1;
+            mbar_arrive_expect_tx(BAR(B_Q), ntiles_q * C::TILE_BYTES);
+            for (int t = 0; t < ntiles_q; t++)
+                for (int s = 0; s < C::NSUB; s++)
+                    tma_load_3d(smem_base + C::OFF_Q + t * C::TILE_BYTES + s * C::SUB_BYTES, &tm_q,
+                                BAR(B_Q), s * 64, q_base + t * 128, bh);
+            int k_issued = 0, v_issued = 0;
+            for (int j = 0; j < n; j++) {
+                const int st = j % C::STAGES;
+                const uint32_t ph = (j / C::STAGES) & 1;
+                if (!mbar_wait(BAR(B_KEMPTY + st), ph ^ 1, abort_flag, p.status, W_TMA_KEMPTY)) break;
+                mbar_arrive_expect_tx(BAR(B_KFULL + st), C::TILE_BYTES);
+                for (int s = 0; s < C::NSUB; s++)
+                    tma_load_3d(smem_base + C::OFF_K + st * C::TILE_BYTES + s * C::SUB_BYTES, &tm_k,
+                                BAR(B_KFULL + st), s * 64, j * 128, bh);
+                k_issued = j + 1;
+                if (!mbar_wait(BAR(B_VEMPTY + st), ph ^ 1, abort_flag, p.status, W_TMA_VEMPTY)) break;
+                mbar_arrive_expect_tx(BAR(B_VFULL + st), C::TILE_BYTES);
+                for (int s = 0; s < C::NSUB; s++)
+                    tma_load_3d(smem_base + C::OFF_V + st * C::TILE_BYTES + s * C::SUB_BYTES, &tm_v,
+                                BAR(B_VFULL + st), s * 64, j * 128, bh);
+                v_issued = j + 1;
+            }
+            // Do not leave the CTA while one of its own copies is still landing in shared memory:
+            // a bounded poll (ignoring the abort flag; a copy that was issued always completes) on
+            // the full-barrier of every stage still in flight.
+            const long long t0 = clock64();
+            for (int j = max(0, k_issued - C::STAGES); j < k_issued; j++)
+                while (!mbar_try_wait(BAR(B_KFULL + j % C::STAGES), (j / C::STAGES) & 1) &&
+                       clock64() - t0 < kWaitLimitCycles) {}
+            for (int j = max(0, v_issued - C::STAGES); j < v_issued; j++)
+                while (!mbar_try_wait(BAR(B_VFULL + j % C::STAGES), (j / C::STAGES) & 1) &&
+                       clock64() - t0 < kWaitLimitCycles) {}
+            while (!mbar_try_wait(BAR(B_Q), 0) && clock64() - t0 < kWaitLimitCycles) {}
+        } else if (warp == 8 && lane == 0) {
+            // ------------------------------------------------------------ MMA issue
+            constexpr uint32_t IDESC_S = idesc_bf16_f32(128, 128, 0, 0);
+            constexpr uint32_t IDESC_O = idesc_bf16_f32(128, HD, 0, 1);
+            auto issue_s = [&](int t, int st) {
+                const uint32_t qa = smem_base + C::OFF_Q + t * C::TILE_BYTES;
+                const uint32_t ka = smem_base + C::OFF_K + st * C::TILE_BYTES;
+#pragma unroll
+                for (int ks = 0; ks < HD / 16; ks++) {
+                    const uint32_t o = (ks / 4) * C::SUB_BYTES + (ks % 4) * 32;
+                    mma_ss(tmem + C::TMEM_S + t * 128, smem_desc_sw128(qa + o, 16, 1024),
+                           smem_desc_sw128(ka + o, 16, 1024), IDESC_S, ks > 0);
+                }
+                tc_commit(BAR(B_S + t));
+            };
+            auto issue_pv = [&](int t, int st, bool first) {
+                const uint32_t va = smem_base + C::OFF_V + st * C::TILE_BYTES;
+#pragma unroll
+                for (int ks = 0; ks < 8; ks++) {
+                    mma_ts(tmem + C::TMEM_O + t * HD, tmem + C::TMEM_S + t * 128 + ks * 8,
+                           smem_desc_sw128(va + ks * 2048, C::SUB_BYTES, 1024), IDESC_O,
+                           (!first || ks > 0) ? 1u : 0u);
+                }
+                tc_commit(BAR(B_O + t));
+            };
+
+            bool ok = mbar_wait(BAR(B_Q), 0, abort_flag, p.status, W_MMA_Q);
+            ok = ok && mbar_wait(BAR(B_KFULL + 0), 0, abort_flag, p.status, W_MMA_K);
+            tc_fence_after();
+            if (n_t[0] > 0) issue_s(0, 0);
+            if (n_t[1] > 0) issue_s(1, 0);
+            tc_commit(BAR(B_KEMPTY + 0));
+            for (int j = 0; j < n && ok; j++) {
+                const int st = j % C::STAGES;
+                const uint32_t ph = (j / C::STAGES) & 1;
+                const int st1 = (j + 1) % C::STAGES;
+                const uint32_t ph1 = ((j + 1) / C::STAGES) & 1;
+                ok = ok && mbar_wait(BAR(B_VFULL + st), ph, abort_flag, p.status, W_MMA_V);
+                bool k_next_ready = false;
+#pragma unroll
+                for (int t = 0; t < 2; t++) {
+                    if (j < n_t[t]) {
+                        ok = ok && mbar_wait(BAR(B_P + t), j & 1, abort_flag, p.status, W_MMA_P);
+                        tc_fence_after();
+                        issue_pv(t, st, j == 0);
+                    }
+                    if (j + 1 < n_t[t]) {
+                        if (!k_next_ready) {
+                            ok = ok && mbar_wait(BAR(B_KFULL + st1), ph1, abort_flag, p.status, W_MMA_K);
+                            tc_fence_after();
+                            k_next_ready = true;
+                        }
+                        issue_s(t, st1);
+                    }
+                }
+                tc_commit(BAR(B_VEMPTY + st));
+                if (j + 1 < n) tc_commit(BAR(B_KEMPTY + st1));
+            }
+        }
+    } else {
+        // ---------------------------------------------------------------- softmax + epilogue
+        reg_alloc_232();
+        const int t = warp / 4;                   // which query tile
+        const int r = threadIdx.x % 128;          // row inside the tile == TMEM lane
+        const int row = q_base + t * 128 + r;     // query row
+        const uint32_t lane_sel = (uint32_t)((warp % 4) * 32) << 16;
+        const uint32_t ts = tmem + lane_sel + C::TMEM_S + t * 128;
+        const uint32_t to = tmem + lane_sel + C::TMEM_O + t * HD;
+        const int nk = n_t[t];
+        const float c = p.scale_log2;
+        const int limit_row = p.causal ? min(p.lk - 1, row + off) : p.lk - 1;
+        const int limit_tile = p.causal ? min(p.lk - 1, q_base + t * 128 + off) : p.lk - 1;
+
+        float m_ref = -INFINITY, l = 0.f;
+        bool ok = true;
+        for (int j = 0; j < nk; j++) {
+            ok = ok && mbar_wait(BAR(B_S + t), j & 1, abort_flag, p.status, W_SM_S);
+            tc_fence_after();
+            float s[128];
+#pragma unroll
+            for (int ch = 0; ch < 4; ch++) {
+                uint32_t u[32];
+                tmem_ld_32x32b_x32(ts + ch * 32, u);
+#pragma unroll
+                for (int i = 0; i < 32; i++) s[ch * 32 + i] = __uint_as_float(u[i]);
+            }
+            tmem_wait_ld();
+
+            if (j * 128 + 127 > limit_tile) {
+#pragma unroll
+                for (int i = 0; i < 128; i++)
+                    if (j * 128 + i > limit_row) s[i] = (c > 0.f) ? -INFINITY : INFINITY;
+            }
+            float mx;
+            if (c > 0.f) {
+                mx = s[0];
+#pragma unroll
+                for (int i = 1; i < 128; i++) mx = fmaxf(mx, s[i]);
+            } else {
+                mx = s[0];
+#pragma unroll
+                for (int i = 1; i < 128; i++) mx = fminf(mx, s[i]);
+            }
+            const float m_new = fmaxf(m_ref, mx * c);
+            if (j == 0) {
+                m_ref = m_new;  // finite: key 0 is visible to every row
+            } else {
+                const bool need = (m_new - m_ref) > RESCALE_THRESHOLD;
+                if (__any_sync(0xffffffffu, need)) {
+                    const float alpha = ex2(m_ref - m_new);
+                    m_ref = m_new;
+                    l *= alpha;
+                    ok = ok && mbar_wait(BAR(B_O + t), (j - 1) & 1, abort_flag, p.status, W_SM_O);
+                    tc_fence_after();
+#pragma unroll
+                    for (int ch = 0; ch < HD / 32; ch++) {
+                        uint32_t o[32];
+                        tmem_ld_32x32b_x32(to + ch * 32, o);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 32; i++) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                        tmem_st_32x32b_x32(to + ch * 32, o);
+                    }
+                }
+            }
+            const float neg_m = -m_ref;
+            float sum = 0.f;
+#pragma unroll
+            for (int ch = 0; ch < 4; ch++) {
+                uint32_t pk[16];
+#pragma unroll
+                for (int i = 0; i < 16; i++) {
+                    const float p0 = ex2(fmaf(s[ch * 32 + 2 * i], c, neg_m));
+                    const float p1 = ex2(fmaf(s[ch * 32 + 2 * i + 1], c, neg_m));
+                    sum += p0 + p1;
+                    pk[i] = pack_bf16(p0, p1);
+                }
+                tmem_st_32x32b_x16(ts + ch * 16, pk);
+            }
+            l += sum;
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(BAR(B_P + t));
+        }
+
+        if (nk > 0) {
+            ok = ok && mbar_wait(BAR(B_O + t), (nk - 1) & 1, abort_flag, p.status, W_SM_OFINAL);
+            tc_fence_after();
+            const float inv = 1.f / l;
+            const bool store = ok && row < p.lq;
+            __nv_bfloat16 *orow = p.out + ((size_t)bh * p.lq + row) * HD;
+#pragma unroll
+            for (int ch = 0; ch < HD / 32; ch++) {
+                uint32_t o[32];
+                tmem_ld_32x32b_x32(to + ch * 32, o);
+                tmem_wait_ld();
+                if (store) {
+#pragma unroll
+                    for (int v4 = 0; v4 < 4; v4++) {
+                        uint4 w;
+                        w.x = pack_bf16(__uint_as_float(o[v4 * 8 + 0]) * inv, __uint_as_float(o[v4 * 8 + 1]) * inv);
+                        w.y = pack_bf16(__uint_as_float(o[v4 * 8 + 2]) * inv, __uint_as_float(o[v4 * 8 + 3]) * inv);
+                        w.z = pack_bf16(__uint_as_float(o[v4 * 8 + 4]) * inv, __uint_as_float(o[v4 * 8 + 5]) * inv);
+                        w.w = pack_bf16(__uint_as_float(o[v4 * 8 + 6]) * inv, __uint_as_float(o[v4 * 8 + 7]) * inv);
+                        *reinterpret_cast<uint4 *>(orow + ch * 32 + v4 * 8) = w;
+                    }
+                }
+            }
+            if (store && p.lse) p.lse[(size_t)bh * p.lq + row] = (m_ref + log2f(l)) * LN2_F;
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 10) tmem_dealloc(tmem, 512);
+}
+
+template <int HD>
+int launch(const AttnArgs &a, DeviceState *st, cudaStream_t s)
+{
+    using C = FwdCfg<HD>;
+    CUtensorMap tq, tk, tv;
+    int rc;
+    if ((rc = make_tensor_map_bf16_3d(&tq, a.q, HD, a.lq, a.bh, 64, 128)) != EMBER_OK) return rc;
+    if ((rc = make_tensor_map_bf16_3d(&tk, a.k, HD, a.lk, a.bh, 64, 128)) != EMBER_OK) return rc;
+    if ((rc = make_tensor_map_bf16_3d(&tv, a.v, HD, a.lk, a.bh, 64, 128)) != EMBER_OK) return rc;
+    FwdParams p;
+    p.out = (__nv_bfloat16 *)a.out;
+    p.lse = a.lse;
+    p.lq = a.lq;
+    p.lk = a.lk;
+    p.causal = a.causal;
+    p.scale_log2 = a.scale * LOG2E_F;
+    p.status = st->status;
+    auto kern = sm100_fwd_kernel<HD>;
+    EMBER_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+    dim3 grid(a.bh, (a.lq + 255) / 256);
+    kern<<<grid, FWD_THREADS, C::SMEM_BYTES, s>>>(tq, tk, tv, p);
+    EMBER_CUDA_TRY(cudaGetLastError());
+    return EMBER_OK;
+}
+
+}  // namespace
+
+bool sm100_fwd_supported(const AttnArgs &a)
+{
+    if (a.dtype != EMBER_BF16) return false;
+    if (a.d != 64 && a.d != 128) return false;
+    if (!(a.scale != 0.f) || !isfinite(a.scale)) return false;
+    if ((a.lq + 255) / 256 > 65535) return false;
+    // TMA needs 16-byte aligned bases; the epilogue stores 16-byte vectors.
+    const uintptr_t bits = (uintptr_t)a.q | (uintptr_t)a.k | (uintptr_t)a.v | (uintptr_t)a.out;
+    return (bits & 15) == 0;
+}
+
+int sm100_attention_fwd(const AttnArgs &a, DeviceState *st, cudaStream_t s)
+{
+    return a.d == 128 ? launch<128>(a, st, s) : launch<64>(a, st, s);
+}
+
+}  // namespace ember

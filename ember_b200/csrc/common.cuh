@@ -1,0 +1,59 @@
+// Shared host-side plumbing of the attention library: per-device state (stream,
+// device status word), error reporting, argument checks.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "../../include/ember_b200.h"
+
+namespace ember {
+
+// Written by device code when a bounded wait gives up. code != 0 means a fault was recorded.
+struct DeviceStatus {
+    int code;   // ember_status (EMBER_ERR_TIMEOUT)
+    int where;  // which wait (kernel-specific code)
+    int block;  // linear block index of the first reporter
+    int extra;
+};
+
+struct DeviceState {
+    bool ready = false;
+    cudaStream_t stream = nullptr;
+    DeviceStatus *status = nullptr;  // device memory
+    int sm_count = 0;
+};
+
+// State of the current device, created on first use. Returns nullptr and sets the error
+// text when CUDA is unusable.
+DeviceState *device_state();
+
+void set_error(const char *fmt, ...);
+int cuda_fail(cudaError_t e, const char *what);
+
+inline cudaStream_t pick_stream(void *stream, DeviceState *st)
+{
+    return stream ? reinterpret_cast<cudaStream_t>(stream) : st->stream;
+}
+
+#define EMBER_CUDA_TRY(expr)                                        \
+    do {                                                            \
+        cudaError_t _e = (expr);                                    \
+        if (_e != cudaSuccess) return ::ember::cuda_fail(_e, #expr); \
+    } while (0)
+
+#define EMBER_REQUIRE(cond, ...)             \
+    do {                                     \
+        if (!(cond)) {                       \
+            ::ember::set_error(__VA_ARGS__); \
+            return EMBER_ERR_INVALID;        \
+        }                                    \
+    } while (0)
+
+inline size_t dtype_size(int dtype) { return dtype == EMBER_BF16 ? 2 : 4; }
+
+inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+}  // namespace ember

@@ -1,0 +1,209 @@
+// Device-buffer / stream plumbing of the attention library: the five memory entry points the
+// reference declares in src/core/memory.h:10-14, re-implemented stream-ordered, plus device
+// selection, bf16 conversion and status reporting.
+#include <stdarg.h>
+#include <string.h>
+
+#include "common.cuh"
+
+namespace ember {
+
+static thread_local char g_err[512] = "";
+static const int kMaxDevices = 64;
+static DeviceState g_dev[kMaxDevices];
+
+void set_error(const char *fmt, ...)
+{
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+}
+
+int cuda_fail(cudaError_t e, const char *what)
+{
+    set_error("CUDA error %d (%s) in %s", (int)e, cudaGetErrorString(e), what);
+    return e == cudaErrorMemoryAllocation ? EMBER_ERR_NOMEM : EMBER_ERR_CUDA;
+}
+
+DeviceState *device_state()
+{
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) {
+        cuda_fail(e, "cudaGetDevice");
+        return nullptr;
+    }
+    if (dev < 0 || dev >= kMaxDevices) {
+        set_error("device index %d out of range", dev);
+        return nullptr;
+    }
+    DeviceState *st = &g_dev[dev];
+    if (st->ready) return st;
+    if ((e = cudaStreamCreateWithFlags(&st->stream, cudaStreamNonBlocking)) != cudaSuccess) {
+        cuda_fail(e, "cudaStreamCreateWithFlags");
+        return nullptr;
+    }
+    if ((e = cudaMalloc(&st->status, sizeof(DeviceStatus))) != cudaSuccess ||
+        (e = cudaMemset(st->status, 0, sizeof(DeviceStatus))) != cudaSuccess) {
+        cuda_fail(e, "status word allocation");
+        return nullptr;
+    }
+    cudaDeviceGetAttribute(&st->sm_count, cudaDevAttrMultiProcessorCount, dev);
+    // Keep freed blocks in the pool instead of returning them to the driver at every sync.
+    cudaMemPool_t pool;
+    if (cudaDeviceGetDefaultMemPool(&pool, dev) == cudaSuccess) {
+        uint64_t thr = UINT64_MAX;
+        cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &thr);
+    }
+    st->ready = true;
+    return st;
+}
+
+template <typename In, typename Out>
+__global__ void convert_kernel(const In *__restrict__ src, Out *__restrict__ dst, size_t n)
+{
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; i < n; i += stride) {
+        if constexpr (sizeof(In) == 4)
+            dst[i] = __float2bfloat16_rn(src[i]);
+        else
+            dst[i] = __bfloat162float(src[i]);
+    }
+}
+
+}  // namespace ember
+
+using namespace ember;
+
+extern "C" {
+
+void *alloc_memory(size_t bytes)
+{
+    DeviceState *st = device_state();
+    if (!st) return nullptr;
+    void *p = nullptr;
+    cudaError_t e = cudaMallocAsync(&p, bytes ? bytes : 1, st->stream);
+    if (e != cudaSuccess) {
+        cuda_fail(e, "cudaMallocAsync");
+        cudaGetLastError();
+        return nullptr;
+    }
+    return p;
+}
+
+void free_memory(void *ptr)
+{
+    if (!ptr) return;
+    DeviceState *st = device_state();
+    if (!st) return;
+    cudaFreeAsync(ptr, st->stream);
+}
+
+void copy_to_device(void *dst_device, const void *src_host, size_t bytes)
+{
+    DeviceState *st = device_state();
+    if (!st) return;
+    cudaError_t e = cudaMemcpyAsync(dst_device, src_host, bytes, cudaMemcpyHostToDevice, st->stream);
+    // Pageable sources are staged before the call returns; pinned ones are not, so wait: the
+    // reference's copy is synchronous (src/core/memory_gpu.cu:32) and callers may reuse src.
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st->stream);
+    if (e != cudaSuccess) cuda_fail(e, "copy_to_device");
+}
+
+void copy_from_device(void *dst_host, const void *src_device, size_t bytes)
+{
+    DeviceState *st = device_state();
+    if (!st) return;
+    cudaError_t e = cudaMemcpyAsync(dst_host, src_device, bytes, cudaMemcpyDeviceToHost, st->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st->stream);
+    if (e != cudaSuccess) cuda_fail(e, "copy_from_device");
+}
+
+void sync_device(void)
+{
+    DeviceState *st = device_state();
+    if (!st) return;
+    cudaError_t e = cudaStreamSynchronize(st->stream);
+    if (e != cudaSuccess) cuda_fail(e, "sync_device");
+}
+
+int ember_set_device(int device)
+{
+    EMBER_CUDA_TRY(cudaSetDevice(device));
+    return device_state() ? EMBER_OK : EMBER_ERR_CUDA;
+}
+
+int ember_get_device(int *device)
+{
+    EMBER_REQUIRE(device != nullptr, "ember_get_device: NULL argument");
+    EMBER_CUDA_TRY(cudaGetDevice(device));
+    return EMBER_OK;
+}
+
+void *ember_stream(void)
+{
+    DeviceState *st = device_state();
+    return st ? (void *)st->stream : nullptr;
+}
+
+int ember_f32_to_bf16(const float *src, void *dst, size_t n, void *stream)
+{
+    DeviceState *st = device_state();
+    if (!st) return EMBER_ERR_CUDA;
+    EMBER_REQUIRE(src && dst, "ember_f32_to_bf16: NULL pointer");
+    if (n == 0) return EMBER_OK;
+    int blocks = (int)((n + 255) / 256 < (size_t)st->sm_count * 16 ? (n + 255) / 256 : (size_t)st->sm_count * 16);
+    convert_kernel<float, __nv_bfloat16><<<blocks, 256, 0, pick_stream(stream, st)>>>(src, (__nv_bfloat16 *)dst, n);
+    EMBER_CUDA_TRY(cudaGetLastError());
+    return EMBER_OK;
+}
+
+int ember_bf16_to_f32(const void *src, float *dst, size_t n, void *stream)
+{
+    DeviceState *st = device_state();
+    if (!st) return EMBER_ERR_CUDA;
+    EMBER_REQUIRE(src && dst, "ember_bf16_to_f32: NULL pointer");
+    if (n == 0) return EMBER_OK;
+    int blocks = (int)((n + 255) / 256 < (size_t)st->sm_count * 16 ? (n + 255) / 256 : (size_t)st->sm_count * 16);
+    convert_kernel<__nv_bfloat16, float><<<blocks, 256, 0, pick_stream(stream, st)>>>((const __nv_bfloat16 *)src, dst, n);
+    EMBER_CUDA_TRY(cudaGetLastError());
+    return EMBER_OK;
+}
+
+const char *ember_status_string(int status)
+{
+    switch (status) {
+        case EMBER_OK: return "ok";
+        case EMBER_ERR_INVALID: return "invalid argument";
+        case EMBER_ERR_UNSUPPORTED: return "unsupported configuration";
+        case EMBER_ERR_CUDA: return "CUDA error";
+        case EMBER_ERR_TIMEOUT: return "device-side wait timed out";
+        case EMBER_ERR_NOMEM: return "out of device memory";
+        case EMBER_ERR_WORKSPACE: return "workspace missing or too small";
+        default: return "unknown status";
+    }
+}
+
+const char *ember_last_error(void) { return g_err; }
+
+int ember_check_device_status(void *stream, int *where)
+{
+    DeviceState *st = device_state();
+    if (!st) return EMBER_ERR_CUDA;
+    cudaStream_t s = pick_stream(stream, st);
+    DeviceStatus h;
+    EMBER_CUDA_TRY(cudaMemcpyAsync(&h, st->status, sizeof(h), cudaMemcpyDeviceToHost, s));
+    EMBER_CUDA_TRY(cudaStreamSynchronize(s));
+    if (where) *where = h.where;
+    if (h.code != 0) {
+        set_error("device-side wait gave up: where=%d block=%d extra=%d", h.where, h.block, h.extra);
+        EMBER_CUDA_TRY(cudaMemsetAsync(st->status, 0, sizeof(DeviceStatus), s));
+        EMBER_CUDA_TRY(cudaStreamSynchronize(s));
+        return EMBER_ERR_TIMEOUT;
+    }
+    return EMBER_OK;
+}
+
+}  // extern "C"

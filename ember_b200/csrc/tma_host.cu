@@ -1,0 +1,51 @@
+// Host-side construction of TMA tensor maps. The driver's encoder is reached through
+// cudaGetDriverEntryPoint, so the library does not link against libcuda.
+#include "ptx.cuh"
+
+namespace ember {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn()
+{
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// A (batch, rows, inner) row-major bf16 tensor viewed as a 3-D TMA tensor; boxes of
+// box_rows x box_inner elements with the 128-byte swizzle (box_inner * 2 bytes must be 128).
+// Out-of-range parts of a box read as zero.
+int make_tensor_map_bf16_3d(CUtensorMap *map, const void *base, uint64_t inner, uint64_t rows,
+                            uint64_t batch, uint32_t box_inner, uint32_t box_rows)
+{
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) {
+        set_error("cuTensorMapEncodeTiled is not available from this driver");
+        return EMBER_ERR_CUDA;
+    }
+    cuuint64_t dims[3] = {inner, rows, batch};
+    cuuint64_t strides[2] = {inner * 2, rows * inner * 2};
+    cuuint32_t box[3] = {box_inner, box_rows, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(base), dims, strides, box,
+                    estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_error("cuTensorMapEncodeTiled failed with CUresult %d (inner=%llu rows=%llu batch=%llu)", (int)r,
+                  (unsigned long long)inner, (unsigned long long)rows, (unsigned long long)batch);
+        return EMBER_ERR_CUDA;
+    }
+    return EMBER_OK;
+}
+
+}  // namespace ember

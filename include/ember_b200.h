@@ -1,0 +1,134 @@
+/* ember_b200.h -- C ABI of the B200 (sm_100a) attention library.
+ *
+ * This header is the drop-in boundary: the declarations a binding for the
+ * reference project (its CPython extension module built from
+ * src/tensor/tensor_api.c) would call, in the style of the reference's own
+ * operator header (src/tensor/operators.h:21-27: raw device pointers, integer
+ * extents, caller-allocated outputs) and memory header (src/core/memory.h:10-14).
+ *
+ * Conventions
+ *   - All tensor pointers are DEVICE pointers to contiguous row-major buffers,
+ *     the only layout the reference has (ember/tensor/tensor_utils.py:85-94).
+ *     q: (batch_heads, lq, d)   k, v: (batch_heads, lk, d)   out: like q
+ *     lse: (batch_heads, lq) float32, natural-log log-sum-exp of the scaled,
+ *     masked scores of each query row.
+ *   - dtype selects the storage type of q/k/v/out/dout/dq/dk/dv: EMBER_F32 or
+ *     EMBER_BF16. Softmax and all accumulation are float32 in both modes.
+ *   - causal != 0 masks key j for query i when j > i + (lk - lq) (lower
+ *     triangle aligned to the bottom-right corner; requires lq <= lk). This is
+ *     the additive {0,-inf} mask the reference would need a broadcast add for
+ *     (src/tensor/operators.def:65).
+ *   - stream is a cudaStream_t passed as void*; NULL means the library's own
+ *     non-blocking stream of the current device (see ember_stream()).
+ *     Calls enqueue work and return; nothing synchronises except where stated.
+ *   - Every function returning int returns an ember_status. The library never
+ *     calls exit() (the reference's GPU_ERR_CHK does: src/core/utils_gpu.cuh:9-19).
+ *   - Not thread-safe, like the reference (its cuBLAS handle is a bare static:
+ *     src/tensor/operators_gpu.cu:24-31).
+ */
+#ifndef EMBER_B200_H
+#define EMBER_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define EMBER_API __attribute__((visibility("default")))
+#else
+#define EMBER_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+    EMBER_OK = 0,
+    EMBER_ERR_INVALID = 1,     /* bad shape, NULL pointer, misaligned pointer */
+    EMBER_ERR_UNSUPPORTED = 2, /* valid request this build has no kernel for  */
+    EMBER_ERR_CUDA = 3,        /* a CUDA runtime/driver call failed           */
+    EMBER_ERR_TIMEOUT = 4,     /* a bounded device-side wait gave up          */
+    EMBER_ERR_NOMEM = 5,       /* device allocation failed                    */
+    EMBER_ERR_WORKSPACE = 6    /* workspace missing or too small              */
+} ember_status;
+
+enum { EMBER_F32 = 0, EMBER_BF16 = 1 };
+
+/* Which operation a workspace is sized for. */
+enum { EMBER_OP_FWD = 0, EMBER_OP_BWD = 1, EMBER_OP_DECODE = 2 };
+
+/* ---- device memory: same five entry points, same meaning, as the reference's
+ *      src/core/memory.h:10-14 (GPU implementation: src/core/memory_gpu.cu:10-43).
+ *      alloc_memory returns NULL on failure (memory_gpu.cu:15-19). Allocation is
+ *      stream-ordered on the library stream instead of one cudaMalloc/cudaFree
+ *      per tensor; copies are ordered on that stream and copy_from_device
+ *      waits for it, as the reference's synchronous cudaMemcpy does. ---- */
+EMBER_API void *alloc_memory(size_t bytes);
+EMBER_API void free_memory(void *ptr);
+EMBER_API void copy_to_device(void *dst_device, const void *src_host, size_t bytes);
+EMBER_API void copy_from_device(void *dst_host, const void *src_device, size_t bytes);
+EMBER_API void sync_device(void);
+
+/* ---- additions the attention path needs from src/core (no counterpart in the
+ *      reference, which is single-device, default-stream, float32-only) ---- */
+EMBER_API int ember_set_device(int device);
+EMBER_API int ember_get_device(int *device);
+EMBER_API void *ember_stream(void); /* the library's stream of the current device, as cudaStream_t */
+EMBER_API int ember_f32_to_bf16(const float *src, void *dst, size_t n, void *stream);
+EMBER_API int ember_bf16_to_f32(const void *src, float *dst, size_t n, void *stream);
+EMBER_API const char *ember_status_string(int status);
+/* Text of the most recent failure on this thread's last call ("" if none). */
+EMBER_API const char *ember_last_error(void);
+/* Reads and clears the device-side status word written by bounded waits.
+ * Synchronises the stream. Returns EMBER_OK or EMBER_ERR_TIMEOUT; *where gets
+ * the code of the wait that gave up (0 if none). */
+EMBER_API int ember_check_device_status(void *stream, int *where);
+
+/* ---- attention forward (prefill, optionally causal). Replaces the composed
+ *      reference path  softmax((q @ kT) * scale [+ mask]) @ v :
+ *      ember/tensor/tensor.py:163-197 (__matmul__) -> src/tensor/tensor_api.c:330-354
+ *      -> src/tensor/operators_gpu.cu:126-136 (cublasSgemmStridedBatched), scalar
+ *      multiply src/tensor/operators.def:54, softmax ember/tensor/tensor.py:430-437
+ *      (max_axis src/tensor/operators_gpu.cu:198-219, sum_axis :175-196).
+ *      k is taken in its natural (batch_heads, lk, d) layout; no host transpose.
+ *      lse may be NULL when the caller does not need it. ---- */
+EMBER_API int ember_attention_fwd(const void *q, const void *k, const void *v, void *out, float *lse,
+                        int batch_heads, int lq, int lk, int d, float scale, int causal, int dtype,
+                        void *stream);
+
+/* ---- attention backward. Replaces the manual-backward composition the
+ *      reference's layers use (ember/nn/layers.py:50-56; softmax gradient as in
+ *      ember/loss/losses.py:53-56): dV = P^T dO, dP = dO V^T, dS = P*(dP - delta)*scale,
+ *      dQ = dS K, dK = dS^T Q, with P recomputed from the saved lse.
+ *      workspace: ember_attention_workspace_bytes(EMBER_OP_BWD, ...) bytes of
+ *      device memory, 256-byte aligned, contents undefined on entry. ---- */
+EMBER_API int ember_attention_bwd(const void *q, const void *k, const void *v, const void *out,
+                        const float *lse, const void *dout, void *dq, void *dk, void *dv,
+                        int batch_heads, int lq, int lk, int d, float scale, int causal, int dtype,
+                        void *workspace, size_t workspace_bytes, void *stream);
+
+/* ---- single-query decode against a long key/value cache (lq == 1, no mask),
+ *      split over the key axis with a log-sum-exp combine. Same reference path as
+ *      the forward with n = 1 rows per batch (src/tensor/operators_gpu.cu:126-136).
+ *      num_splits <= 0 lets the library choose. workspace as above with
+ *      EMBER_OP_DECODE (may be NULL/0 when the chosen split count is 1). ---- */
+EMBER_API int ember_attention_decode(const void *q, const void *k, const void *v, void *out, float *lse,
+                           int batch_heads, int lk, int d, float scale, int dtype, int num_splits,
+                           void *workspace, size_t workspace_bytes, void *stream);
+
+/* Bytes of workspace the call with these arguments needs (0 if none). For
+ * EMBER_OP_DECODE lq is ignored; num_splits <= 0 means "the library's choice". */
+EMBER_API size_t ember_attention_workspace_bytes(int op, int batch_heads, int lq, int lk, int d, int dtype,
+                                       int num_splits);
+/* The split count ember_attention_decode uses for num_splits <= 0. */
+EMBER_API int ember_attention_decode_splits(int batch_heads, int lk, int d, int dtype);
+
+/* Name of the kernel family the forward/backward dispatcher picks for these
+ * arguments: "sm100_tcgen05" or "simt_f32". For tests and the benchmark. */
+EMBER_API const char *ember_attention_kernel_name(int op, int lq, int lk, int d, int dtype);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* EMBER_B200_H */

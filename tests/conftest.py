@@ -1,0 +1,44 @@
+import os
+import sys
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests", "golden"))
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (B200); run with -m gpu")
+
+
+def bf16_round(x: np.ndarray) -> np.ndarray:
+    """Round float32 values to the nearest bfloat16 (ties to even), returned as float32."""
+    u = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32).astype(np.uint64)
+    r = ((u + 0x7FFF + ((u >> 16) & 1)) >> 16) << 16
+    return r.astype(np.uint32).view(np.float32).reshape(x.shape)
+
+
+@pytest.fixture(scope="session")
+def golden():
+    return np.load(os.path.join(ROOT, "tests", "golden", "attention_golden.npz"))
+
+
+def golden_inputs(meta, with_dout=False):
+    from inputs import normal
+
+    B, H, Lq, Lk, D, causal, seed = (int(x) for x in meta)
+    q = normal(seed, (B, H, Lq, D))
+    k = normal(seed + 100, (B, H, Lk, D))
+    v = normal(seed + 200, (B, H, Lk, D))
+    out = [q, k, v]
+    if with_dout:
+        out.append(normal(seed + 300, (B, H, Lq, D)))
+    return out, bool(causal)
+
+
+def seeded(shape, seed, scale=1.0):
+    rng = np.random.default_rng(seed)
+    return (rng.standard_normal(shape, dtype=np.float32) * np.float32(scale)).astype(np.float32)

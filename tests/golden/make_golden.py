@@ -1,0 +1,102 @@
+"""Generates tests/golden/attention_golden.npz by running the REFERENCE itself.
+
+Run in a container that has the reference checkout (default /root/reference):
+
+    make -C oracle ref && python tests/golden/make_golden.py
+
+The reference's Python package is copied to a scratch directory under /tmp
+together with the two CPython extension modules that ``make -C oracle ref``
+compiled from the reference's unmodified C sources (CPU backend), imported as
+``ember`` from there, and attention is composed from its public operators:
+
+    forward : em.softmax((q @ kT) * scale [+ mask], axis=-1) @ v
+    backward: dV = pT @ dO ; dP = dO @ vT ; delta = em.sum(dP * p, -1, keepdims)
+              dS = (p * (dP - delta)) * scale ; dQ = dS @ k ; dK = dST @ q
+
+Transposes of rank-4 tensors are done in NumPy because the reference's
+transpose is 2-D only. Inputs come from the bit-reproducible generator in
+``inputs.py`` (seeds: q = seed, k = seed+100, v = seed+200, dO = seed+300), so the
+fixture file stores outputs only.
+"""
+import glob
+import os
+import shutil
+import sys
+import tempfile
+
+import numpy as np
+
+REF = os.environ.get("EMBER_REFERENCE", "/root/reference")
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, HERE)
+from inputs import normal  # noqa: E402
+
+ROOT = os.path.dirname(os.path.dirname(HERE))
+
+CASES = {
+    # name: (B, H, Lq, Lk, D, causal, seed, with_backward)
+    "c1_fwd_f32": (2, 4, 128, 128, 64, False, 1, False),  # BASELINE configs[0]
+    "c1_causal": (1, 2, 128, 128, 64, True, 2, True),
+    "ragged_causal": (1, 2, 48, 80, 32, True, 3, True),
+    "ragged_noncausal": (1, 3, 37, 129, 64, False, 4, True),
+    "decode": (2, 2, 1, 300, 64, False, 5, False),
+    "d128": (1, 1, 130, 130, 128, True, 6, True),
+}
+
+
+def import_reference():
+    tmp = tempfile.mkdtemp(prefix="ember_ref_")
+    shutil.copytree(os.path.join(REF, "ember"), os.path.join(tmp, "ember"))
+    sos = glob.glob(os.path.join(ROOT, "oracle", "_ref", "ember", "_core", "*.so"))
+    assert len(sos) == 2, "run `make -C oracle ref` first"
+    for so in sos:
+        shutil.copy(so, os.path.join(tmp, "ember", "_core"))
+    sys.path.insert(0, tmp)
+    import ember  # noqa
+
+    return ember
+
+
+def main():
+    em = import_reference()
+    T = em.Tensor
+    out = {}
+    for name, (B, H, Lq, Lk, D, causal, seed, bwd) in CASES.items():
+        q = normal(seed, (B, H, Lq, D))
+        k = normal(seed + 100, (B, H, Lk, D))
+        v = normal(seed + 200, (B, H, Lk, D))
+        scale = float(1.0 / np.sqrt(D))
+        tq, tv = T(q), T(v)
+        tkT = T(np.ascontiguousarray(np.swapaxes(k, -1, -2)))
+        s = (tq @ tkT) * scale
+        if causal:
+            i = np.arange(Lq)[:, None]
+            j = np.arange(Lk)[None, :]
+            mask = np.where(j > i + (Lk - Lq), -np.inf, 0.0).astype(np.float32)
+            s = s + T(mask)
+        p = em.softmax(s, axis=-1)
+        o = p @ tv
+        mx = em.amax(s, axis=-1, keepdims=True)
+        se = em.sum(em.exp(s - mx), axis=-1, keepdims=True)
+        lse = mx.to_np().astype(np.float64) + np.log(se.to_np().astype(np.float64))
+        out[name + "/meta"] = np.array([B, H, Lq, Lk, D, int(causal), seed], np.int64)
+        out[name + "/scale"] = np.float32(scale)
+        out[name + "/out"] = o.to_np()
+        out[name + "/lse"] = lse[..., 0].astype(np.float32)
+        if bwd:
+            g = normal(seed + 300, (B, H, Lq, D))
+            tg = T(g)
+            pn = p.to_np()
+            dv = T(np.ascontiguousarray(np.swapaxes(pn, -1, -2))) @ tg
+            dp = tg @ T(np.ascontiguousarray(np.swapaxes(v, -1, -2)))
+            delta = em.sum(dp * p, axis=-1, keepdims=True)
+            ds = (p * (dp - delta)) * scale
+            dq = ds @ T(k)
+            dk = T(np.ascontiguousarray(np.swapaxes(ds.to_np(), -1, -2))) @ tq
+            out[name + "/dq"], out[name + "/dk"], out[name + "/dv"] = dq.to_np(), dk.to_np(), dv.to_np()
+        print(name, "ok", out[name + "/out"].shape)
+    np.savez_compressed(os.path.join(HERE, "attention_golden.npz"), **out)
+
+
+if __name__ == "__main__":
+    main()
