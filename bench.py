@@ -1,0 +1,559 @@
+#!/usr/bin/env python
+"""Benchmark of the attention hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--no-extra]
+
+Headline workload (N=1): causal prefill forward, bf16 in/out, B=4 H=32 L=4096 D=128, scale
+1/sqrt(128), inputs N(0,1)*0.5 from a seed. One "step" is one forward pass over that batch. With
+N>1 every rank runs the same batch on its own GPU (the (batch*head) axis shards with no collective,
+so this is weak scaling: per-GPU work is fixed) and `value` is the whole-job rate.
+
+Printed JSON (one line, rank 0): metric/value/unit as TFLOP/s of algorithmic work
+(4*B*H*L*L*D/2 flop per step), `roofline` for the forward kernel against the measured dense bf16
+peak, `e2e` (host buffers in pinned memory -> copy_to_device -> kernel -> copy_from_device through
+the C ABI, all inside the timed region), `cpu_baseline` (the reference's own C operators composed
+into attention, timed on the host cores on a bounded sample) and, at N=1, `extra` with the backward
+and split-KV decode results.
+
+`--impl reference` times only the CPU reference arm and prints the same line shape.
+torch is used for device selection, input generation, events and torch.distributed plumbing; the
+attention itself runs in this repo's CUDA library through its C ABI (ctypes).
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import math
+import os
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOAD = dict(name="causal_prefill_fwd_bf16_B4_H32_L4096_D128", B=4, H=32, L=4096, D=128)
+BWD_WORKLOAD = dict(name="causal_fwd_bwd_bf16_B2_H32_L8192_D128", B=2, H=32, L=8192, D=128)
+DECODE_WORKLOAD = dict(name="decode_bf16_B64_H32_Lk32768_D128", B=64, H=32, Lk=32768, D=128)
+NOMINAL_BF16_TFLOPS = 2250.0
+NOMINAL_HBM_GBS = 8000.0
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return dict(hbm_gbs=float(p["hbm_gbs"]), bf16_tflops=float(p["bf16_tflops"]),
+                    bf16_tflops_sustained=float(p.get("bf16_tflops_sustained", p["bf16_tflops"])), source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source="fallback")
+
+
+# ------------------------------------------------------------------------------------------------
+# CPU reference arm
+# ------------------------------------------------------------------------------------------------
+def cpu_reference_sample(rows: int, slices: int, threads: int):
+    """Times the composed reference attention (causal, L=4096, D=128) for the first `rows` query rows
+    of `slices` independent (batch, head) slices, `threads` slices at a time. Returns seconds and
+    which implementation ran ("reference": the reference's compiled C operators; "port": the C
+    restatement)."""
+    from oracle import cpu_oracle, ref_ops
+
+    L, D = WORKLOAD["L"], WORKLOAD["D"]
+    rng = np.random.default_rng(1234)
+    q = (rng.standard_normal((slices, rows, D), dtype=np.float32) * 0.5)
+    k = (rng.standard_normal((slices, L, D), dtype=np.float32) * 0.5)
+    v = (rng.standard_normal((slices, L, D), dtype=np.float32) * 0.5)
+    scale = 1.0 / math.sqrt(D)
+    if ref_ops.available():
+        kind = "reference"
+        # rows [0, rows) of the causal problem: key j visible to row i iff j <= i (top-left rows of
+        # the square mask), expressed the only way the reference can: an additive {0,-inf} mask.
+        i = np.arange(rows)[:, None]
+        j = np.arange(L)[None, :]
+        mask = np.where(j > i, -np.inf, 0.0).astype(np.float32)
+
+        def one(s):
+            p, _, _ = ref_ops._probs(q[s], k[s], scale, mask)
+            ref_ops._mm(p, v[s])
+
+        t0 = time.perf_counter()
+        if threads <= 1:
+            for s in range(slices):
+                one(s)
+        else:
+            ths = []
+            nxt = iter(range(slices))
+            lock = threading.Lock()
+
+            def work():
+                while True:
+                    with lock:
+                        s = next(nxt, None)
+                    if s is None:
+                        return
+                    one(s)
+
+            for _ in range(threads):
+                th = threading.Thread(target=work)
+                th.start()
+                ths.append(th)
+            for th in ths:
+                th.join()
+        return time.perf_counter() - t0, kind
+    kind = "port"
+    cpu_oracle.set_threads(threads)
+    # the port's causal mask is bottom-right aligned; pass the first `rows` keys' worth of offset by
+    # running non-causal over all L keys, which costs the reference path the same (it multiplies the
+    # full rectangle either way).
+    t0 = time.perf_counter()
+    cpu_oracle.attention_fwd(q, k, v, scale, False)
+    dt = time.perf_counter() - t0
+    cpu_oracle.set_threads(1)
+    return dt, kind
+
+
+def cpu_baseline_value(rows: int, threads: int, repeats: int = 1):
+    """TFLOP/s (algorithmic causal flops of the headline workload / extrapolated time) of the CPU
+    reference on `threads` host threads, from a bounded sample."""
+    B, H, L, D = (WORKLOAD[x] for x in "BHLD")
+    slices = threads
+    best = None
+    for _ in range(repeats):
+        dt, kind = cpu_reference_sample(rows, slices, threads)
+        best = dt if best is None else min(best, dt)
+    # The reference multiplies the full (rows x L) rectangle whatever the mask, so its time is
+    # proportional to rows*slices; the whole workload has B*H slices of L rows.
+    full_seconds = best * (L / rows) * (B * H / slices)
+    flops = 4.0 * B * H * L * L * D / 2.0
+    return dict(value=flops / full_seconds / 1e12, unit="TFLOP/s", cores=threads, kind=kind,
+                sample=f"first {rows} query rows of {slices} (batch,head) slices of the headline workload "
+                       f"({best:.2f} s measured, extrapolated x{(L / rows) * (B * H / slices):.0f})"), full_seconds
+
+
+def host_threads():
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except Exception:
+        return os.cpu_count() or 1
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = min(host_threads(), 64)
+    rows = 256
+    times = []
+    kind = "port"
+    for step in range(args.warmup + args.steps):
+        dt, kind = cpu_reference_sample(rows, threads, threads)
+        if step >= args.warmup:
+            times.append(dt)
+    B, H, L, D = (WORKLOAD[x] for x in "BHLD")
+    mean = sum(times) / len(times)
+    factor = (L / rows) * (B * H / threads)
+    full_seconds = mean * factor
+    flops = 4.0 * B * H * L * L * D / 2.0
+    value = flops / full_seconds / 1e12
+    sample = (f"each step: first {rows} query rows of {threads} (batch,head) slices on {threads} host threads "
+              f"({mean:.3f} s/step measured), extrapolated x{factor:.0f} to the full batch")
+    line = {
+        "metric": "attention_causal_prefill_fwd_tflops", "value": value, "unit": "TFLOP/s", "impl": "reference",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": full_seconds * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD["name"], "note": "reference CPU path computes in float32 with double-accumulated matmuls"},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": threads, "kind": kind, "sample": sample},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------
+# GPU arm
+# ------------------------------------------------------------------------------------------------
+class ClockSampler:
+    """Polls NVML for SM clock and clock-event reasons of one GPU while the benchmark runs."""
+
+    def __init__(self, torch_index: int):
+        self.samples = []  # (t, sm_mhz, reasons_bitmask, power_w)
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._th = None
+        try:
+            import pynvml
+
+            self.nv = pynvml
+            pynvml.nvmlInit()
+            import torch
+
+            uuid = str(torch.cuda.get_device_properties(torch_index).uuid)
+            self.h = None
+            for i in range(pynvml.nvmlDeviceGetCount()):
+                h = pynvml.nvmlDeviceGetHandleByIndex(i)
+                u = pynvml.nvmlDeviceGetUUID(h)
+                u = u.decode() if isinstance(u, bytes) else u
+                if uuid in u or u.replace("GPU-", "") == uuid:
+                    self.h = h
+            if self.h is None:
+                self.h = pynvml.nvmlDeviceGetHandleByIndex(torch_index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _loop(self):
+        nv = self.nv
+        while not self._stop.is_set():
+            try:
+                mhz = nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)
+                try:
+                    reasons = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:
+                    reasons = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                try:
+                    power = nv.nvmlDeviceGetPowerUsage(self.h) / 1000.0
+                except Exception:
+                    power = 0.0
+                self.samples.append((time.perf_counter(), mhz, reasons, power))
+            except Exception:
+                pass
+            time.sleep(0.01)
+
+    def start(self):
+        if self.nv is not None:
+            self._th = threading.Thread(target=self._loop, daemon=True)
+            self._th.start()
+
+    def stop(self):
+        self._stop.set()
+        if self._th:
+            self._th.join(timeout=1.0)
+
+    def summary(self, t0: float, t1: float):
+        if self.nv is None or not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "window": "unavailable"}
+        inside = [s for s in self.samples if t0 <= s[0] <= t1]
+        window = "timed_region"
+        if len(inside) < 2:
+            inside = self.samples
+            window = "whole_gpu_phase"
+        nv = self.nv
+        names = {
+            "hw_slowdown": getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8),
+            "hw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
+            "sw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
+            "sw_power_cap": getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4),
+            "hw_power_brake": getattr(nv, "nvmlClocksEventReasonHwPowerBrakeSlowdown", 0x80),
+        }
+        mask = 0
+        for s in inside:
+            mask |= s[2]
+        reasons = [n for n, bit in names.items() if mask & bit]
+        return {"sm_mhz": float(np.median([s[1] for s in inside])), "sm_max_mhz": self.max_mhz, "reasons": reasons,
+                "power_w_max": max(s[3] for s in inside), "samples": len(inside), "window": window}
+
+
+def run_gpu_arm(args):
+    import torch
+    import torch.distributed as dist
+
+    from ember_b200 import _lib
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; there is no CPU fallback for the attention path")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    L = _lib.lib()
+    _lib.check(L.ember_set_device(local_rank))
+    dev = torch.device("cuda", local_rank)
+    # A stream of our own: the handle of torch's default stream is 0, which the C ABI reads as "use
+    # the library's stream", and then the events below would not see the kernels.
+    stream = torch.cuda.Stream(device=dev)
+    torch.cuda.set_stream(stream)
+    assert stream.cuda_stream != 0
+    sptr = ctypes.c_void_p(stream.cuda_stream)
+    peaks = measured_peaks()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    B, H, S, D = (WORKLOAD[x] for x in "BHLD")
+    scale = 1.0 / math.sqrt(D)
+    gen = torch.Generator(device=dev).manual_seed(1000 + rank)
+    q, k, v = ((torch.randn((B, H, S, D), generator=gen, device=dev, dtype=torch.float32) * 0.5).to(torch.bfloat16)
+               for _ in range(3))
+    out = torch.empty_like(q)
+    lse = torch.empty((B, H, S), device=dev, dtype=torch.float32)
+    flops_step = 4.0 * B * H * S * S * D / 2.0
+
+    def fwd():
+        _lib.check(L.ember_attention_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(),
+                                         B * H, S, S, D, scale, 1, _lib.EMBER_BF16, sptr))
+
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    for _ in range(max(args.warmup, 3)):
+        fwd()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_wall0 = time.perf_counter()
+    e0.record(stream)
+    for _ in range(args.steps):
+        fwd()
+    e1.record(stream)
+    barrier()
+    t_wall1 = time.perf_counter()
+    ms_total = max_over_ranks(e0.elapsed_time(e1))
+    ms_step = ms_total / args.steps
+    value = world * flops_step / (ms_step * 1e-3) / 1e12
+    where = ctypes.c_int(0)
+    _lib.check(L.ember_check_device_status(sptr, ctypes.byref(where)))
+
+    # ---- end to end through the C ABI with host buffers (pinned), copies inside the timed region
+    hq, hk, hv = (t.cpu().pin_memory() for t in (q, k, v))
+    ho = torch.empty_like(hq).pin_memory()
+    nbytes = hq.numel() * 2
+    dq_, dk_, dv_, do_ = (ctypes.c_void_p(L.alloc_memory(nbytes)) for _ in range(4))
+    dl_ = ctypes.c_void_p(L.alloc_memory(B * H * S * 4))
+
+    def e2e_step():
+        L.copy_to_device(dq_, hq.data_ptr(), nbytes)
+        L.copy_to_device(dk_, hk.data_ptr(), nbytes)
+        L.copy_to_device(dv_, hv.data_ptr(), nbytes)
+        _lib.check(L.ember_attention_fwd(dq_, dk_, dv_, do_, dl_, B * H, S, S, D, scale, 1, _lib.EMBER_BF16, None))
+        L.copy_from_device(ho.data_ptr(), do_, nbytes)  # waits for the library stream
+
+    e2e_steps = max(3, min(args.steps, 10))
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_step()
+    barrier()
+    e2e_s = max_over_ranks((time.perf_counter() - t0) / e2e_steps)
+    e2e_value = world * flops_step / e2e_s / 1e12
+    e2e_ok = bool(torch.equal(ho.to(dev), out))
+    for p_ in (dq_, dk_, dv_, do_, dl_):
+        L.free_memory(p_)
+    sampler.stop()
+    clocks = sampler.summary(t_wall0, t_wall1)
+
+    line = {
+        "metric": "attention_causal_prefill_fwd_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": WORKLOAD["name"], "per_gpu": True, "causal": True, "scale": scale,
+                   "inputs": "N(0,1)*0.5 seeded per rank, resident in HBM",
+                   "l2": "inputs (403 MB per step) larger than L2 (126 MB); no flush",
+                   "kernel": L.ember_attention_kernel_name(0, S, S, D, 1).decode()},
+        "roofline": {"bound": "tensor", "achieved": flops_step / (ms_step * 1e-3) / 1e12, "peak": peaks["bf16_tflops"],
+                     "unit": "TFLOP/s", "frac": flops_step / (ms_step * 1e-3) / 1e12 / peaks["bf16_tflops"],
+                     "traffic": None, "peak_source": peaks["source"] + " burst cuBLAS bf16",
+                     "frac_of_nominal_2250": flops_step / (ms_step * 1e-3) / 1e12 / NOMINAL_BF16_TFLOPS,
+                     "frac_of_sustained": flops_step / (ms_step * 1e-3) / 1e12 / peaks["bf16_tflops_sustained"]},
+        "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": 3 * nbytes, "d2h_bytes_per_step": nbytes,
+                "ms_per_step": e2e_s * 1e3, "steps": e2e_steps, "result_matches_device_run": e2e_ok},
+        "gpu_launches": args.steps,
+        "clocks": clocks,
+    }
+
+    if rank == 0 and world == 1:
+        cb, _ = cpu_baseline_value(rows=1024, threads=min(host_threads(), 64), repeats=1)
+        line["cpu_baseline"] = cb
+        if not args.no_extra:
+            line["extra"] = run_extras(L, _lib, torch, dev, sptr, stream, peaks)
+    if world > 1:
+        dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+
+
+def run_extras(L, _lib, torch, dev, sptr, stream, peaks):
+    """Backward (causal fwd+bwd workload) and split-KV decode, each with its own roofline entry."""
+    extra = {}
+
+    def timed(fn, steps, warm=3):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        for _ in range(steps):
+            fn()
+        b.record(stream)
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / steps
+
+    # ---- backward
+    B, H, S, D = (BWD_WORKLOAD[x] for x in "BHLD")
+    scale = 1.0 / math.sqrt(D)
+    gen = torch.Generator(device=dev).manual_seed(7)
+    q, k, v = ((torch.randn((B, H, S, D), generator=gen, device=dev) * 0.5).to(torch.bfloat16) for _ in range(3))
+    do = torch.randn((B, H, S, D), generator=gen, device=dev).to(torch.bfloat16)
+    o = torch.empty_like(q)
+    lse = torch.empty((B, H, S), device=dev, dtype=torch.float32)
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(q), torch.empty_like(q)
+    wsn = L.ember_attention_workspace_bytes(_lib.EMBER_OP_BWD, B * H, S, S, D, 1, 0)
+    ws = torch.empty(wsn, device=dev, dtype=torch.uint8)
+
+    def fwd():
+        _lib.check(L.ember_attention_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), B * H,
+                                         S, S, D, scale, 1, 1, sptr))
+
+    def bwd():
+        _lib.check(L.ember_attention_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(),
+                                         do.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), B * H, S, S, D,
+                                         scale, 1, 1, ws.data_ptr(), wsn, sptr))
+
+    fwd_flops = 4.0 * B * H * S * S * D / 2.0
+    kern = L.ember_attention_kernel_name(_lib.EMBER_OP_BWD, S, S, D, 1).decode()
+    ms_f = timed(fwd, 10)
+    ms_b = timed(bwd, 10 if kern == "sm100_tcgen05" else 2, warm=1)
+    extra["fwd_L8192"] = {"workload": BWD_WORKLOAD["name"], "ms": ms_f, "tflops": fwd_flops / ms_f / 1e9,
+                          "frac_of_measured_peak": fwd_flops / ms_f / 1e9 / peaks["bf16_tflops"]}
+    extra["bwd_L8192"] = {"workload": BWD_WORKLOAD["name"], "kernel": kern, "ms": ms_b,
+                          "tflops": 2.5 * fwd_flops / ms_b / 1e9,
+                          "frac_of_measured_peak": 2.5 * fwd_flops / ms_b / 1e9 / peaks["bf16_tflops"]}
+    del q, k, v, do, o, dq, dk, dv, ws
+
+    # ---- decode
+    B, H, Lk, D = (DECODE_WORKLOAD[x] for x in ("B", "H", "Lk", "D"))
+    scale = 1.0 / math.sqrt(D)
+    kc = torch.empty((B, H, Lk, D), device=dev, dtype=torch.bfloat16)
+    vc = torch.empty((B, H, Lk, D), device=dev, dtype=torch.bfloat16)
+    for t in (kc, vc):  # fill in slabs to bound temporary memory
+        for b in range(B):
+            t[b] = (torch.randn((H, Lk, D), generator=gen, device=dev) * 0.5).to(torch.bfloat16)
+    qd = (torch.randn((B, H, 1, D), generator=gen, device=dev) * 0.5).to(torch.bfloat16)
+    od = torch.empty_like(qd)
+    ld = torch.empty((B, H), device=dev, dtype=torch.float32)
+    splits = L.ember_attention_decode_splits(B * H, Lk, D, 1)
+    wsn = L.ember_attention_workspace_bytes(_lib.EMBER_OP_DECODE, B * H, 1, Lk, D, 1, 0)
+    ws = torch.empty(max(wsn, 256), device=dev, dtype=torch.uint8)
+
+    def dec():
+        _lib.check(L.ember_attention_decode(qd.data_ptr(), kc.data_ptr(), vc.data_ptr(), od.data_ptr(), ld.data_ptr(),
+                                            B * H, Lk, D, scale, 1, 0, ws.data_ptr(), wsn, sptr))
+
+    ms_d = timed(dec, 10)
+    nbytes = 2.0 * B * H * Lk * D * 2
+    extra["decode"] = {"workload": DECODE_WORKLOAD["name"], "splits": splits, "ms": ms_d, "gbs": nbytes / ms_d / 1e6,
+                       "roofline": {"bound": "hbm", "achieved": nbytes / ms_d / 1e6, "peak": peaks["hbm_gbs"],
+                                    "unit": "GB/s", "frac": nbytes / ms_d / 1e6 / peaks["hbm_gbs"],
+                                    "frac_of_nominal_8000": nbytes / ms_d / 1e6 / NOMINAL_HBM_GBS,
+                                    "peak_source": peaks["source"] + " copy"}}
+    return extra
+
+
+def run_profile_case(args):
+    """A small single-kernel case for ncu captures (never a benchmark value): inputs larger than L2,
+    a few hundred MB to a few GB on the device, `steps` launches after `warmup`."""
+    import torch
+
+    from ember_b200 import _lib
+
+    torch.cuda.set_device(0)
+    L = _lib.lib()
+    _lib.check(L.ember_set_device(0))
+    dev = torch.device("cuda", 0)
+    stream = torch.cuda.Stream(device=dev)
+    torch.cuda.set_stream(stream)
+    sptr = ctypes.c_void_p(stream.cuda_stream)
+    gen = torch.Generator(device=dev).manual_seed(3)
+    D = 128
+    scale = 1.0 / math.sqrt(D)
+    if args.profile in ("fwd", "bwd"):
+        B, H, S = 2, 32, 4096
+        q, k, v, do = ((torch.randn((B, H, S, D), generator=gen, device=dev) * 0.5).to(torch.bfloat16) for _ in range(4))
+        o, dq, dk, dv = (torch.empty_like(q) for _ in range(4))
+        lse = torch.empty((B, H, S), device=dev, dtype=torch.float32)
+        wsn = L.ember_attention_workspace_bytes(_lib.EMBER_OP_BWD, B * H, S, S, D, 1, 0)
+        ws = torch.empty(wsn, device=dev, dtype=torch.uint8)
+
+        def fwd():
+            _lib.check(L.ember_attention_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(),
+                                             B * H, S, S, D, scale, 1, 1, sptr))
+
+        def bwd():
+            _lib.check(L.ember_attention_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(),
+                                             do.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), B * H, S, S,
+                                             D, scale, 1, 1, ws.data_ptr(), wsn, sptr))
+
+        fwd()
+        fn = fwd if args.profile == "fwd" else bwd
+        work = 4.0 * B * H * S * S * D / 2.0 * (1.0 if args.profile == "fwd" else 2.5)
+        unit, name = "TFLOP/s", f"causal_{args.profile}_bf16_B{B}_H{H}_L{S}_D{D}"
+    else:
+        B, H, Lk = 8, 32, 32768
+        kc = (torch.randn((B, H, Lk, D), generator=gen, device=dev) * 0.5).to(torch.bfloat16)
+        vc = (torch.randn((B, H, Lk, D), generator=gen, device=dev) * 0.5).to(torch.bfloat16)
+        qd = (torch.randn((B, H, 1, D), generator=gen, device=dev) * 0.5).to(torch.bfloat16)
+        od = torch.empty_like(qd)
+        ld = torch.empty((B, H), device=dev, dtype=torch.float32)
+        wsn = L.ember_attention_workspace_bytes(_lib.EMBER_OP_DECODE, B * H, 1, Lk, D, 1, 0)
+        ws = torch.empty(max(wsn, 256), device=dev, dtype=torch.uint8)
+
+        def fn():
+            _lib.check(L.ember_attention_decode(qd.data_ptr(), kc.data_ptr(), vc.data_ptr(), od.data_ptr(),
+                                                ld.data_ptr(), B * H, Lk, D, scale, 1, 0, ws.data_ptr(), wsn, sptr))
+
+        work = 2.0 * B * H * Lk * D * 2
+        unit, name = "GB/s", f"decode_bf16_B{B}_H{H}_Lk{Lk}_D{D}"
+    for _ in range(args.warmup):
+        fn()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record(stream)
+    for _ in range(args.steps):
+        fn()
+    b.record(stream)
+    torch.cuda.synchronize()
+    ms = a.elapsed_time(b) / args.steps
+    rate = work / ms / (1e9 if unit == "TFLOP/s" else 1e6)
+    print(json.dumps({"profile_case": name, "ms_per_launch": ms, "rate": rate, "unit": unit,
+                      "note": "small case for profiler captures; not a benchmark value"}), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-extra", action="store_true", help="skip the backward and decode extras at N=1")
+    ap.add_argument("--profile", choices=["fwd", "bwd", "decode"], default=None,
+                    help="run only a small single-kernel case (for ncu captures) and exit")
+    args = ap.parse_args()
+    if args.profile:
+        if args.steps == 200 and args.warmup == 10:
+            args.steps, args.warmup = 3, 2
+        run_profile_case(args)
+        return
+    if args.impl == "reference":
+        if args.steps == 200 and args.warmup == 10:  # defaults are sized for the GPU arm
+            args.steps, args.warmup = 5, 1
+        run_reference_arm(args)
+    else:
+        run_gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()
