@@ -1,12 +1,528 @@
-// Placeholder translation unit: the tcgen05 backward is not built yet; the dispatcher falls back
-// to the CUDA-core backward for every shape.
+// Attention backward for sm_100a: bf16 in/out, float32 recompute of P from the saved log-sum-exp,
+// float32 accumulation in tensor memory. Two kernels plus the delta preprocess:
+//
+//   delta[row] = sum_c dO[row][c] * O[row][c]                      (CUDA cores, attn_simt.cu)
+//
+//   dK/dV kernel: one CTA per (batch*head, 128-key tile), looping over the 128-row query tiles that
+//     can see those keys. Scores are formed TRANSPOSED so that keys sit on the TMEM lanes:
+//       S^T  = K Q^T          dP^T = V dO^T                       (smem x smem -> TMEM)
+//       P^T  = exp2(S^T*c - lse*log2e)     dS^T = P^T * (dP^T - delta)   (registers, bf16 -> TMEM)
+//       dV  += P^T dO         dK  += dS^T Q                       (TMEM x smem -> TMEM)
+//     TMEM: S^T 128 + dP^T 128 + dV HD + dK HD columns -- full at HD = 128, so no dQ accumulator
+//     fits next to them; dQ gets its own pass:
+//
+//   dQ kernel: one CTA per (batch*head, 128-row query tile), looping over the key tiles it sees:
+//       S = Q K^T   dP = dO V^T   dS = P * (dP - delta)   dQ += dS K
+//
+// Both results are deterministic (no atomics). The scale factor of dS is applied once, to the
+// accumulated dK / dQ, in the epilogue.
+//
+//   warps 0-7   compute: thread (row r, half h) owns TMEM lane r and 64 of the 128 score columns
+//   warp  8     MMA issue (one lane)      warp 9   TMA producer (one lane)      warp 10  TMEM alloc
+#include <math.h>
+
+#include "common.cuh"
 #include "kernels.cuh"
+#include "ptx.cuh"
 
 namespace ember {
-bool sm100_bwd_supported(const AttnArgs &) { return false; }
-int sm100_attention_bwd(const AttnArgs &, float *, DeviceState *, cudaStream_t)
+
+namespace {
+
+using namespace ptx;
+
+constexpr int BWD_THREADS = 384;
+constexpr float LOG2E_B = 1.4426950408889634f;
+
+template <int HD>
+struct BwdCfg {
+    static constexpr int NSUB = HD / 64;
+    static constexpr int SUB_BYTES = 128 * 128;
+    static constexpr int TILE_BYTES = NSUB * SUB_BYTES;
+    static constexpr int STAGES = 2;
+    static constexpr int OFF_RES0 = 0;                  // resident tile 0 (K, or Q)
+    static constexpr int OFF_RES1 = TILE_BYTES;         // resident tile 1 (V, or dO)
+    static constexpr int OFF_STAGE = 2 * TILE_BYTES;    // each stage: two tiles back to back
+    static constexpr int STAGE_BYTES = 2 * TILE_BYTES;
+    static constexpr int OFF_BAR = OFF_STAGE + STAGES * STAGE_BYTES;
+    static constexpr int OFF_ROWVEC = OFF_BAR + 256;    // [2 buffers][2 vectors][128] floats
+    static constexpr int SMEM_BYTES = OFF_ROWVEC + 2048 + 1024;
+    static constexpr int T_S = 0, T_DP = 128, T_ACC0 = 256, T_ACC1 = 256 + HD;
+    // barrier indices
+    static constexpr int B_RES = 0, B_FULL = 1, B_EMPTY = B_FULL + STAGES, B_SDP = B_EMPTY + STAGES,
+                         B_PDS = B_SDP + 1, B_ACC = B_PDS + 1, NUM_BARS = B_ACC + 1;
+};
+
+enum { WB_RES = 101, WB_FULL, WB_EMPTY, WB_SDP, WB_PDS, WB_ACC };
+
+struct BwdParams {
+    __nv_bfloat16 *dq, *dk, *dv;
+    const float *lse, *delta;
+    int lq, lk, causal;
+    float scale, scale_log2;
+    DeviceStatus *status;
+};
+
+__device__ __forceinline__ void named_bar_sync(int id, int count)
 {
-    set_error("tcgen05 backward is not available");
-    return EMBER_ERR_UNSUPPORTED;
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
 }
+
+// Common prologue: barriers, TMEM allocation, tensor-map prefetch. Returns the TMEM base.
+template <typename C>
+__device__ __forceinline__ uint32_t bwd_setup(uint32_t smem_base, uint8_t *smem_gen, int warp, int lane,
+                                              const CUtensorMap *m0, const CUtensorMap *m1,
+                                              const CUtensorMap *m2, const CUtensorMap *m3)
+{
+    const uint32_t bar0 = smem_base + C::OFF_BAR;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem_gen + C::OFF_BAR + 8 * C::NUM_BARS);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        mbar_init(bar0 + 8 * C::B_RES, 1);
+        for (int s = 0; s < C::STAGES; s++) {
+            mbar_init(bar0 + 8 * (C::B_FULL + s), 1);
+            mbar_init(bar0 + 8 * (C::B_EMPTY + s), 1);
+        }
+        mbar_init(bar0 + 8 * C::B_SDP, 1);
+        mbar_init(bar0 + 8 * C::B_PDS, 256);
+        mbar_init(bar0 + 8 * C::B_ACC, 1);
+        fence_mbar_init();
+    }
+    if (warp == 10) {
+        tmem_alloc(smem_u32(tmem_slot), 512);
+        tmem_relinquish();
+    }
+    if (warp == 9 && lane == 0) {
+        prefetch_tensormap(m0);
+        prefetch_tensormap(m1);
+        prefetch_tensormap(m2);
+        prefetch_tensormap(m3);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    return *tmem_slot;
+}
+
+// Bounded drain of the producer's outstanding copies before the CTA may exit.
+template <typename C>
+__device__ __forceinline__ void drain_copies(uint32_t bar0, int issued)
+{
+    const long long t0 = clock64();
+    for (int j = max(0, issued - C::STAGES); j < issued; j++)
+        while (!mbar_try_wait(bar0 + 8 * (C::B_FULL + j % C::STAGES), (j / C::STAGES) & 1) &&
+               clock64() - t0 < kWaitLimitCycles) {}
+    while (!mbar_try_wait(bar0 + 8 * C::B_RES, 0) && clock64() - t0 < kWaitLimitCycles) {}
+}
+
+// acc (TMEM, fp32, 128 x HD) -> bf16 rows in global memory, times `mul`; thread (r, h) stores
+// columns [h*HD/2, (h+1)*HD/2) of row r when `store` is set.
+template <int HD>
+__device__ __forceinline__ void store_acc(uint32_t tacc, __nv_bfloat16 *grow, int h, float mul, bool store)
+{
+#pragma unroll
+    for (int ch = 0; ch < HD / 64; ch++) {
+        const int col = h * (HD / 2) + ch * 32;
+        uint32_t o[32];
+        tmem_ld_32x32b_x32(tacc + col, o);
+        tmem_wait_ld();
+        if (store) {
+#pragma unroll
+            for (int v4 = 0; v4 < 4; v4++) {
+                uint4 w;
+                w.x = pack_bf16(__uint_as_float(o[v4 * 8 + 0]) * mul, __uint_as_float(o[v4 * 8 + 1]) * mul);
+                w.y = pack_bf16(__uint_as_float(o[v4 * 8 + 2]) * mul, __uint_as_float(o[v4 * 8 + 3]) * mul);
+                w.z = pack_bf16(__uint_as_float(o[v4 * 8 + 4]) * mul, __uint_as_float(o[v4 * 8 + 5]) * mul);
+                w.w = pack_bf16(__uint_as_float(o[v4 * 8 + 6]) * mul, __uint_as_float(o[v4 * 8 + 7]) * mul);
+                *reinterpret_cast<uint4 *>(grow + col + v4 * 8) = w;
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// dK / dV
+// ------------------------------------------------------------------------------------------------
+template <int HD>
+__global__ void __launch_bounds__(BWD_THREADS, 1)
+    sm100_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                          const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
+                          const BwdParams p)
+{
+    using C = BwdCfg<HD>;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t bar0 = smem_base + C::OFF_BAR;
+    auto BAR = [&](int i) { return bar0 + 8u * (uint32_t)i; };
+    volatile int *abort_flag =
+        reinterpret_cast<volatile int *>(smem_gen + C::OFF_BAR + 8 * C::NUM_BARS + 4);
+    float *rowvec = reinterpret_cast<float *>(smem_gen + C::OFF_ROWVEC);
+
+    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const int bh = blockIdx.x;
+    const int k0 = blockIdx.y * 128;
+    const int off = p.lk - p.lq;
+    const int i_begin = p.causal ? max(0, k0 - off) / 128 : 0;  // first query tile that sees key k0
+    const int n = (p.lq + 127) / 128 - i_begin;
+
+    const uint32_t tmem = bwd_setup<C>(smem_base, smem_gen, warp, lane, &tm_q, &tm_k, &tm_v, &tm_do);
+
+    if (warp >= 8) {
+        reg_dealloc_40();
+        if (warp == 9 && lane == 0) {
+            // ---------------------------------------------------------------- TMA producer
+            mbar_arrive_expect_tx(BAR(C::B_RES), 2 * C::TILE_BYTES);
+            for (int s = 0; s < C::NSUB; s++) {
+                tma_load_3d(smem_base + C::OFF_RES0 + s * C::SUB_BYTES, &tm_k, BAR(C::B_RES), s * 64, k0, bh);
+                tma_load_3d(smem_base + C::OFF_RES1 + s * C::SUB_BYTES, &tm_v, BAR(C::B_RES), s * 64, k0, bh);
+            }
+            int issued = 0;
+            for (int i = 0; i < n; i++) {
+                const int st = i % C::STAGES;
+                const uint32_t ph = (i / C::STAGES) & 1;
+                if (!mbar_wait(BAR(C::B_EMPTY + st), ph ^ 1, abort_flag, p.status, WB_EMPTY)) break;
+                mbar_arrive_expect_tx(BAR(C::B_FULL + st), 2 * C::TILE_BYTES);
+                const uint32_t dst = smem_base + C::OFF_STAGE + st * C::STAGE_BYTES;
+                const int q0 = (i_begin + i) * 128;
+                for (int s = 0; s < C::NSUB; s++) {
+                    tma_load_3d(dst + s * C::SUB_BYTES, &tm_q, BAR(C::B_FULL + st), s * 64, q0, bh);
+                    tma_load_3d(dst + C::TILE_BYTES + s * C::SUB_BYTES, &tm_do, BAR(C::B_FULL + st), s * 64, q0, bh);
+                }
+                issued = i + 1;
+            }
+            drain_copies<C>(bar0, issued);
+        } else if (warp == 8 && lane == 0) {
+            // ---------------------------------------------------------------- MMA issue
+            constexpr uint32_t IDESC_SS = idesc_bf16_f32(128, 128, 0, 0);
+            constexpr uint32_t IDESC_TS = idesc_bf16_f32(128, HD, 0, 1);
+            const uint32_t ka = smem_base + C::OFF_RES0, va = smem_base + C::OFF_RES1;
+            bool ok = mbar_wait(BAR(C::B_RES), 0, abort_flag, p.status, WB_RES);
+            for (int i = 0; i < n && ok; i++) {
+                const int st = i % C::STAGES;
+                const uint32_t ph = (i / C::STAGES) & 1;
+                const uint32_t qa = smem_base + C::OFF_STAGE + st * C::STAGE_BYTES;
+                const uint32_t doa = qa + C::TILE_BYTES;
+                ok = ok && mbar_wait(BAR(C::B_FULL + st), ph, abort_flag, p.status, WB_FULL);
+                tc_fence_after();
+#pragma unroll
+                for (int ks = 0; ks < HD / 16; ks++) {  // S^T = K Q^T
+                    const uint32_t o = (ks / 4) * C::SUB_BYTES + (ks % 4) * 32;
+                    mma_ss(tmem + C::T_S, smem_desc_sw128(ka + o, 16, 1024), smem_desc_sw128(qa + o, 16, 1024),
+                           IDESC_SS, ks > 0);
+                }
+#pragma unroll
+                for (int ks = 0; ks < HD / 16; ks++) {  // dP^T = V dO^T
+                    const uint32_t o = (ks / 4) * C::SUB_BYTES + (ks % 4) * 32;
+                    mma_ss(tmem + C::T_DP, smem_desc_sw128(va + o, 16, 1024), smem_desc_sw128(doa + o, 16, 1024),
+                           IDESC_SS, ks > 0);
+                }
+                tc_commit(BAR(C::B_SDP));
+                ok = ok && mbar_wait(BAR(C::B_PDS), i & 1, abort_flag, p.status, WB_PDS);
+                tc_fence_after();
+#pragma unroll
+                for (int ks = 0; ks < 8; ks++)  // dV += P^T dO
+                    mma_ts(tmem + C::T_ACC0, tmem + C::T_S + ks * 8,
+                           smem_desc_sw128(doa + ks * 2048, C::SUB_BYTES, 1024), IDESC_TS, (i > 0 || ks > 0) ? 1u : 0u);
+#pragma unroll
+                for (int ks = 0; ks < 8; ks++)  // dK += dS^T Q
+                    mma_ts(tmem + C::T_ACC1, tmem + C::T_DP + ks * 8,
+                           smem_desc_sw128(qa + ks * 2048, C::SUB_BYTES, 1024), IDESC_TS, (i > 0 || ks > 0) ? 1u : 0u);
+                tc_commit(BAR(C::B_EMPTY + st));
+            }
+            tc_commit(BAR(C::B_ACC));
+        }
+    } else {
+        // -------------------------------------------------------------------- compute
+        reg_alloc_232();
+        const int h = warp / 4;                // which half of the 128 score columns
+        const int r = threadIdx.x % 128;       // TMEM lane == key row inside the tile
+        const int key = k0 + r;
+        const uint32_t lane_sel = (uint32_t)((warp % 4) * 32) << 16;
+        const uint32_t t_s = tmem + lane_sel + C::T_S, t_dp = tmem + lane_sel + C::T_DP;
+        const float c = p.scale_log2;
+        const float *lse_g = p.lse + (size_t)bh * p.lq;
+        const float *delta_g = p.delta + (size_t)bh * p.lq;
+        bool ok = true;
+        for (int i = 0; i < n; i++) {
+            const int q0 = (i_begin + i) * 128;
+            float *rv = rowvec + (i & 1) * 256;
+            {
+                const int qrow = q0 + (threadIdx.x & 127);
+                if (threadIdx.x < 128)
+                    rv[threadIdx.x] = qrow < p.lq ? lse_g[qrow] * LOG2E_B : INFINITY;
+                else
+                    rv[threadIdx.x] = qrow < p.lq ? delta_g[qrow] : 0.f;
+            }
+            ok = ok && mbar_wait(BAR(C::B_SDP), i & 1, abort_flag, p.status, WB_SDP);
+            tc_fence_after();
+            float s[64], dp[64];
+#pragma unroll
+            for (int ch = 0; ch < 2; ch++) {
+                uint32_t u[32], w[32];
+                tmem_ld_32x32b_x32(t_s + h * 64 + ch * 32, u);
+                tmem_ld_32x32b_x32(t_dp + h * 64 + ch * 32, w);
+#pragma unroll
+                for (int x = 0; x < 32; x++) {
+                    s[ch * 32 + x] = __uint_as_float(u[x]);
+                    dp[ch * 32 + x] = __uint_as_float(w[x]);
+                }
+            }
+            tmem_wait_ld();
+            // Every thread has read its scores (the bf16 results overwrite columns another thread of
+            // the same lane still needs) and the lse/delta vectors are visible.
+            named_bar_sync(1, 256);
+            const bool need_mask = p.causal && (k0 + 127 > q0 + off);
+#pragma unroll
+            for (int ch = 0; ch < 4; ch++) {
+                uint32_t pk[8], dk_[8];
+#pragma unroll
+                for (int x = 0; x < 8; x++) {
+                    float pv[2], dv_[2];
+#pragma unroll
+                    for (int e = 0; e < 2; e++) {
+                        const int cc = ch * 16 + 2 * x + e;
+                        const int qq = h * 64 + cc;
+                        float pe = ex2(fmaf(s[cc], c, -rv[qq]));
+                        if (need_mask && key > q0 + qq + off) pe = 0.f;
+                        pv[e] = pe;
+                        dv_[e] = pe * (dp[cc] - rv[128 + qq]);
+                    }
+                    pk[x] = pack_bf16(pv[0], pv[1]);
+                    dk_[x] = pack_bf16(dv_[0], dv_[1]);
+                }
+                // 16 score columns -> 8 packed columns
+                asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(
+                                 t_s + h * 32 + ch * 8),
+                             "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3]), "r"(pk[4]), "r"(pk[5]), "r"(pk[6]), "r"(pk[7])
+                             : "memory");
+                asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(
+                                 t_dp + h * 32 + ch * 8),
+                             "r"(dk_[0]), "r"(dk_[1]), "r"(dk_[2]), "r"(dk_[3]), "r"(dk_[4]), "r"(dk_[5]), "r"(dk_[6]),
+                             "r"(dk_[7])
+                             : "memory");
+            }
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(BAR(C::B_PDS));
+        }
+        ok = ok && mbar_wait(BAR(C::B_ACC), 0, abort_flag, p.status, WB_ACC);
+        tc_fence_after();
+        const bool store = ok && key < p.lk;
+        const size_t grow = ((size_t)bh * p.lk + key) * HD;
+        store_acc<HD>(tmem + lane_sel + C::T_ACC0, p.dv + grow, h, 1.f, store);
+        store_acc<HD>(tmem + lane_sel + C::T_ACC1, p.dk + grow, h, p.scale, store);
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 10) tmem_dealloc(tmem, 512);
+}
+
+// ------------------------------------------------------------------------------------------------
+// dQ
+// ------------------------------------------------------------------------------------------------
+template <int HD>
+__global__ void __launch_bounds__(BWD_THREADS, 1)
+    sm100_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                        const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
+                        const BwdParams p)
+{
+    using C = BwdCfg<HD>;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t bar0 = smem_base + C::OFF_BAR;
+    auto BAR = [&](int i) { return bar0 + 8u * (uint32_t)i; };
+    volatile int *abort_flag =
+        reinterpret_cast<volatile int *>(smem_gen + C::OFF_BAR + 8 * C::NUM_BARS + 4);
+
+    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const int bh = blockIdx.x;
+    const int qtile = gridDim.y - 1 - blockIdx.y;  // heaviest causal tiles first
+    const int q0 = qtile * 128;
+    const int off = p.lk - p.lq;
+    const int visible = p.causal ? min(p.lk, q0 + 128 + off) : p.lk;
+    const int n = (visible + 127) / 128;
+
+    const uint32_t tmem = bwd_setup<C>(smem_base, smem_gen, warp, lane, &tm_q, &tm_k, &tm_v, &tm_do);
+
+    if (warp >= 8) {
+        reg_dealloc_40();
+        if (warp == 9 && lane == 0) {
+            mbar_arrive_expect_tx(BAR(C::B_RES), 2 * C::TILE_BYTES);
+            for (int s = 0; s < C::NSUB; s++) {
+                tma_load_3d(smem_base + C::OFF_RES0 + s * C::SUB_BYTES, &tm_q, BAR(C::B_RES), s * 64, q0, bh);
+                tma_load_3d(smem_base + C::OFF_RES1 + s * C::SUB_BYTES, &tm_do, BAR(C::B_RES), s * 64, q0, bh);
+            }
+            int issued = 0;
+            for (int j = 0; j < n; j++) {
+                const int st = j % C::STAGES;
+                const uint32_t ph = (j / C::STAGES) & 1;
+                if (!mbar_wait(BAR(C::B_EMPTY + st), ph ^ 1, abort_flag, p.status, WB_EMPTY)) break;
+                mbar_arrive_expect_tx(BAR(C::B_FULL + st), 2 * C::TILE_BYTES);
+                const uint32_t dst = smem_base + C::OFF_STAGE + st * C::STAGE_BYTES;
+                for (int s = 0; s < C::NSUB; s++) {
+                    tma_load_3d(dst + s * C::SUB_BYTES, &tm_k, BAR(C::B_FULL + st), s * 64, j * 128, bh);
+                    tma_load_3d(dst + C::TILE_BYTES + s * C::SUB_BYTES, &tm_v, BAR(C::B_FULL + st), s * 64, j * 128, bh);
+                }
+                issued = j + 1;
+            }
+            drain_copies<C>(bar0, issued);
+        } else if (warp == 8 && lane == 0) {
+            constexpr uint32_t IDESC_SS = idesc_bf16_f32(128, 128, 0, 0);
+            constexpr uint32_t IDESC_TS = idesc_bf16_f32(128, HD, 0, 1);
+            const uint32_t qa = smem_base + C::OFF_RES0, doa = smem_base + C::OFF_RES1;
+            bool ok = mbar_wait(BAR(C::B_RES), 0, abort_flag, p.status, WB_RES);
+            for (int j = 0; j < n && ok; j++) {
+                const int st = j % C::STAGES;
+                const uint32_t ph = (j / C::STAGES) & 1;
+                const uint32_t ka = smem_base + C::OFF_STAGE + st * C::STAGE_BYTES;
+                const uint32_t va = ka + C::TILE_BYTES;
+                ok = ok && mbar_wait(BAR(C::B_FULL + st), ph, abort_flag, p.status, WB_FULL);
+                tc_fence_after();
+#pragma unroll
+                for (int ks = 0; ks < HD / 16; ks++) {  // S = Q K^T
+                    const uint32_t o = (ks / 4) * C::SUB_BYTES + (ks % 4) * 32;
+                    mma_ss(tmem + C::T_S, smem_desc_sw128(qa + o, 16, 1024), smem_desc_sw128(ka + o, 16, 1024),
+                           IDESC_SS, ks > 0);
+                }
+#pragma unroll
+                for (int ks = 0; ks < HD / 16; ks++) {  // dP = dO V^T
+                    const uint32_t o = (ks / 4) * C::SUB_BYTES + (ks % 4) * 32;
+                    mma_ss(tmem + C::T_DP, smem_desc_sw128(doa + o, 16, 1024), smem_desc_sw128(va + o, 16, 1024),
+                           IDESC_SS, ks > 0);
+                }
+                tc_commit(BAR(C::B_SDP));
+                ok = ok && mbar_wait(BAR(C::B_PDS), j & 1, abort_flag, p.status, WB_PDS);
+                tc_fence_after();
+#pragma unroll
+                for (int ks = 0; ks < 8; ks++)  // dQ += dS K
+                    mma_ts(tmem + C::T_ACC0, tmem + C::T_DP + ks * 8,
+                           smem_desc_sw128(ka + ks * 2048, C::SUB_BYTES, 1024), IDESC_TS, (j > 0 || ks > 0) ? 1u : 0u);
+                tc_commit(BAR(C::B_EMPTY + st));
+            }
+            tc_commit(BAR(C::B_ACC));
+        }
+    } else {
+        reg_alloc_232();
+        const int h = warp / 4;
+        const int r = threadIdx.x % 128;
+        const int row = q0 + r;
+        const uint32_t lane_sel = (uint32_t)((warp % 4) * 32) << 16;
+        const uint32_t t_s = tmem + lane_sel + C::T_S, t_dp = tmem + lane_sel + C::T_DP;
+        const float c = p.scale_log2;
+        const bool row_ok = row < p.lq;
+        const float lse2 = row_ok ? p.lse[(size_t)bh * p.lq + row] * LOG2E_B : INFINITY;
+        const float dl = row_ok ? p.delta[(size_t)bh * p.lq + row] : 0.f;
+        const int limit_row = p.causal ? min(p.lk - 1, row + off) : p.lk - 1;
+        const int limit_tile = p.causal ? min(p.lk - 1, q0 + off) : p.lk - 1;
+        bool ok = true;
+        for (int j = 0; j < n; j++) {
+            ok = ok && mbar_wait(BAR(C::B_SDP), j & 1, abort_flag, p.status, WB_SDP);
+            tc_fence_after();
+            float s[64], dp[64];
+#pragma unroll
+            for (int ch = 0; ch < 2; ch++) {
+                uint32_t u[32], w[32];
+                tmem_ld_32x32b_x32(t_s + h * 64 + ch * 32, u);
+                tmem_ld_32x32b_x32(t_dp + h * 64 + ch * 32, w);
+#pragma unroll
+                for (int x = 0; x < 32; x++) {
+                    s[ch * 32 + x] = __uint_as_float(u[x]);
+                    dp[ch * 32 + x] = __uint_as_float(w[x]);
+                }
+            }
+            tmem_wait_ld();
+            named_bar_sync(1, 256);  // all dP columns are read before any thread overwrites them with dS
+            const bool need_mask = j * 128 + 127 > limit_tile;
+            const int kbase = j * 128 + h * 64;
+#pragma unroll
+            for (int ch = 0; ch < 4; ch++) {
+                uint32_t dk_[8];
+#pragma unroll
+                for (int x = 0; x < 8; x++) {
+                    float dv_[2];
+#pragma unroll
+                    for (int e = 0; e < 2; e++) {
+                        const int cc = ch * 16 + 2 * x + e;
+                        float pe = ex2(fmaf(s[cc], c, -lse2));
+                        if (need_mask && kbase + cc > limit_row) pe = 0.f;
+                        dv_[e] = pe * (dp[cc] - dl);
+                    }
+                    dk_[x] = pack_bf16(dv_[0], dv_[1]);
+                }
+                asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(
+                                 t_dp + h * 32 + ch * 8),
+                             "r"(dk_[0]), "r"(dk_[1]), "r"(dk_[2]), "r"(dk_[3]), "r"(dk_[4]), "r"(dk_[5]), "r"(dk_[6]),
+                             "r"(dk_[7])
+                             : "memory");
+            }
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(BAR(C::B_PDS));
+        }
+        ok = ok && mbar_wait(BAR(C::B_ACC), 0, abort_flag, p.status, WB_ACC);
+        tc_fence_after();
+        store_acc<HD>(tmem + lane_sel + C::T_ACC0, p.dq + ((size_t)bh * p.lq + row) * HD, h, p.scale, ok && row_ok);
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 10) tmem_dealloc(tmem, 512);
+}
+
+template <int HD>
+int launch(const AttnArgs &a, float *delta, DeviceState *st, cudaStream_t s)
+{
+    using C = BwdCfg<HD>;
+    int rc = launch_delta(a, delta, s);
+    if (rc) return rc;
+    CUtensorMap tq, tk, tv, tdo;
+    if ((rc = make_tensor_map_bf16_3d(&tq, a.q, HD, a.lq, a.bh, 64, 128)) != EMBER_OK) return rc;
+    if ((rc = make_tensor_map_bf16_3d(&tk, a.k, HD, a.lk, a.bh, 64, 128)) != EMBER_OK) return rc;
+    if ((rc = make_tensor_map_bf16_3d(&tv, a.v, HD, a.lk, a.bh, 64, 128)) != EMBER_OK) return rc;
+    if ((rc = make_tensor_map_bf16_3d(&tdo, a.dout, HD, a.lq, a.bh, 64, 128)) != EMBER_OK) return rc;
+    BwdParams p;
+    p.dq = (__nv_bfloat16 *)a.dq;
+    p.dk = (__nv_bfloat16 *)a.dk;
+    p.dv = (__nv_bfloat16 *)a.dv;
+    p.lse = a.lse;
+    p.delta = delta;
+    p.lq = a.lq;
+    p.lk = a.lk;
+    p.causal = a.causal;
+    p.scale = a.scale;
+    p.scale_log2 = a.scale * LOG2E_B;
+    p.status = st->status;
+    auto k1 = sm100_bwd_dkdv_kernel<HD>;
+    auto k2 = sm100_bwd_dq_kernel<HD>;
+    EMBER_CUDA_TRY(cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+    EMBER_CUDA_TRY(cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+    k1<<<dim3(a.bh, (a.lk + 127) / 128), BWD_THREADS, C::SMEM_BYTES, s>>>(tq, tk, tv, tdo, p);
+    EMBER_CUDA_TRY(cudaGetLastError());
+    k2<<<dim3(a.bh, (a.lq + 127) / 128), BWD_THREADS, C::SMEM_BYTES, s>>>(tq, tk, tv, tdo, p);
+    EMBER_CUDA_TRY(cudaGetLastError());
+    return EMBER_OK;
+}
+
+}  // namespace
+
+bool sm100_bwd_supported(const AttnArgs &a)
+{
+    if (a.dtype != EMBER_BF16) return false;
+    if (a.d != 64 && a.d != 128) return false;
+    if (!isfinite(a.scale)) return false;
+    if ((a.lq + 127) / 128 > 65535 || (a.lk + 127) / 128 > 65535) return false;
+    const uintptr_t bits = (uintptr_t)a.q | (uintptr_t)a.k | (uintptr_t)a.v | (uintptr_t)a.dout |
+                           (uintptr_t)a.dq | (uintptr_t)a.dk | (uintptr_t)a.dv;
+    return (bits & 15) == 0;
+}
+
+int sm100_attention_bwd(const AttnArgs &a, float *delta, DeviceState *st, cudaStream_t s)
+{
+    return a.d == 128 ? launch<128>(a, delta, st, s) : launch<64>(a, delta, st, s);
+}
+
 }  // namespace ember

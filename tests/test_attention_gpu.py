@@ -113,6 +113,15 @@ def test_bf16_forward_negative_scale():
     assert np.abs(o - ro).max() <= BF16_TOL and np.abs(lse - rl).max() <= BF16_TOL
 
 
+def test_bf16_backward_is_deterministic():
+    q, k, v = (bf16_round(seeded((1, 3, 640, 128), s, 0.5)) for s in (1, 2, 3))
+    g = bf16_round(seeded((1, 3, 640, 128), 4))
+    a = run_bwd(q, k, v, g, None, True, "bfloat16")
+    b = run_bwd(q, k, v, g, None, True, "bfloat16")
+    for x, y in zip(a, b):
+        assert np.array_equal(x, y)
+
+
 def test_bf16_forward_is_deterministic():
     q, k, v = (bf16_round(seeded((1, 4, 640, 128), s, 0.5)) for s in (1, 2, 3))
     a = run_fwd(q, k, v, None, True, "bfloat16")[0]
@@ -120,10 +129,16 @@ def test_bf16_forward_is_deterministic():
     assert np.array_equal(a, b)
 
 
-@pytest.mark.parametrize("shape", [(1, 2, 96, 160, 64), (1, 1, 200, 200, 128), (1, 2, 64, 64, 80)])
+@pytest.mark.parametrize("shape", [
+    (1, 2, 96, 160, 64), (1, 1, 200, 200, 128), (1, 2, 64, 64, 80),       # last one: CUDA-core path
+    (1, 1, 128, 128, 128), (1, 2, 256, 256, 128), (1, 2, 300, 300, 128), (1, 1, 200, 520, 128),
+    (2, 2, 512, 512, 128), (1, 2, 300, 300, 64), (1, 1, 1, 257, 128), (1, 2, 640, 1024, 64),
+])
 @pytest.mark.parametrize("causal", [False, True])
 def test_bf16_backward(shape, causal):
     B, H, Lq, Lk, D = shape
+    if D in (64, 128):
+        assert _lib.lib().ember_attention_kernel_name(1, Lq, Lk, D, 1) == b"sm100_tcgen05"
     q, k, v = (bf16_round(seeded((B, H, L, D), s, 0.5)) for L, s in ((Lq, 1), (Lk, 2), (Lk, 3)))
     g = bf16_round(seeded((B, H, Lq, D), 4))
     ref = cpu_oracle.attention_bwd(q, k, v, g, None, causal)
