@@ -38,6 +38,8 @@ SIGNATURES = {
     "ember_attention_fwd": (_i, [_vp] * 5 + [_i] * 4 + [_f, _i, _i, _vp]),
     "ember_attention_bwd": (_i, [_vp] * 9 + [_i] * 4 + [_f, _i, _i, _vp, _sz, _vp]),
     "ember_attention_decode": (_i, [_vp] * 5 + [_i] * 3 + [_f, _i, _i, _vp, _sz, _vp]),
+    "ember_attention_decode_static": (_i, [_vp] * 5 + [_i] * 3 + [_f, _i, _i, _vp]),
+    "ember_attention_decode_static_capacity": (_sz, []),
     "ember_attention_workspace_bytes": (_sz, [_i] * 7),
     "ember_attention_decode_splits": (_i, [_i] * 4),
     "ember_attention_kernel_name": (ctypes.c_char_p, [_i] * 5),

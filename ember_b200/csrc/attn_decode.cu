@@ -321,3 +321,81 @@ int decode_attention(const AttnArgs &a, int splits, void *workspace, DeviceState
 }
 
 }  // namespace ember
+
+// ------------------------------------------------------------------------------------------------
+// Decode without any allocation: the split partials live in a fixed array inside the library image.
+// ------------------------------------------------------------------------------------------------
+namespace {
+
+// 4 MiB of float32 partials. Every GPU that loads this library carries the array until the process
+// exits, so it is kept modest; it bounds batch_heads * splits * (d + 2) (see the entry point).
+constexpr size_t kStaticScratchFloats = 1u << 20;
+static __device__ __align__(256) float g_decode_scratch[kStaticScratchFloats];
+
+// Device address of g_decode_scratch, per device. In host code the array's name is only a handle
+// for the runtime, not something a kernel can dereference, so the address is looked up once per
+// device with cudaGetSymbolAddress while that device is current.
+constexpr int kMaxScratchDevices = 64;
+float *g_scratch_addr[kMaxScratchDevices] = {};
+
+size_t static_partials_floats(int bh, int d, int splits)
+{
+    return ember::decode_workspace_bytes(bh, d, splits) / sizeof(float);
+}
+
+}  // namespace
+
+extern "C" EMBER_API int ember_attention_decode_static(const void *q, const void *k, const void *v, void *out,
+                                                       float *lse, int batch_heads, int lk, int d, float scale,
+                                                       int dtype, int num_splits, void *stream)
+{
+    using namespace ember;
+    EMBER_REQUIRE(dtype == EMBER_F32 || dtype == EMBER_BF16, "ember_attention_decode_static: unknown dtype %d", dtype);
+    EMBER_REQUIRE(batch_heads > 0 && lk > 0 && d > 0,
+                  "ember_attention_decode_static: extents must be positive, got batch_heads=%d lk=%d d=%d",
+                  batch_heads, lk, d);
+    EMBER_REQUIRE(isfinite(scale), "ember_attention_decode_static: scale must be finite");
+    EMBER_REQUIRE(q && k && v && out, "ember_attention_decode_static: NULL tensor pointer");
+    EMBER_REQUIRE((((uintptr_t)q | (uintptr_t)k | (uintptr_t)v) & 15) == 0,
+                  "ember_attention_decode_static: q, k and v must be 16-byte aligned");
+
+    int dev = 0;
+    EMBER_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxScratchDevices) {
+        set_error("ember_attention_decode_static: device index %d out of range", dev);
+        return EMBER_ERR_UNSUPPORTED;
+    }
+    if (!g_scratch_addr[dev]) {  // first call on this device: resolve the array's device address
+        float *ptr = nullptr;
+        EMBER_CUDA_TRY(cudaGetSymbolAddress((void **)&ptr, g_decode_scratch));
+        g_scratch_addr[dev] = ptr;
+    }
+
+    int splits = num_splits;
+    if (splits <= 0) {
+        int sms = 0;
+        EMBER_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+        splits = decode_pick_splits(batch_heads, lk, d, dtype, sms);
+        // the library's own choice shrinks until the partials fit; one split needs no scratch at all
+        while (splits > 1 && static_partials_floats(batch_heads, d, splits) > kStaticScratchFloats) splits--;
+    }
+    if (splits > lk) splits = lk;
+    const size_t need = static_partials_floats(batch_heads, d, splits);
+    if (need > kStaticScratchFloats) {
+        set_error("ember_attention_decode_static: %d splits of %d (batch*head) rows with d=%d need %zu bytes of "
+                  "partials, the built-in scratch holds %zu; pass fewer splits or use ember_attention_decode",
+                  splits, batch_heads, d, need * sizeof(float), kStaticScratchFloats * sizeof(float));
+        return EMBER_ERR_WORKSPACE;
+    }
+    AttnArgs a;
+    a.q = q; a.k = k; a.v = v; a.out = out; a.lse = lse;
+    a.bh = batch_heads; a.lq = 1; a.lk = lk; a.d = d;
+    a.scale = scale; a.causal = 0; a.dtype = dtype;
+    return decode_attention(a, splits, g_scratch_addr[dev], nullptr, reinterpret_cast<cudaStream_t>(stream));
+}
+
+extern "C" EMBER_API size_t ember_attention_decode_static_capacity(void)
+{
+    return kStaticScratchFloats * sizeof(float);
+}
+

@@ -116,6 +116,31 @@ EMBER_API int ember_attention_decode(const void *q, const void *k, const void *v
                            int batch_heads, int lk, int d, float scale, int dtype, int num_splits,
                            void *workspace, size_t workspace_bytes, void *stream);
 
+/* ---- decode for callers that cannot allocate. No counterpart in the reference.
+ *      Some hosts of this library may not call cudaMalloc on the path that runs decode: a
+ *      serving loop that has handed the whole device to its own arena, code running where an
+ *      allocation would synchronise the device or is forbidden outright. This variant takes no
+ *      workspace and allocates nothing (no cudaMalloc/cudaFree, no pool, no stream creation): the
+ *      per-split partials go to a fixed 4 MiB array that is part of the library image, so every
+ *      GPU that loads the library holds those 4 MiB until the process exits.
+ *      Limits: batch_heads * splits * d * 4 bytes plus batch_heads * splits * 8 bytes (each
+ *      rounded up to 256) must fit in ember_attention_decode_static_capacity() bytes; a request
+ *      beyond that returns EMBER_ERR_WORKSPACE with the sizes in ember_last_error(). With
+ *      num_splits <= 0 the library lowers its own split choice until it fits (one split needs no
+ *      scratch), so that form never fails for size.
+ *      stream: a cudaStream_t as void*; NULL here means the CUDA default stream (the library's
+ *      own stream is not created by this call).
+ *      The first call on each device looks up the array's device address
+ *      (cudaGetSymbolAddress) with that device current; make that first call outside any
+ *      stream capture. All calls share the one array and it keeps the previous call's contents:
+ *      nothing in it needs clearing (each call overwrites what it later reads), but two calls
+ *      that overlap on the GPU (different streams, no ordering between them) race on it. ---- */
+EMBER_API int ember_attention_decode_static(const void *q, const void *k, const void *v, void *out,
+                                            float *lse, int batch_heads, int lk, int d, float scale,
+                                            int dtype, int num_splits, void *stream);
+/* Size in bytes of the built-in scratch array of ember_attention_decode_static. */
+EMBER_API size_t ember_attention_decode_static_capacity(void);
+
 /* Bytes of workspace the call with these arguments needs (0 if none). For
  * EMBER_OP_DECODE lq is ignored; num_splits <= 0 means "the library's choice". */
 EMBER_API size_t ember_attention_workspace_bytes(int op, int batch_heads, int lq, int lk, int d, int dtype,
