@@ -62,7 +62,25 @@ def build(force: bool = False, verbose: bool = False) -> str:
                     print(out)
     if jobs or not os.path.exists(LIB):
         run([_nvcc(), "-shared", "-o", LIB, *objs, "-cudart", "shared"])
+    build_binding(force or bool(jobs))
     return LIB
+
+
+def build_binding(force: bool = False) -> str:
+    """Compiles the CPython binding (csrc/tensor_api.c) into ember_b200/_core/, linked against the
+    CUDA library beside it (found at run time through an $ORIGIN-relative rpath)."""
+    import sysconfig
+
+    src = os.path.join(CSRC, "tensor_api.c")
+    out = os.path.join(HERE, "_core", "_tensor" + sysconfig.get_config_var("EXT_SUFFIX"))
+    hdr = os.path.join(os.path.dirname(HERE), "include", "ember_b200.h")
+    if force or not os.path.exists(out) or os.path.getmtime(out) < max(os.path.getmtime(src), os.path.getmtime(hdr)):
+        cmd = [os.environ.get("CC", "gcc"), "-O2", "-fPIC", "-shared", "-I", sysconfig.get_paths()["include"], src,
+               "-o", out, "-L", HERE, "-lember_b200", "-Wl,-rpath,$ORIGIN/.."]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError("binding build failed: %s\n%s" % (" ".join(cmd), r.stderr))
+    return out
 
 
 if __name__ == "__main__":

@@ -193,7 +193,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
                 issued = i + 1;
             }
             drain_copies<C>(bar0, issued);
-        } else if (warp == 8 && lane == 0) {
+        } else if (warp == 8) {  // all 32 lanes, converged; one elected lane issues
             // ---------------------------------------------------------------- MMA issue
             constexpr uint32_t IDESC_SS = idesc_bf16_f32(128, 128, 0, 0);
             constexpr uint32_t IDESC_TS = idesc_bf16_f32(128, HD, 0, 1);
@@ -206,32 +206,33 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
                 const uint32_t doa = qa + C::TILE_BYTES;
                 ok = ok && mbar_wait(BAR(C::B_FULL + st), ph, abort_flag, p.status, WB_FULL);
                 tc_fence_after();
+                const uint32_t k_lo = desc_lo(ka, 16), v_lo = desc_lo(va, 16);
+                const uint32_t q_lo = desc_lo(qa, 16), do_lo = desc_lo(doa, 16);
+                const uint32_t qmn_lo = desc_lo(qa, C::SUB_BYTES), domn_lo = desc_lo(doa, C::SUB_BYTES);
 #pragma unroll
                 for (int ks = 0; ks < HD / 16; ks++) {  // S^T = K Q^T
-                    const uint32_t o = (ks / 4) * C::SUB_BYTES + (ks % 4) * 32;
-                    mma_ss(tmem + C::T_S, smem_desc_sw128(ka + o, 16, 1024), smem_desc_sw128(qa + o, 16, 1024),
-                           IDESC_SS, ks > 0);
+                    const uint32_t o16 = ((ks / 4) * C::SUB_BYTES + (ks % 4) * 32) >> 4;
+                    mma_ss_lo(tmem + C::T_S, k_lo + o16, q_lo + o16, IDESC_SS, ks > 0);
                 }
 #pragma unroll
                 for (int ks = 0; ks < HD / 16; ks++) {  // dP^T = V dO^T
-                    const uint32_t o = (ks / 4) * C::SUB_BYTES + (ks % 4) * 32;
-                    mma_ss(tmem + C::T_DP, smem_desc_sw128(va + o, 16, 1024), smem_desc_sw128(doa + o, 16, 1024),
-                           IDESC_SS, ks > 0);
+                    const uint32_t o16 = ((ks / 4) * C::SUB_BYTES + (ks % 4) * 32) >> 4;
+                    mma_ss_lo(tmem + C::T_DP, v_lo + o16, do_lo + o16, IDESC_SS, ks > 0);
                 }
-                tc_commit(BAR(C::B_SDP));
+                tc_commit_elect(BAR(C::B_SDP));
                 ok = ok && mbar_wait(BAR(C::B_PDS), i & 1, abort_flag, p.status, WB_PDS);
                 tc_fence_after();
 #pragma unroll
                 for (int ks = 0; ks < 8; ks++)  // dV += P^T dO
-                    mma_ts(tmem + C::T_ACC0, tmem + C::T_S + ks * 8,
-                           smem_desc_sw128(doa + ks * 2048, C::SUB_BYTES, 1024), IDESC_TS, (i > 0 || ks > 0) ? 1u : 0u);
+                    mma_ts_lo(tmem + C::T_ACC0, tmem + C::T_S + ks * 8, domn_lo + ks * (2048 >> 4), IDESC_TS,
+                              (i > 0 || ks > 0) ? 1u : 0u);
 #pragma unroll
                 for (int ks = 0; ks < 8; ks++)  // dK += dS^T Q
-                    mma_ts(tmem + C::T_ACC1, tmem + C::T_DP + ks * 8,
-                           smem_desc_sw128(qa + ks * 2048, C::SUB_BYTES, 1024), IDESC_TS, (i > 0 || ks > 0) ? 1u : 0u);
-                tc_commit(BAR(C::B_EMPTY + st));
+                    mma_ts_lo(tmem + C::T_ACC1, tmem + C::T_DP + ks * 8, qmn_lo + ks * (2048 >> 4), IDESC_TS,
+                              (i > 0 || ks > 0) ? 1u : 0u);
+                tc_commit_elect(BAR(C::B_EMPTY + st));
             }
-            tc_commit(BAR(C::B_ACC));
+            tc_commit_elect(BAR(C::B_ACC));
         }
     } else {
         // -------------------------------------------------------------------- compute
@@ -370,7 +371,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
                 issued = j + 1;
             }
             drain_copies<C>(bar0, issued);
-        } else if (warp == 8 && lane == 0) {
+        } else if (warp == 8) {  // all 32 lanes, converged; one elected lane issues
             constexpr uint32_t IDESC_SS = idesc_bf16_f32(128, 128, 0, 0);
             constexpr uint32_t IDESC_TS = idesc_bf16_f32(128, HD, 0, 1);
             const uint32_t qa = smem_base + C::OFF_RES0, doa = smem_base + C::OFF_RES1;
@@ -382,28 +383,29 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
                 const uint32_t va = ka + C::TILE_BYTES;
                 ok = ok && mbar_wait(BAR(C::B_FULL + st), ph, abort_flag, p.status, WB_FULL);
                 tc_fence_after();
+                const uint32_t q_lo = desc_lo(qa, 16), do_lo = desc_lo(doa, 16);
+                const uint32_t k_lo = desc_lo(ka, 16), v_lo = desc_lo(va, 16);
+                const uint32_t kmn_lo = desc_lo(ka, C::SUB_BYTES);
 #pragma unroll
                 for (int ks = 0; ks < HD / 16; ks++) {  // S = Q K^T
-                    const uint32_t o = (ks / 4) * C::SUB_BYTES + (ks % 4) * 32;
-                    mma_ss(tmem + C::T_S, smem_desc_sw128(qa + o, 16, 1024), smem_desc_sw128(ka + o, 16, 1024),
-                           IDESC_SS, ks > 0);
+                    const uint32_t o16 = ((ks / 4) * C::SUB_BYTES + (ks % 4) * 32) >> 4;
+                    mma_ss_lo(tmem + C::T_S, q_lo + o16, k_lo + o16, IDESC_SS, ks > 0);
                 }
 #pragma unroll
                 for (int ks = 0; ks < HD / 16; ks++) {  // dP = dO V^T
-                    const uint32_t o = (ks / 4) * C::SUB_BYTES + (ks % 4) * 32;
-                    mma_ss(tmem + C::T_DP, smem_desc_sw128(doa + o, 16, 1024), smem_desc_sw128(va + o, 16, 1024),
-                           IDESC_SS, ks > 0);
+                    const uint32_t o16 = ((ks / 4) * C::SUB_BYTES + (ks % 4) * 32) >> 4;
+                    mma_ss_lo(tmem + C::T_DP, do_lo + o16, v_lo + o16, IDESC_SS, ks > 0);
                 }
-                tc_commit(BAR(C::B_SDP));
+                tc_commit_elect(BAR(C::B_SDP));
                 ok = ok && mbar_wait(BAR(C::B_PDS), j & 1, abort_flag, p.status, WB_PDS);
                 tc_fence_after();
 #pragma unroll
                 for (int ks = 0; ks < 8; ks++)  // dQ += dS K
-                    mma_ts(tmem + C::T_ACC0, tmem + C::T_DP + ks * 8,
-                           smem_desc_sw128(ka + ks * 2048, C::SUB_BYTES, 1024), IDESC_TS, (j > 0 || ks > 0) ? 1u : 0u);
-                tc_commit(BAR(C::B_EMPTY + st));
+                    mma_ts_lo(tmem + C::T_ACC0, tmem + C::T_DP + ks * 8, kmn_lo + ks * (2048 >> 4), IDESC_TS,
+                              (j > 0 || ks > 0) ? 1u : 0u);
+                tc_commit_elect(BAR(C::B_EMPTY + st));
             }
-            tc_commit(BAR(C::B_ACC));
+            tc_commit_elect(BAR(C::B_ACC));
         }
     } else {
         reg_alloc_232();

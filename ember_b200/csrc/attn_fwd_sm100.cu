@@ -33,6 +33,29 @@ constexpr int FWD_THREADS = 384;
 constexpr float LOG2E_F = 1.4426950408889634f;
 constexpr float LN2_F = 0.6931471805599453f;
 constexpr float RESCALE_THRESHOLD = 8.0f;  // log2 units
+constexpr int EMU_PAIRS_OF_4 = 1;          // pairs per group of 4 pairs whose exponentials avoid the MUFU
+
+// 2^x for a pair of x <= ~8 on the FMA/ALU pipes (packed float32 pairs): round-to-nearest split
+// x = n + f, f in [-0.5, 0.5], a cubic for 2^f (relative error 7.5e-5, far below bf16 resolution) and
+// an exponent-field add for 2^n. Inputs below -125 (masked scores are -inf) are clamped and come out
+// as ~2^-125, i.e. zero in bf16.
+__device__ __forceinline__ void exp2_poly2(f32x2 x2, float &p0, float &p1)
+{
+    float x0, x1;
+    unpack2(x2, x0, x1);
+    x2 = pack2(fmaxf(x0, -125.f), fmaxf(x1, -125.f));
+    const f32x2 magic = pack2(12582912.f, 12582912.f);  // 1.5 * 2^23: integer part -> low mantissa bits
+    const f32x2 xr = add2(x2, magic);
+    const f32x2 f = sub2(x2, sub2(xr, magic));
+    f32x2 pl = fma2(pack2(0.05517167f, 0.05517167f), f, pack2(0.24261112f, 0.24261112f));
+    pl = fma2(pl, f, pack2(0.69326099f, 0.69326099f));
+    pl = fma2(pl, f, pack2(0.99992807f, 0.99992807f));
+    float r0, r1, q0, q1;
+    unpack2(xr, r0, r1);
+    unpack2(pl, q0, q1);
+    p0 = __int_as_float(__float_as_int(q0) + (__float_as_int(r0) << 23));
+    p1 = __int_as_float(__float_as_int(q1) + (__float_as_int(r1) << 23));
+}
 
 template <int HD>
 struct FwdCfg {
@@ -44,7 +67,7 @@ struct FwdCfg {
     static constexpr int OFF_K = OFF_Q + 2 * TILE_BYTES;
     static constexpr int OFF_V = OFF_K + STAGES * TILE_BYTES;
     static constexpr int OFF_BAR = OFF_V + STAGES * TILE_BYTES;
-    static constexpr int NUM_BARS = 1 + 4 * STAGES + 6;
+    static constexpr int NUM_BARS = 1 + 4 * STAGES + 8;
     static constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;  // barriers + misc, + alignment slack
     static constexpr int TMEM_S = 0;
     static constexpr int TMEM_O = 256;
@@ -78,7 +101,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
     auto BAR = [&](int i) { return bar0 + 8u * (uint32_t)i; };
     const int B_Q = 0;
     const int B_KFULL = 1, B_KEMPTY = B_KFULL + C::STAGES, B_VFULL = B_KEMPTY + C::STAGES,
-              B_VEMPTY = B_VFULL + C::STAGES, B_S = B_VEMPTY + C::STAGES, B_P = B_S + 2, B_O = B_P + 2;
+              B_VEMPTY = B_VFULL + C::STAGES, B_S = B_VEMPTY + C::STAGES, B_P = B_S + 2, B_O = B_P + 4;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem_gen + C::OFF_BAR + 8 * C::NUM_BARS);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
@@ -113,7 +136,8 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
         }
         for (int t = 0; t < 2; t++) {
             mbar_init(BAR(B_S + t), 1);
-            mbar_init(BAR(B_P + t), 128);
+            mbar_init(BAR(B_P + 2 * t), 4);      // first 64 keys of P written (one arrival per warp)
+            mbar_init(BAR(B_P + 2 * t + 1), 4);  // last 64 keys of P written
             mbar_init(BAR(B_O + t), 1);
         }
         fence_mbar_init();
@@ -170,30 +194,30 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
                 while (!mbar_try_wait(BAR(B_VFULL + j % C::STAGES), (j / C::STAGES) & 1) &&
                        clock64() - t0 < kWaitLimitCycles) {}
             while (!mbar_try_wait(BAR(B_Q), 0) && clock64() - t0 < kWaitLimitCycles) {}
-        } else if (warp == 8 && lane == 0) {
+        } else if (warp == 8) {  // all 32 lanes, converged; one elected lane issues
             // ------------------------------------------------------------ MMA issue
             constexpr uint32_t IDESC_S = idesc_bf16_f32(128, 128, 0, 0);
             constexpr uint32_t IDESC_O = idesc_bf16_f32(128, HD, 0, 1);
             auto issue_s = [&](int t, int st) {
-                const uint32_t qa = smem_base + C::OFF_Q + t * C::TILE_BYTES;
-                const uint32_t ka = smem_base + C::OFF_K + st * C::TILE_BYTES;
+                const uint32_t q_lo = desc_lo(smem_base + C::OFF_Q + t * C::TILE_BYTES, 16);
+                const uint32_t k_lo = desc_lo(smem_base + C::OFF_K + st * C::TILE_BYTES, 16);
 #pragma unroll
                 for (int ks = 0; ks < HD / 16; ks++) {
-                    const uint32_t o = (ks / 4) * C::SUB_BYTES + (ks % 4) * 32;
-                    mma_ss(tmem + C::TMEM_S + t * 128, smem_desc_sw128(qa + o, 16, 1024),
-                           smem_desc_sw128(ka + o, 16, 1024), IDESC_S, ks > 0);
+                    const uint32_t o16 = ((ks / 4) * C::SUB_BYTES + (ks % 4) * 32) >> 4;
+                    mma_ss_lo(tmem + C::TMEM_S + t * 128, q_lo + o16, k_lo + o16, IDESC_S, ks > 0);
                 }
-                tc_commit(BAR(B_S + t));
+                tc_commit_elect(BAR(B_S + t));
             };
-            auto issue_pv = [&](int t, int st, bool first) {
-                const uint32_t va = smem_base + C::OFF_V + st * C::TILE_BYTES;
+            // O_t += P_t V for keys [64*half, 64*half + 64) of the tile
+            auto issue_pv_half = [&](int t, int st, int half, bool first) {
+                const uint32_t v_lo = desc_lo(smem_base + C::OFF_V + st * C::TILE_BYTES, C::SUB_BYTES);
 #pragma unroll
-                for (int ks = 0; ks < 8; ks++) {
-                    mma_ts(tmem + C::TMEM_O + t * HD, tmem + C::TMEM_S + t * 128 + ks * 8,
-                           smem_desc_sw128(va + ks * 2048, C::SUB_BYTES, 1024), IDESC_O,
-                           (!first || ks > 0) ? 1u : 0u);
+                for (int k4 = 0; k4 < 4; k4++) {
+                    const int ks = half * 4 + k4;
+                    mma_ts_lo(tmem + C::TMEM_O + t * HD, tmem + C::TMEM_S + t * 128 + ks * 8, v_lo + ks * (2048 >> 4),
+                              IDESC_O, (!first || ks > 0) ? 1u : 0u);
                 }
-                tc_commit(BAR(B_O + t));
+                if (half == 1) tc_commit_elect(BAR(B_O + t));
             };
 
             bool ok = mbar_wait(BAR(B_Q), 0, abort_flag, p.status, W_MMA_Q);
@@ -201,7 +225,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
             tc_fence_after();
             if (n_t[0] > 0) issue_s(0, 0);
             if (n_t[1] > 0) issue_s(1, 0);
-            tc_commit(BAR(B_KEMPTY + 0));
+            tc_commit_elect(BAR(B_KEMPTY + 0));
             for (int j = 0; j < n && ok; j++) {
                 const int st = j % C::STAGES;
                 const uint32_t ph = (j / C::STAGES) & 1;
@@ -212,9 +236,12 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
 #pragma unroll
                 for (int t = 0; t < 2; t++) {
                     if (j < n_t[t]) {
-                        ok = ok && mbar_wait(BAR(B_P + t), j & 1, abort_flag, p.status, W_MMA_P);
+                        ok = ok && mbar_wait(BAR(B_P + 2 * t), j & 1, abort_flag, p.status, W_MMA_P);
                         tc_fence_after();
-                        issue_pv(t, st, j == 0);
+                        issue_pv_half(t, st, 0, j == 0);
+                        ok = ok && mbar_wait(BAR(B_P + 2 * t + 1), j & 1, abort_flag, p.status, W_MMA_P);
+                        tc_fence_after();
+                        issue_pv_half(t, st, 1, j == 0);
                     }
                     if (j + 1 < n_t[t]) {
                         if (!k_next_ready) {
@@ -225,8 +252,8 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
                         issue_s(t, st1);
                     }
                 }
-                tc_commit(BAR(B_VEMPTY + st));
-                if (j + 1 < n) tc_commit(BAR(B_KEMPTY + st1));
+                tc_commit_elect(BAR(B_VEMPTY + st));
+                if (j + 1 < n) tc_commit_elect(BAR(B_KEMPTY + st1));
             }
         }
     } else {
@@ -263,16 +290,28 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
                 for (int i = 0; i < 128; i++)
                     if (j * 128 + i > limit_row) s[i] = (c > 0.f) ? -INFINITY : INFINITY;
             }
-            float mx;
+            // row maximum (minimum for a negative scale): 8 independent chains of 3-input max
+            float mx8[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) mx8[i] = s[i];
             if (c > 0.f) {
-                mx = s[0];
 #pragma unroll
-                for (int i = 1; i < 128; i++) mx = fmaxf(mx, s[i]);
+                for (int i = 8; i + 16 <= 128; i += 16)
+#pragma unroll
+                    for (int k8 = 0; k8 < 8; k8++) mx8[k8] = max3(mx8[k8], s[i + k8], s[i + 8 + k8]);
+#pragma unroll
+                for (int k8 = 0; k8 < 8; k8++) mx8[k8] = fmaxf(mx8[k8], s[120 + k8]);
+                mx8[0] = max3(max3(mx8[0], mx8[1], mx8[2]), max3(mx8[3], mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7]));
             } else {
-                mx = s[0];
 #pragma unroll
-                for (int i = 1; i < 128; i++) mx = fminf(mx, s[i]);
+                for (int i = 8; i + 16 <= 128; i += 16)
+#pragma unroll
+                    for (int k8 = 0; k8 < 8; k8++) mx8[k8] = min3(mx8[k8], s[i + k8], s[i + 8 + k8]);
+#pragma unroll
+                for (int k8 = 0; k8 < 8; k8++) mx8[k8] = fminf(mx8[k8], s[120 + k8]);
+                mx8[0] = min3(min3(mx8[0], mx8[1], mx8[2]), min3(mx8[3], mx8[4], mx8[5]), fminf(mx8[6], mx8[7]));
             }
+            const float mx = mx8[0];
             const float m_new = fmaxf(m_ref, mx * c);
             if (j == 0) {
                 m_ref = m_new;  // finite: key 0 is visible to every row
@@ -295,24 +334,41 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
                     }
                 }
             }
-            const float neg_m = -m_ref;
-            float sum = 0.f;
+            const f32x2 negm2 = pack2(-m_ref, -m_ref);
+            const f32x2 c2 = pack2(c, c);
+            f32x2 sum2[4] = {0, 0, 0, 0};  // bit pattern of (0.f, 0.f)
 #pragma unroll
-            for (int ch = 0; ch < 4; ch++) {
-                uint32_t pk[16];
+            for (int half = 0; half < 2; half++) {
 #pragma unroll
-                for (int i = 0; i < 16; i++) {
-                    const float p0 = ex2(fmaf(s[ch * 32 + 2 * i], c, neg_m));
-                    const float p1 = ex2(fmaf(s[ch * 32 + 2 * i + 1], c, neg_m));
-                    sum += p0 + p1;
-                    pk[i] = pack_bf16(p0, p1);
+                for (int ch = 2 * half; ch < 2 * half + 2; ch++) {
+                    uint32_t pk[16];
+#pragma unroll
+                    for (int i = 0; i < 16; i++) {
+                        const f32x2 x2 = fma2(pack2(s[ch * 32 + 2 * i], s[ch * 32 + 2 * i + 1]), c2, negm2);
+                        float p0, p1;
+                        if (i % 4 < EMU_PAIRS_OF_4) {  // polynomial on the FMA pipe
+                            exp2_poly2(x2, p0, p1);
+                        } else {                        // MUFU
+                            float x0, x1;
+                            unpack2(x2, x0, x1);
+                            p0 = ex2(x0);
+                            p1 = ex2(x1);
+                        }
+                        sum2[i & 3] = add2(sum2[i & 3], pack2(p0, p1));
+                        pk[i] = pack_bf16(p0, p1);
+                    }
+                    tmem_st_32x32b_x16(ts + ch * 16, pk);
                 }
-                tmem_st_32x32b_x16(ts + ch * 16, pk);
+                tmem_wait_st();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(BAR(B_P + 2 * t + half));
             }
-            l += sum;
-            tmem_wait_st();
-            tc_fence_before();
-            mbar_arrive(BAR(B_P + t));
+            {
+                float a0, a1;
+                unpack2(add2(add2(sum2[0], sum2[1]), add2(sum2[2], sum2[3])), a0, a1);
+                l += a0 + a1;
+            }
         }
 
         if (nk > 0) {

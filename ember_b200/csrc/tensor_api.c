@@ -1,0 +1,384 @@
+/* tensor_api.c -- CPython binding of the attention path (module ember_b200._core._tensor).
+ *
+ * Written in the style of the reference's binding (src/tensor/tensor_api.c): a `_Tensor` type that
+ * owns one device buffer (d_ptr + element count first in the struct, as in
+ * src/core/tensor_types.h:6-9), METH_VARARGS module functions that parse with "O!" against the
+ * type, validate sizes (ValueError with a formatted message, as tensor_api.c:196-199,338-347),
+ * allocate the results (MemoryError on failure, as :28-31), call ONE extern "C" function of the
+ * CUDA library and wrap the result. Shapes are passed from Python as ints because the native
+ * object only knows its element count (tensor_api.c:386-394). Additions over the reference: a
+ * dtype field (0 = float32, 1 = bfloat16) and a 64-bit element count after the reference's two
+ * fields; native status codes become Python exceptions instead of exit().
+ */
+#define PY_SSIZE_T_CLEAN
+#include <Python.h>
+#include <structmember.h>
+
+#include "../../include/ember_b200.h"
+
+typedef struct {
+    PyObject_HEAD void *d_ptr;
+    int size;            /* element count, saturated at INT_MAX (reference field) */
+    int dtype;           /* EMBER_F32 / EMBER_BF16 */
+    long long size64;    /* exact element count */
+} _Tensor;
+
+static PyTypeObject _TensorType;
+
+static size_t elem_size(int dtype) { return dtype == EMBER_BF16 ? 2 : 4; }
+
+static PyObject *raise_status(int rc)
+{
+    PyObject *exc = rc == EMBER_ERR_INVALID ? PyExc_ValueError
+                    : rc == EMBER_ERR_NOMEM ? PyExc_MemoryError
+                                            : PyExc_RuntimeError;
+    PyErr_Format(exc, "%s: %s", ember_status_string(rc), ember_last_error());
+    return NULL;
+}
+
+/* ---- allocation helper: a result _Tensor with `n` device elements of `dtype` ---- */
+static _Tensor *alloc_result(long long n, int dtype)
+{
+    _Tensor *t = (_Tensor *)_TensorType.tp_alloc(&_TensorType, 0);
+    if (!t) return NULL;
+    t->size64 = n;
+    t->size = n > 2147483647LL ? 2147483647 : (int)n;
+    t->dtype = dtype;
+    t->d_ptr = alloc_memory((size_t)(n > 0 ? n : 1) * elem_size(dtype));
+    if (!t->d_ptr) {
+        Py_DECREF(t);
+        PyErr_Format(PyExc_MemoryError, "Failed to allocate device memory: %s", ember_last_error());
+        return NULL;
+    }
+    return t;
+}
+
+static void _Tensor_dealloc(_Tensor *self)
+{
+    if (self->d_ptr) free_memory(self->d_ptr);
+    Py_TYPE(self)->tp_free((PyObject *)self);
+}
+
+static int _Tensor_init(_Tensor *self, PyObject *args, PyObject *kwds)
+{
+    long long n = 0;
+    int dtype = EMBER_F32;
+    if (!PyArg_ParseTuple(args, "L|i", &n, &dtype)) return -1;
+    if (n < 0 || (dtype != EMBER_F32 && dtype != EMBER_BF16)) {
+        PyErr_SetString(PyExc_ValueError, "_Tensor(size, dtype): size must be >= 0 and dtype 0 or 1");
+        return -1;
+    }
+    self->size64 = n;
+    self->size = n > 2147483647LL ? 2147483647 : (int)n;
+    self->dtype = dtype;
+    self->d_ptr = alloc_memory((size_t)(n > 0 ? n : 1) * elem_size(dtype));
+    if (!self->d_ptr) {
+        PyErr_Format(PyExc_MemoryError, "Failed to allocate device memory: %s", ember_last_error());
+        return -1;
+    }
+    return 0;
+}
+
+/* host float32 buffer -> this tensor (converted on the device when the tensor is bf16) */
+static int upload_f32(_Tensor *t, const float *host, long long n)
+{
+    if (t->dtype == EMBER_F32) {
+        copy_to_device(t->d_ptr, host, (size_t)n * 4);
+        return 0;
+    }
+    void *stage = alloc_memory((size_t)n * 4);
+    if (!stage) {
+        PyErr_Format(PyExc_MemoryError, "Failed to allocate device memory: %s", ember_last_error());
+        return -1;
+    }
+    copy_to_device(stage, host, (size_t)n * 4);
+    int rc = ember_f32_to_bf16((const float *)stage, t->d_ptr, (size_t)n, NULL);
+    free_memory(stage); /* stream-ordered: released after the conversion has run */
+    if (rc) {
+        raise_status(rc);
+        return -1;
+    }
+    return 0;
+}
+
+/* _from_numpy(buffer, dtype=0): C-contiguous float32 buffer -> device tensor
+ * (reference: tensor_api.c:151-186, which also insists on format "f"). */
+static PyObject *_from_numpy(PyObject *module, PyObject *args)
+{
+    PyObject *obj;
+    int dtype = EMBER_F32;
+    if (!PyArg_ParseTuple(args, "O|i", &obj, &dtype)) return NULL;
+    if (dtype != EMBER_F32 && dtype != EMBER_BF16) {
+        PyErr_SetString(PyExc_ValueError, "dtype must be 0 (float32) or 1 (bfloat16)");
+        return NULL;
+    }
+    Py_buffer view;
+    if (PyObject_GetBuffer(obj, &view, PyBUF_C_CONTIGUOUS | PyBUF_FORMAT) < 0) return NULL;
+    if (!view.format || view.format[0] != 'f' || view.format[1] != '\0' || view.itemsize != 4) {
+        PyBuffer_Release(&view);
+        PyErr_SetString(PyExc_TypeError, "Expected a C-contiguous float32 array");
+        return NULL;
+    }
+    long long n = (long long)(view.len / 4);
+    _Tensor *t = alloc_result(n, dtype);
+    if (t && n > 0 && upload_f32(t, (const float *)view.buf, n) < 0) {
+        Py_DECREF(t);
+        t = NULL;
+    }
+    PyBuffer_Release(&view);
+    return (PyObject *)t;
+}
+
+/* tensor._copy_to_buffer(writable float32 buffer): device -> host, widening bf16; waits for the
+ * device like the reference's _to_np (tensor_api.c:132-149). */
+static PyObject *_Tensor_copy_to_buffer(_Tensor *self, PyObject *args)
+{
+    PyObject *obj;
+    if (!PyArg_ParseTuple(args, "O", &obj)) return NULL;
+    Py_buffer view;
+    if (PyObject_GetBuffer(obj, &view, PyBUF_C_CONTIGUOUS | PyBUF_WRITABLE | PyBUF_FORMAT) < 0) return NULL;
+    if (!view.format || view.format[0] != 'f' || view.itemsize != 4 || (long long)(view.len / 4) != self->size64) {
+        PyBuffer_Release(&view);
+        PyErr_Format(PyExc_ValueError, "Expected a writable float32 buffer of %lld elements", self->size64);
+        return NULL;
+    }
+    if (self->size64 > 0) {
+        if (self->dtype == EMBER_F32) {
+            copy_from_device(view.buf, self->d_ptr, (size_t)self->size64 * 4);
+        } else {
+            void *stage = alloc_memory((size_t)self->size64 * 4);
+            if (!stage) {
+                PyBuffer_Release(&view);
+                PyErr_Format(PyExc_MemoryError, "Failed to allocate device memory: %s", ember_last_error());
+                return NULL;
+            }
+            int rc = ember_bf16_to_f32(self->d_ptr, (float *)stage, (size_t)self->size64, NULL);
+            if (!rc) copy_from_device(view.buf, stage, (size_t)self->size64 * 4);
+            free_memory(stage);
+            if (rc) {
+                PyBuffer_Release(&view);
+                return raise_status(rc);
+            }
+        }
+    }
+    PyBuffer_Release(&view);
+    Py_RETURN_NONE;
+}
+
+static PyObject *_Tensor_ptr(_Tensor *self, PyObject *noargs)
+{
+    return PyLong_FromVoidPtr(self->d_ptr);
+}
+
+/* _convert(t, dtype) -> new tensor of the other storage type (or t itself) */
+static PyObject *_convert(PyObject *module, PyObject *args)
+{
+    _Tensor *t;
+    int dtype;
+    if (!PyArg_ParseTuple(args, "O!i", &_TensorType, &t, &dtype)) return NULL;
+    if (dtype == t->dtype) {
+        Py_INCREF(t);
+        return (PyObject *)t;
+    }
+    if (dtype != EMBER_F32 && dtype != EMBER_BF16) {
+        PyErr_SetString(PyExc_ValueError, "dtype must be 0 (float32) or 1 (bfloat16)");
+        return NULL;
+    }
+    _Tensor *out = alloc_result(t->size64, dtype);
+    if (!out) return NULL;
+    int rc = dtype == EMBER_BF16 ? ember_f32_to_bf16((const float *)t->d_ptr, out->d_ptr, (size_t)t->size64, NULL)
+                                 : ember_bf16_to_f32(t->d_ptr, (float *)out->d_ptr, (size_t)t->size64, NULL);
+    if (rc) {
+        Py_DECREF(out);
+        return raise_status(rc);
+    }
+    return (PyObject *)out;
+}
+
+static int check_sizes(const char *fn, _Tensor *q, _Tensor *k, _Tensor *v, long long bh, int lq, int lk, int d)
+{
+    if (bh <= 0 || lq <= 0 || lk <= 0 || d <= 0 || bh > 2147483647LL) {
+        PyErr_Format(PyExc_ValueError, "%s: extents must be positive (B*H=%lld Lq=%d Lk=%d D=%d)", fn, bh, lq, lk, d);
+        return -1;
+    }
+    if (q->size64 != bh * lq * d || k->size64 != bh * lk * d || v->size64 != k->size64) {
+        PyErr_Format(PyExc_ValueError, "%s: size mismatch: q %lld (expected %lld), k %lld, v %lld (expected %lld)", fn,
+                     q->size64, bh * lq * d, k->size64, v->size64, bh * lk * d);
+        return -1;
+    }
+    if (q->dtype != k->dtype || k->dtype != v->dtype) {
+        PyErr_Format(PyExc_TypeError, "%s: q, k and v must share a dtype", fn);
+        return -1;
+    }
+    return 0;
+}
+
+/* _attention_fwd(q, k, v, B, H, Lq, Lk, D, scale, causal) -> (out, lse) */
+static PyObject *_attention_fwd(PyObject *module, PyObject *args)
+{
+    _Tensor *q, *k, *v;
+    int B, H, lq, lk, d, causal;
+    float scale;
+    if (!PyArg_ParseTuple(args, "O!O!O!iiiiifi", &_TensorType, &q, &_TensorType, &k, &_TensorType, &v, &B, &H, &lq,
+                          &lk, &d, &scale, &causal))
+        return NULL;
+    const long long bh = (long long)B * H;
+    if (check_sizes("attention", q, k, v, bh, lq, lk, d) < 0) return NULL;
+    _Tensor *out = alloc_result(bh * lq * d, q->dtype);
+    if (!out) return NULL;
+    _Tensor *lse = alloc_result(bh * lq, EMBER_F32);
+    if (!lse) {
+        Py_DECREF(out);
+        return NULL;
+    }
+    int rc = ember_attention_fwd(q->d_ptr, k->d_ptr, v->d_ptr, out->d_ptr, (float *)lse->d_ptr, (int)bh, lq, lk, d,
+                                 scale, causal, q->dtype, NULL);
+    if (rc) {
+        Py_DECREF(out);
+        Py_DECREF(lse);
+        return raise_status(rc);
+    }
+    return Py_BuildValue("(NN)", out, lse);
+}
+
+/* _attention_bwd(q, k, v, out, lse, dout, B, H, Lq, Lk, D, scale, causal) -> (dq, dk, dv) */
+static PyObject *_attention_bwd(PyObject *module, PyObject *args)
+{
+    _Tensor *q, *k, *v, *o, *lse, *g;
+    int B, H, lq, lk, d, causal;
+    float scale;
+    if (!PyArg_ParseTuple(args, "O!O!O!O!O!O!iiiiifi", &_TensorType, &q, &_TensorType, &k, &_TensorType, &v,
+                          &_TensorType, &o, &_TensorType, &lse, &_TensorType, &g, &B, &H, &lq, &lk, &d, &scale, &causal))
+        return NULL;
+    const long long bh = (long long)B * H;
+    if (check_sizes("attention_backward", q, k, v, bh, lq, lk, d) < 0) return NULL;
+    if (o->size64 != q->size64 || g->size64 != q->size64 || lse->size64 != bh * lq) {
+        PyErr_Format(PyExc_ValueError, "attention_backward: size mismatch: out %lld, dout %lld (expected %lld), lse %lld (expected %lld)",
+                     o->size64, g->size64, q->size64, lse->size64, bh * lq);
+        return NULL;
+    }
+    if (o->dtype != q->dtype || g->dtype != q->dtype || lse->dtype != EMBER_F32) {
+        PyErr_SetString(PyExc_TypeError, "attention_backward: out/dout must have q's dtype and lse must be float32");
+        return NULL;
+    }
+    _Tensor *dq = alloc_result(q->size64, q->dtype), *dk = NULL, *dv = NULL;
+    void *ws = NULL;
+    if (dq) dk = alloc_result(k->size64, q->dtype);
+    if (dk) dv = alloc_result(v->size64, q->dtype);
+    const size_t wsn = ember_attention_workspace_bytes(EMBER_OP_BWD, (int)bh, lq, lk, d, q->dtype, 0);
+    if (dv) {
+        ws = alloc_memory(wsn);
+        if (!ws) PyErr_Format(PyExc_MemoryError, "Failed to allocate device memory: %s", ember_last_error());
+    }
+    if (!ws) {
+        Py_XDECREF(dq);
+        Py_XDECREF(dk);
+        Py_XDECREF(dv);
+        return NULL;
+    }
+    int rc = ember_attention_bwd(q->d_ptr, k->d_ptr, v->d_ptr, o->d_ptr, (const float *)lse->d_ptr, g->d_ptr, dq->d_ptr,
+                                 dk->d_ptr, dv->d_ptr, (int)bh, lq, lk, d, scale, causal, q->dtype, ws, wsn, NULL);
+    free_memory(ws); /* stream-ordered: released after the kernels that use it */
+    if (rc) {
+        Py_DECREF(dq);
+        Py_DECREF(dk);
+        Py_DECREF(dv);
+        return raise_status(rc);
+    }
+    return Py_BuildValue("(NNN)", dq, dk, dv);
+}
+
+/* _attention_decode(q, k, v, B, H, Lk, D, scale, num_splits) -> (out, lse) */
+static PyObject *_attention_decode(PyObject *module, PyObject *args)
+{
+    _Tensor *q, *k, *v;
+    int B, H, lk, d, splits;
+    float scale;
+    if (!PyArg_ParseTuple(args, "O!O!O!iiiifi", &_TensorType, &q, &_TensorType, &k, &_TensorType, &v, &B, &H, &lk, &d,
+                          &scale, &splits))
+        return NULL;
+    const long long bh = (long long)B * H;
+    if (check_sizes("attention_decode", q, k, v, bh, 1, lk, d) < 0) return NULL;
+    _Tensor *out = alloc_result(bh * d, q->dtype);
+    if (!out) return NULL;
+    _Tensor *lse = alloc_result(bh, EMBER_F32);
+    if (!lse) {
+        Py_DECREF(out);
+        return NULL;
+    }
+    const size_t wsn = ember_attention_workspace_bytes(EMBER_OP_DECODE, (int)bh, 1, lk, d, q->dtype, splits);
+    void *ws = NULL;
+    if (wsn) {
+        ws = alloc_memory(wsn);
+        if (!ws) {
+            Py_DECREF(out);
+            Py_DECREF(lse);
+            PyErr_Format(PyExc_MemoryError, "Failed to allocate device memory: %s", ember_last_error());
+            return NULL;
+        }
+    }
+    int rc = ember_attention_decode(q->d_ptr, k->d_ptr, v->d_ptr, out->d_ptr, (float *)lse->d_ptr, (int)bh, lk, d, scale,
+                                    q->dtype, splits, ws, wsn, NULL);
+    if (ws) free_memory(ws);
+    if (rc) {
+        Py_DECREF(out);
+        Py_DECREF(lse);
+        return raise_status(rc);
+    }
+    return Py_BuildValue("(NN)", out, lse);
+}
+
+static PyObject *_sync(PyObject *module, PyObject *noargs)
+{
+    sync_device();
+    Py_RETURN_NONE;
+}
+
+static PyMethodDef _Tensor_methods[] = {
+    {"_copy_to_buffer", (PyCFunction)_Tensor_copy_to_buffer, METH_VARARGS, "Copy to a writable float32 host buffer"},
+    {"_ptr", (PyCFunction)_Tensor_ptr, METH_NOARGS, "Device address as an int"},
+    {NULL}};
+
+static PyMemberDef _Tensor_members[] = {{"size", T_LONGLONG, offsetof(_Tensor, size64), READONLY, "element count"},
+                                        {"dtype", T_INT, offsetof(_Tensor, dtype), READONLY, "0 float32, 1 bfloat16"},
+                                        {NULL}};
+
+#define OP_METHOD(NAME) {#NAME, (PyCFunction)NAME, METH_VARARGS, "Attention path: " #NAME}
+
+static PyMethodDef module_methods[] = {OP_METHOD(_from_numpy),
+                                       OP_METHOD(_convert),
+                                       OP_METHOD(_attention_fwd),
+                                       OP_METHOD(_attention_bwd),
+                                       OP_METHOD(_attention_decode),
+                                       {"_sync", (PyCFunction)_sync, METH_NOARGS, "Wait for the library stream"},
+                                       {NULL, NULL, 0, NULL}};
+
+static struct PyModuleDef tensor_module = {PyModuleDef_HEAD_INIT, "_tensor",
+                                           "B200 attention path behind the reference's binding surface", -1, module_methods};
+
+static PyTypeObject _TensorType = {
+    PyVarObject_HEAD_INIT(NULL, 0).tp_name = "ember_b200._core._tensor._Tensor",
+    .tp_basicsize = sizeof(_Tensor),
+    .tp_flags = Py_TPFLAGS_DEFAULT,
+    .tp_new = PyType_GenericNew,
+    .tp_init = (initproc)_Tensor_init,
+    .tp_dealloc = (destructor)_Tensor_dealloc,
+    .tp_methods = _Tensor_methods,
+    .tp_members = _Tensor_members,
+};
+
+PyMODINIT_FUNC PyInit__tensor(void)
+{
+    if (PyType_Ready(&_TensorType) < 0) return NULL;
+    PyObject *m = PyModule_Create(&tensor_module);
+    if (!m) return NULL;
+    Py_INCREF(&_TensorType);
+    if (PyModule_AddObject(m, "_Tensor", (PyObject *)&_TensorType) < 0) {
+        Py_DECREF(&_TensorType);
+        Py_DECREF(m);
+        return NULL;
+    }
+    PyModule_AddIntConstant(m, "F32", EMBER_F32);
+    PyModule_AddIntConstant(m, "BF16", EMBER_BF16);
+    return m;
+}

@@ -101,3 +101,19 @@ def test_native_argument_checks_return_invalid_without_touching_the_gpu():
         _lib.check(_lib.EMBER_ERR_NOMEM)
     with pytest.raises(RuntimeError):
         _lib.check(_lib.EMBER_ERR_TIMEOUT)
+
+
+def test_cpython_binding_surface_and_type_errors():
+    import numpy as np
+
+    from ember_b200 import _core
+
+    for name in ("_Tensor", "_from_numpy", "_convert", "_attention_fwd", "_attention_bwd", "_attention_decode", "_sync"):
+        assert hasattr(_core, name)
+    assert (_core.F32, _core.BF16) == (_lib.EMBER_F32, _lib.EMBER_BF16)
+    with pytest.raises(TypeError):  # "O!" parse failure, as in the reference binding
+        _core._attention_fwd(1, 2, 3, 1, 1, 4, 4, 8, 1.0, 0)
+    with pytest.raises(TypeError):  # only float32 host buffers are accepted (reference: format "f")
+        _core._from_numpy(np.zeros(4, np.float64))
+    with pytest.raises(ValueError):
+        _core._from_numpy(np.zeros(4, np.float32), 7)
