@@ -17,6 +17,12 @@
 // Both results are deterministic (no atomics). The scale factor of dS is applied once, to the
 // accumulated dK / dQ, in the epilogue.
 //
+// Each kernel is software-pipelined over its tiles in two phases so that the tensor core works
+// while the compute warps do: in the dK/dV kernel the exponentials of tile i+1 run while
+// dK(i) and dP^T(i+1) are multiplied, and dS^T(i+1) is formed while dV(i+1) and S^T(i+2) are; the
+// dQ kernel issues S(j+1) as soon as S(j) has been read into registers. A quarter of the
+// exponentials are evaluated as a polynomial on the FMA pipe to keep the MUFU off the critical path.
+//
 //   warps 0-7   compute: thread (row r, half h) owns TMEM lane r and 64 of the 128 score columns
 //   warp  8     MMA issue (one lane)      warp 9   TMA producer (one lane)      warp 10  TMEM alloc
 #include <math.h>
@@ -49,11 +55,15 @@ struct BwdCfg {
     static constexpr int SMEM_BYTES = OFF_ROWVEC + 2048 + 1024;
     static constexpr int T_S = 0, T_DP = 128, T_ACC0 = 256, T_ACC1 = 256 + HD;
     // barrier indices
-    static constexpr int B_RES = 0, B_FULL = 1, B_EMPTY = B_FULL + STAGES, B_SDP = B_EMPTY + STAGES,
-                         B_PDS = B_SDP + 1, B_ACC = B_PDS + 1, NUM_BARS = B_ACC + 1;
+    static constexpr int B_RES = 0, B_FULL = 1, B_EMPTY = B_FULL + STAGES,
+                         B_S = B_EMPTY + STAGES,   // S (or S^T) of the current tile is in TMEM
+                         B_DP = B_S + 1,           // dP (or dP^T) is in TMEM
+                         B_P = B_DP + 1,           // dK/dV: P^T written; dQ: S has been read (8 warp arrivals)
+                         B_DS = B_P + 1,           // dS (or dS^T) written (8 warp arrivals)
+                         B_ACC = B_DS + 1, NUM_BARS = B_ACC + 1;
 };
 
-enum { WB_RES = 101, WB_FULL, WB_EMPTY, WB_SDP, WB_PDS, WB_ACC };
+enum { WB_RES = 101, WB_FULL, WB_EMPTY, WB_S, WB_DP, WB_P, WB_DS, WB_ACC };
 
 struct BwdParams {
     __nv_bfloat16 *dq, *dk, *dv;
@@ -84,8 +94,10 @@ __device__ __forceinline__ uint32_t bwd_setup(uint32_t smem_base, uint8_t *smem_
             mbar_init(bar0 + 8 * (C::B_FULL + s), 1);
             mbar_init(bar0 + 8 * (C::B_EMPTY + s), 1);
         }
-        mbar_init(bar0 + 8 * C::B_SDP, 1);
-        mbar_init(bar0 + 8 * C::B_PDS, 256);
+        mbar_init(bar0 + 8 * C::B_S, 1);
+        mbar_init(bar0 + 8 * C::B_DP, 1);
+        mbar_init(bar0 + 8 * C::B_P, 8);
+        mbar_init(bar0 + 8 * C::B_DS, 8);
         mbar_init(bar0 + 8 * C::B_ACC, 1);
         fence_mbar_init();
     }
@@ -139,6 +151,49 @@ __device__ __forceinline__ void store_acc(uint32_t tacc, __nv_bfloat16 *grow, in
             }
         }
     }
+}
+
+constexpr int BWD_EMU_PAIRS_OF_4 = 1;  // pairs per group of 4 whose exponentials avoid the MUFU
+
+// p = 2^x for a pair, through the MUFU or the FMA-pipe polynomial depending on the pair's position
+__device__ __forceinline__ void exp2_pair(f32x2 x2, int pair_index, float &p0, float &p1)
+{
+    if (pair_index % 4 < BWD_EMU_PAIRS_OF_4) {
+        exp2_poly2(x2, p0, p1);
+    } else {
+        float x0, x1;
+        unpack2(x2, x0, x1);
+        p0 = ex2(x0);
+        p1 = ex2(x1);
+    }
+}
+
+__device__ __forceinline__ void tmem_st_x8(uint32_t taddr, const uint32_t (&r)[8])
+{
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr), "r"(r[0]),
+                 "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                 : "memory");
+}
+
+// Loads 64 consecutive float32 columns of this thread's TMEM lane.
+__device__ __forceinline__ void tmem_ld_64(uint32_t taddr, float (&v)[64])
+{
+#pragma unroll
+    for (int ch = 0; ch < 2; ch++) {
+        uint32_t u[32];
+        tmem_ld_32x32b_x32(taddr + ch * 32, u);
+#pragma unroll
+        for (int x = 0; x < 32; x++) v[ch * 32 + x] = __uint_as_float(u[x]);
+    }
+    tmem_wait_ld();
+}
+
+// After this warp's TMEM stores (or loads) are complete: one arrival per warp on `bar`.
+__device__ __forceinline__ void warp_arrive(uint32_t bar, int lane)
+{
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -198,39 +253,55 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
             constexpr uint32_t IDESC_SS = idesc_bf16_f32(128, 128, 0, 0);
             constexpr uint32_t IDESC_TS = idesc_bf16_f32(128, HD, 0, 1);
             const uint32_t ka = smem_base + C::OFF_RES0, va = smem_base + C::OFF_RES1;
-            bool ok = mbar_wait(BAR(C::B_RES), 0, abort_flag, p.status, WB_RES);
-            for (int i = 0; i < n && ok; i++) {
-                const int st = i % C::STAGES;
-                const uint32_t ph = (i / C::STAGES) & 1;
-                const uint32_t qa = smem_base + C::OFF_STAGE + st * C::STAGE_BYTES;
-                const uint32_t doa = qa + C::TILE_BYTES;
-                ok = ok && mbar_wait(BAR(C::B_FULL + st), ph, abort_flag, p.status, WB_FULL);
-                tc_fence_after();
-                const uint32_t k_lo = desc_lo(ka, 16), v_lo = desc_lo(va, 16);
-                const uint32_t q_lo = desc_lo(qa, 16), do_lo = desc_lo(doa, 16);
-                const uint32_t qmn_lo = desc_lo(qa, C::SUB_BYTES), domn_lo = desc_lo(doa, C::SUB_BYTES);
+            const uint32_t k_lo = desc_lo(ka, 16), v_lo = desc_lo(va, 16);
+            auto stage_addr = [&](int i) { return smem_base + C::OFF_STAGE + (i % C::STAGES) * C::STAGE_BYTES; };
+            auto issue_st = [&](int i) {  // S^T = K Q^T
+                const uint32_t q_lo = desc_lo(stage_addr(i), 16);
 #pragma unroll
-                for (int ks = 0; ks < HD / 16; ks++) {  // S^T = K Q^T
+                for (int ks = 0; ks < HD / 16; ks++) {
                     const uint32_t o16 = ((ks / 4) * C::SUB_BYTES + (ks % 4) * 32) >> 4;
                     mma_ss_lo(tmem + C::T_S, k_lo + o16, q_lo + o16, IDESC_SS, ks > 0);
                 }
+                tc_commit_elect(BAR(C::B_S));
+            };
+            auto issue_dpt = [&](int i) {  // dP^T = V dO^T
+                const uint32_t do_lo = desc_lo(stage_addr(i) + C::TILE_BYTES, 16);
 #pragma unroll
-                for (int ks = 0; ks < HD / 16; ks++) {  // dP^T = V dO^T
+                for (int ks = 0; ks < HD / 16; ks++) {
                     const uint32_t o16 = ((ks / 4) * C::SUB_BYTES + (ks % 4) * 32) >> 4;
                     mma_ss_lo(tmem + C::T_DP, v_lo + o16, do_lo + o16, IDESC_SS, ks > 0);
                 }
-                tc_commit_elect(BAR(C::B_SDP));
-                ok = ok && mbar_wait(BAR(C::B_PDS), i & 1, abort_flag, p.status, WB_PDS);
+                tc_commit_elect(BAR(C::B_DP));
+            };
+            bool ok = mbar_wait(BAR(C::B_RES), 0, abort_flag, p.status, WB_RES);
+            ok = ok && mbar_wait(BAR(C::B_FULL + 0), 0, abort_flag, p.status, WB_FULL);
+            tc_fence_after();
+            issue_st(0);
+            issue_dpt(0);
+            for (int i = 0; i < n && ok; i++) {
+                const int st = i % C::STAGES;
+                const uint32_t domn_lo = desc_lo(stage_addr(i) + C::TILE_BYTES, C::SUB_BYTES);
+                const uint32_t qmn_lo = desc_lo(stage_addr(i), C::SUB_BYTES);
+                ok = ok && mbar_wait(BAR(C::B_P), i & 1, abort_flag, p.status, WB_P);
                 tc_fence_after();
 #pragma unroll
                 for (int ks = 0; ks < 8; ks++)  // dV += P^T dO
                     mma_ts_lo(tmem + C::T_ACC0, tmem + C::T_S + ks * 8, domn_lo + ks * (2048 >> 4), IDESC_TS,
                               (i > 0 || ks > 0) ? 1u : 0u);
+                if (i + 1 < n) {
+                    ok = ok && mbar_wait(BAR(C::B_FULL + (i + 1) % C::STAGES), ((i + 1) / C::STAGES) & 1, abort_flag,
+                                         p.status, WB_FULL);
+                    tc_fence_after();
+                    issue_st(i + 1);  // overwrites P^T(i): ordered after dV(i) by issue order
+                }
+                ok = ok && mbar_wait(BAR(C::B_DS), i & 1, abort_flag, p.status, WB_DS);
+                tc_fence_after();
 #pragma unroll
                 for (int ks = 0; ks < 8; ks++)  // dK += dS^T Q
                     mma_ts_lo(tmem + C::T_ACC1, tmem + C::T_DP + ks * 8, qmn_lo + ks * (2048 >> 4), IDESC_TS,
                               (i > 0 || ks > 0) ? 1u : 0u);
                 tc_commit_elect(BAR(C::B_EMPTY + st));
+                if (i + 1 < n) issue_dpt(i + 1);  // overwrites dS^T(i): ordered after dK(i)
             }
             tc_commit_elect(BAR(C::B_ACC));
         }
@@ -256,57 +327,62 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
                 else
                     rv[threadIdx.x] = qrow < p.lq ? delta_g[qrow] : 0.f;
             }
-            ok = ok && mbar_wait(BAR(C::B_SDP), i & 1, abort_flag, p.status, WB_SDP);
+            // ---- phase 1: P^T = exp2(S^T * c - lse2), bf16 into TMEM for dV += P^T dO
+            ok = ok && mbar_wait(BAR(C::B_S), i & 1, abort_flag, p.status, WB_S);
             tc_fence_after();
-            float s[64], dp[64];
-#pragma unroll
-            for (int ch = 0; ch < 2; ch++) {
-                uint32_t u[32], w[32];
-                tmem_ld_32x32b_x32(t_s + h * 64 + ch * 32, u);
-                tmem_ld_32x32b_x32(t_dp + h * 64 + ch * 32, w);
-#pragma unroll
-                for (int x = 0; x < 32; x++) {
-                    s[ch * 32 + x] = __uint_as_float(u[x]);
-                    dp[ch * 32 + x] = __uint_as_float(w[x]);
-                }
-            }
-            tmem_wait_ld();
-            // Every thread has read its scores (the bf16 results overwrite columns another thread of
-            // the same lane still needs) and the lse/delta vectors are visible.
+            float pv[64];
+            tmem_ld_64(t_s + h * 64, pv);
+            // Every thread has read its scores (the bf16 P^T overwrites columns another thread of the
+            // same lane still needs) and the lse/delta vectors are visible.
             named_bar_sync(1, 256);
             const bool need_mask = p.causal && (k0 + 127 > q0 + off);
+            const f32x2 c2 = pack2(c, c);
 #pragma unroll
             for (int ch = 0; ch < 4; ch++) {
-                uint32_t pk[8], dk_[8];
+                uint32_t pk[8];
 #pragma unroll
                 for (int x = 0; x < 8; x++) {
-                    float pv[2], dv_[2];
-#pragma unroll
-                    for (int e = 0; e < 2; e++) {
-                        const int cc = ch * 16 + 2 * x + e;
-                        const int qq = h * 64 + cc;
-                        float pe = ex2(fmaf(s[cc], c, -rv[qq]));
-                        if (need_mask && key > q0 + qq + off) pe = 0.f;
-                        pv[e] = pe;
-                        dv_[e] = pe * (dp[cc] - rv[128 + qq]);
+                    const int cc = ch * 16 + 2 * x;
+                    const int qq = h * 64 + cc;
+                    const float2 l2 = *reinterpret_cast<const float2 *>(&rv[qq]);
+                    const f32x2 x2 = fma2(pack2(pv[cc], pv[cc + 1]), c2, pack2(-l2.x, -l2.y));
+                    float p0, p1;
+                    exp2_pair(x2, x, p0, p1);
+                    if (need_mask) {
+                        if (key > q0 + qq + off) p0 = 0.f;
+                        if (key > q0 + qq + 1 + off) p1 = 0.f;
                     }
-                    pk[x] = pack_bf16(pv[0], pv[1]);
-                    dk_[x] = pack_bf16(dv_[0], dv_[1]);
+                    pv[cc] = p0;
+                    pv[cc + 1] = p1;
+                    pk[x] = pack_bf16(p0, p1);
                 }
-                // 16 score columns -> 8 packed columns
-                asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(
-                                 t_s + h * 32 + ch * 8),
-                             "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3]), "r"(pk[4]), "r"(pk[5]), "r"(pk[6]), "r"(pk[7])
-                             : "memory");
-                asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(
-                                 t_dp + h * 32 + ch * 8),
-                             "r"(dk_[0]), "r"(dk_[1]), "r"(dk_[2]), "r"(dk_[3]), "r"(dk_[4]), "r"(dk_[5]), "r"(dk_[6]),
-                             "r"(dk_[7])
-                             : "memory");
+                tmem_st_x8(t_s + h * 32 + ch * 8, pk);  // 16 score columns -> 8 packed columns
             }
             tmem_wait_st();
-            tc_fence_before();
-            mbar_arrive(BAR(C::B_PDS));
+            warp_arrive(BAR(C::B_P), lane);
+
+            // ---- phase 2: dS^T = P^T * (dP^T - delta), bf16 into TMEM for dK += dS^T Q
+            ok = ok && mbar_wait(BAR(C::B_DP), i & 1, abort_flag, p.status, WB_DP);
+            tc_fence_after();
+            float dp[64];
+            tmem_ld_64(t_dp + h * 64, dp);
+            named_bar_sync(2, 256);  // all of dP^T is read before any thread overwrites it with dS^T
+#pragma unroll
+            for (int ch = 0; ch < 4; ch++) {
+                uint32_t pk[8];
+#pragma unroll
+                for (int x = 0; x < 8; x++) {
+                    const int cc = ch * 16 + 2 * x;
+                    const float2 d2 = *reinterpret_cast<const float2 *>(&rv[128 + h * 64 + cc]);
+                    const f32x2 ds2 = mul2(pack2(pv[cc], pv[cc + 1]), sub2(pack2(dp[cc], dp[cc + 1]), pack2(d2.x, d2.y)));
+                    float d0, d1;
+                    unpack2(ds2, d0, d1);
+                    pk[x] = pack_bf16(d0, d1);
+                }
+                tmem_st_x8(t_dp + h * 32 + ch * 8, pk);
+            }
+            tmem_wait_st();
+            warp_arrive(BAR(C::B_DS), lane);
         }
         ok = ok && mbar_wait(BAR(C::B_ACC), 0, abort_flag, p.status, WB_ACC);
         tc_fence_after();
@@ -375,35 +451,49 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
             constexpr uint32_t IDESC_SS = idesc_bf16_f32(128, 128, 0, 0);
             constexpr uint32_t IDESC_TS = idesc_bf16_f32(128, HD, 0, 1);
             const uint32_t qa = smem_base + C::OFF_RES0, doa = smem_base + C::OFF_RES1;
-            bool ok = mbar_wait(BAR(C::B_RES), 0, abort_flag, p.status, WB_RES);
-            for (int j = 0; j < n && ok; j++) {
-                const int st = j % C::STAGES;
-                const uint32_t ph = (j / C::STAGES) & 1;
-                const uint32_t ka = smem_base + C::OFF_STAGE + st * C::STAGE_BYTES;
-                const uint32_t va = ka + C::TILE_BYTES;
-                ok = ok && mbar_wait(BAR(C::B_FULL + st), ph, abort_flag, p.status, WB_FULL);
-                tc_fence_after();
-                const uint32_t q_lo = desc_lo(qa, 16), do_lo = desc_lo(doa, 16);
-                const uint32_t k_lo = desc_lo(ka, 16), v_lo = desc_lo(va, 16);
-                const uint32_t kmn_lo = desc_lo(ka, C::SUB_BYTES);
+            const uint32_t q_lo = desc_lo(qa, 16), do_lo = desc_lo(doa, 16);
+            auto stage_addr = [&](int j) { return smem_base + C::OFF_STAGE + (j % C::STAGES) * C::STAGE_BYTES; };
+            auto issue_s = [&](int j) {  // S = Q K^T
+                const uint32_t k_lo = desc_lo(stage_addr(j), 16);
 #pragma unroll
-                for (int ks = 0; ks < HD / 16; ks++) {  // S = Q K^T
+                for (int ks = 0; ks < HD / 16; ks++) {
                     const uint32_t o16 = ((ks / 4) * C::SUB_BYTES + (ks % 4) * 32) >> 4;
                     mma_ss_lo(tmem + C::T_S, q_lo + o16, k_lo + o16, IDESC_SS, ks > 0);
                 }
+                tc_commit_elect(BAR(C::B_S));
+            };
+            auto issue_dp = [&](int j) {  // dP = dO V^T
+                const uint32_t v_lo = desc_lo(stage_addr(j) + C::TILE_BYTES, 16);
 #pragma unroll
-                for (int ks = 0; ks < HD / 16; ks++) {  // dP = dO V^T
+                for (int ks = 0; ks < HD / 16; ks++) {
                     const uint32_t o16 = ((ks / 4) * C::SUB_BYTES + (ks % 4) * 32) >> 4;
                     mma_ss_lo(tmem + C::T_DP, do_lo + o16, v_lo + o16, IDESC_SS, ks > 0);
                 }
-                tc_commit_elect(BAR(C::B_SDP));
-                ok = ok && mbar_wait(BAR(C::B_PDS), j & 1, abort_flag, p.status, WB_PDS);
+                tc_commit_elect(BAR(C::B_DP));
+            };
+            bool ok = mbar_wait(BAR(C::B_RES), 0, abort_flag, p.status, WB_RES);
+            ok = ok && mbar_wait(BAR(C::B_FULL + 0), 0, abort_flag, p.status, WB_FULL);
+            tc_fence_after();
+            issue_s(0);
+            issue_dp(0);
+            for (int j = 0; j < n && ok; j++) {
+                const int st = j % C::STAGES;
+                const uint32_t kmn_lo = desc_lo(stage_addr(j), C::SUB_BYTES);
+                if (j + 1 < n) {
+                    ok = ok && mbar_wait(BAR(C::B_FULL + (j + 1) % C::STAGES), ((j + 1) / C::STAGES) & 1, abort_flag,
+                                         p.status, WB_FULL);
+                    ok = ok && mbar_wait(BAR(C::B_P), j & 1, abort_flag, p.status, WB_P);  // S(j) has been read
+                    tc_fence_after();
+                    issue_s(j + 1);
+                }
+                ok = ok && mbar_wait(BAR(C::B_DS), j & 1, abort_flag, p.status, WB_DS);
                 tc_fence_after();
 #pragma unroll
                 for (int ks = 0; ks < 8; ks++)  // dQ += dS K
                     mma_ts_lo(tmem + C::T_ACC0, tmem + C::T_DP + ks * 8, kmn_lo + ks * (2048 >> 4), IDESC_TS,
                               (j > 0 || ks > 0) ? 1u : 0u);
                 tc_commit_elect(BAR(C::B_EMPTY + st));
+                if (j + 1 < n) issue_dp(j + 1);  // overwrites dS(j): ordered after dQ(j)
             }
             tc_commit_elect(BAR(C::B_ACC));
         }
@@ -422,48 +512,49 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
         const int limit_tile = p.causal ? min(p.lk - 1, q0 + off) : p.lk - 1;
         bool ok = true;
         for (int j = 0; j < n; j++) {
-            ok = ok && mbar_wait(BAR(C::B_SDP), j & 1, abort_flag, p.status, WB_SDP);
+            // ---- phase 1: P = exp2(S * c - lse2) in registers; S is released as soon as it is read
+            ok = ok && mbar_wait(BAR(C::B_S), j & 1, abort_flag, p.status, WB_S);
             tc_fence_after();
-            float s[64], dp[64];
-#pragma unroll
-            for (int ch = 0; ch < 2; ch++) {
-                uint32_t u[32], w[32];
-                tmem_ld_32x32b_x32(t_s + h * 64 + ch * 32, u);
-                tmem_ld_32x32b_x32(t_dp + h * 64 + ch * 32, w);
-#pragma unroll
-                for (int x = 0; x < 32; x++) {
-                    s[ch * 32 + x] = __uint_as_float(u[x]);
-                    dp[ch * 32 + x] = __uint_as_float(w[x]);
-                }
-            }
-            tmem_wait_ld();
-            named_bar_sync(1, 256);  // all dP columns are read before any thread overwrites them with dS
+            float pv[64];
+            tmem_ld_64(t_s + h * 64, pv);
+            warp_arrive(BAR(C::B_P), lane);
             const bool need_mask = j * 128 + 127 > limit_tile;
             const int kbase = j * 128 + h * 64;
+            const f32x2 c2 = pack2(c, c), nl2 = pack2(-lse2, -lse2);
+#pragma unroll
+            for (int x = 0; x < 32; x++) {
+                const f32x2 x2 = fma2(pack2(pv[2 * x], pv[2 * x + 1]), c2, nl2);
+                float p0, p1;
+                exp2_pair(x2, x, p0, p1);
+                if (need_mask) {
+                    if (kbase + 2 * x > limit_row) p0 = 0.f;
+                    if (kbase + 2 * x + 1 > limit_row) p1 = 0.f;
+                }
+                pv[2 * x] = p0;
+                pv[2 * x + 1] = p1;
+            }
+            // ---- phase 2: dS = P * (dP - delta), bf16 into TMEM for dQ += dS K
+            ok = ok && mbar_wait(BAR(C::B_DP), j & 1, abort_flag, p.status, WB_DP);
+            tc_fence_after();
+            float dp[64];
+            tmem_ld_64(t_dp + h * 64, dp);
+            named_bar_sync(1, 256);  // all of dP is read before any thread overwrites it with dS
+            const f32x2 dl2 = pack2(dl, dl);
 #pragma unroll
             for (int ch = 0; ch < 4; ch++) {
-                uint32_t dk_[8];
+                uint32_t pk[8];
 #pragma unroll
                 for (int x = 0; x < 8; x++) {
-                    float dv_[2];
-#pragma unroll
-                    for (int e = 0; e < 2; e++) {
-                        const int cc = ch * 16 + 2 * x + e;
-                        float pe = ex2(fmaf(s[cc], c, -lse2));
-                        if (need_mask && kbase + cc > limit_row) pe = 0.f;
-                        dv_[e] = pe * (dp[cc] - dl);
-                    }
-                    dk_[x] = pack_bf16(dv_[0], dv_[1]);
+                    const int cc = ch * 16 + 2 * x;
+                    const f32x2 ds2 = mul2(pack2(pv[cc], pv[cc + 1]), sub2(pack2(dp[cc], dp[cc + 1]), dl2));
+                    float d0, d1;
+                    unpack2(ds2, d0, d1);
+                    pk[x] = pack_bf16(d0, d1);
                 }
-                asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(
-                                 t_dp + h * 32 + ch * 8),
-                             "r"(dk_[0]), "r"(dk_[1]), "r"(dk_[2]), "r"(dk_[3]), "r"(dk_[4]), "r"(dk_[5]), "r"(dk_[6]),
-                             "r"(dk_[7])
-                             : "memory");
+                tmem_st_x8(t_dp + h * 32 + ch * 8, pk);
             }
             tmem_wait_st();
-            tc_fence_before();
-            mbar_arrive(BAR(C::B_PDS));
+            warp_arrive(BAR(C::B_DS), lane);
         }
         ok = ok && mbar_wait(BAR(C::B_ACC), 0, abort_flag, p.status, WB_ACC);
         tc_fence_after();

@@ -18,6 +18,7 @@
 // which after the first tiles is rare. Causal tiles above the diagonal are never loaded or
 // multiplied; only tiles crossed by the diagonal (or by the end of the key axis) pay for a mask.
 #include <math.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 #include "kernels.cuh"
@@ -33,29 +34,6 @@ constexpr int FWD_THREADS = 384;
 constexpr float LOG2E_F = 1.4426950408889634f;
 constexpr float LN2_F = 0.6931471805599453f;
 constexpr float RESCALE_THRESHOLD = 8.0f;  // log2 units
-constexpr int EMU_PAIRS_OF_4 = 1;          // pairs per group of 4 pairs whose exponentials avoid the MUFU
-
-// 2^x for a pair of x <= ~8 on the FMA/ALU pipes (packed float32 pairs): round-to-nearest split
-// x = n + f, f in [-0.5, 0.5], a cubic for 2^f (relative error 7.5e-5, far below bf16 resolution) and
-// an exponent-field add for 2^n. Inputs below -125 (masked scores are -inf) are clamped and come out
-// as ~2^-125, i.e. zero in bf16.
-__device__ __forceinline__ void exp2_poly2(f32x2 x2, float &p0, float &p1)
-{
-    float x0, x1;
-    unpack2(x2, x0, x1);
-    x2 = pack2(fmaxf(x0, -125.f), fmaxf(x1, -125.f));
-    const f32x2 magic = pack2(12582912.f, 12582912.f);  // 1.5 * 2^23: integer part -> low mantissa bits
-    const f32x2 xr = add2(x2, magic);
-    const f32x2 f = sub2(x2, sub2(xr, magic));
-    f32x2 pl = fma2(pack2(0.05517167f, 0.05517167f), f, pack2(0.24261112f, 0.24261112f));
-    pl = fma2(pl, f, pack2(0.69326099f, 0.69326099f));
-    pl = fma2(pl, f, pack2(0.99992807f, 0.99992807f));
-    float r0, r1, q0, q1;
-    unpack2(xr, r0, r1);
-    unpack2(pl, q0, q1);
-    p0 = __int_as_float(__float_as_int(q0) + (__float_as_int(r0) << 23));
-    p1 = __int_as_float(__float_as_int(q1) + (__float_as_int(r1) << 23));
-}
 
 template <int HD>
 struct FwdCfg {
@@ -87,7 +65,9 @@ struct FwdParams {
     DeviceStatus *status;
 };
 
-template <int HD>
+// EMU: of every 4 pairs of exponentials, how many are evaluated as a polynomial on the FMA pipe
+// instead of the MUFU (0..4).
+template <int HD, int EMU>
 __global__ void __launch_bounds__(FWD_THREADS, 1)
     sm100_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                      const __grid_constant__ CUtensorMap tm_v, const FwdParams p)
@@ -346,7 +326,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
                     for (int i = 0; i < 16; i++) {
                         const f32x2 x2 = fma2(pack2(s[ch * 32 + 2 * i], s[ch * 32 + 2 * i + 1]), c2, negm2);
                         float p0, p1;
-                        if (i % 4 < EMU_PAIRS_OF_4) {  // polynomial on the FMA pipe
+                        if (i % 4 < EMU) {  // polynomial on the FMA pipe
                             exp2_poly2(x2, p0, p1);
                         } else {                        // MUFU
                             float x0, x1;
@@ -403,7 +383,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
     if (warp == 10) tmem_dealloc(tmem, 512);
 }
 
-template <int HD>
+template <int HD, int EMU>
 int launch(const AttnArgs &a, DeviceState *st, cudaStream_t s)
 {
     using C = FwdCfg<HD>;
@@ -420,7 +400,7 @@ int launch(const AttnArgs &a, DeviceState *st, cudaStream_t s)
     p.causal = a.causal;
     p.scale_log2 = a.scale * LOG2E_F;
     p.status = st->status;
-    auto kern = sm100_fwd_kernel<HD>;
+    auto kern = sm100_fwd_kernel<HD, EMU>;
     EMBER_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
     dim3 grid(a.bh, (a.lq + 255) / 256);
     kern<<<grid, FWD_THREADS, C::SMEM_BYTES, s>>>(tq, tk, tv, p);
@@ -441,9 +421,29 @@ bool sm100_fwd_supported(const AttnArgs &a)
     return (bits & 15) == 0;
 }
 
+// Debugging knob: EMBER_FWD_EMU=0..2 overrides the share of polynomial exponentials (read once).
+static int fwd_emu_setting()
+{
+    static int v = -1;
+    if (v < 0) {
+        const char *e = getenv("EMBER_FWD_EMU");
+        v = e ? atoi(e) : 1;
+        if (v < 0 || v > 2) v = 1;
+    }
+    return v;
+}
+
 int sm100_attention_fwd(const AttnArgs &a, DeviceState *st, cudaStream_t s)
 {
-    return a.d == 128 ? launch<128>(a, st, s) : launch<64>(a, st, s);
+    const int emu = fwd_emu_setting();
+    if (a.d == 128) {
+        if (emu == 0) return launch<128, 0>(a, st, s);
+        if (emu == 2) return launch<128, 2>(a, st, s);
+        return launch<128, 1>(a, st, s);
+    }
+    if (emu == 0) return launch<64, 0>(a, st, s);
+    if (emu == 2) return launch<64, 2>(a, st, s);
+    return launch<64, 1>(a, st, s);
 }
 
 }  // namespace ember

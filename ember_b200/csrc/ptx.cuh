@@ -369,6 +369,28 @@ __device__ __forceinline__ float ex2(float x)
     return y;
 }
 
+// 2^x for a pair of x <= ~8 on the FMA/ALU pipes (packed float32 pairs): round-to-nearest split
+// x = n + f, f in [-0.5, 0.5], a cubic for 2^f (relative error 7.5e-5, far below bf16 resolution) and
+// an exponent-field add for 2^n. Inputs below -125 (masked scores are -inf) are clamped and come out
+// as ~2^-125, i.e. zero in bf16.
+__device__ __forceinline__ void exp2_poly2(f32x2 x2, float &p0, float &p1)
+{
+    float x0, x1;
+    unpack2(x2, x0, x1);
+    x2 = pack2(fmaxf(x0, -125.f), fmaxf(x1, -125.f));
+    const f32x2 magic = pack2(12582912.f, 12582912.f);  // 1.5 * 2^23: integer part -> low mantissa bits
+    const f32x2 xr = add2(x2, magic);
+    const f32x2 f = sub2(x2, sub2(xr, magic));
+    f32x2 pl = fma2(pack2(0.05517167f, 0.05517167f), f, pack2(0.24261112f, 0.24261112f));
+    pl = fma2(pl, f, pack2(0.69326099f, 0.69326099f));
+    pl = fma2(pl, f, pack2(0.99992807f, 0.99992807f));
+    float r0, r1, q0, q1;
+    unpack2(xr, r0, r1);
+    unpack2(pl, q0, q1);
+    p0 = __int_as_float(__float_as_int(q0) + (__float_as_int(r0) << 23));
+    p1 = __int_as_float(__float_as_int(q1) + (__float_as_int(r1) << 23));
+}
+
 }  // namespace ptx
 
 // Host side: building TMA tensor maps through the driver entry point (no link against libcuda).
