@@ -45,25 +45,33 @@ struct BwdCfg {
     static constexpr int NSUB = HD / 64;
     static constexpr int SUB_BYTES = 128 * 128;
     static constexpr int TILE_BYTES = NSUB * SUB_BYTES;
-    static constexpr int STAGES = 2;
+    // Two rings of streamed tiles. Ring A holds the operand that stays in use until the END of an
+    // iteration (Q in the dK/dV kernel: last read by dK; K in the dQ kernel: last read by dQ), so its
+    // next-but-one tile can only start loading late; three buffers keep that TMA latency off the
+    // critical path. Ring B (dO, resp. V) is released in the first half of an iteration; two suffice.
+    static constexpr int NA = 3, NB = 2;
     static constexpr int OFF_RES0 = 0;                  // resident tile 0 (K, or Q)
     static constexpr int OFF_RES1 = TILE_BYTES;         // resident tile 1 (V, or dO)
-    static constexpr int OFF_STAGE = 2 * TILE_BYTES;    // each stage: two tiles back to back
-    static constexpr int STAGE_BYTES = 2 * TILE_BYTES;
-    static constexpr int OFF_BAR = OFF_STAGE + STAGES * STAGE_BYTES;
-    static constexpr int OFF_ROWVEC = OFF_BAR + 256;    // [2 buffers][2 vectors][128] floats
-    static constexpr int SMEM_BYTES = OFF_ROWVEC + 2048 + 1024;
+    static constexpr int OFF_A = 2 * TILE_BYTES;
+    static constexpr int OFF_B = OFF_A + NA * TILE_BYTES;
+    static constexpr int OFF_BAR = OFF_B + NB * TILE_BYTES;
+    static constexpr int OFF_ROWVEC = OFF_BAR + 144;    // [2 buffers][2 vectors][128] floats
+    static constexpr int USED_BYTES = OFF_ROWVEC + 2048;
+    // 7 tiles of 32 KB leave 880 bytes below the 227 KB limit at HD = 128: that is the room for
+    // rounding the dynamic shared memory base up to 1024 bytes (the kernel checks that it fits).
+    static constexpr int SMEM_BYTES = HD == 128 ? 232448 : USED_BYTES + 1024;
     static constexpr int T_S = 0, T_DP = 128, T_ACC0 = 256, T_ACC1 = 256 + HD;
     // barrier indices
-    static constexpr int B_RES = 0, B_FULL = 1, B_EMPTY = B_FULL + STAGES,
-                         B_S = B_EMPTY + STAGES,   // S (or S^T) of the current tile is in TMEM
+    static constexpr int B_RES = 0, B_FULLA = 1, B_EMPTYA = B_FULLA + NA, B_FULLB = B_EMPTYA + NA,
+                         B_EMPTYB = B_FULLB + NB,
+                         B_S = B_EMPTYB + NB,      // S (or S^T) of the current tile is in TMEM
                          B_DP = B_S + 1,           // dP (or dP^T) is in TMEM
                          B_P = B_DP + 1,           // dK/dV: P^T written; dQ: S has been read (8 warp arrivals)
                          B_DS = B_P + 1,           // dS (or dS^T) written (8 warp arrivals)
                          B_ACC = B_DS + 1, NUM_BARS = B_ACC + 1;
 };
 
-enum { WB_RES = 101, WB_FULL, WB_EMPTY, WB_S, WB_DP, WB_P, WB_DS, WB_ACC };
+enum { WB_RES = 101, WB_FULL, WB_EMPTY, WB_S, WB_DP, WB_P, WB_DS, WB_ACC, WB_SMEM };
 
 struct BwdParams {
     __nv_bfloat16 *dq, *dk, *dv;
@@ -90,9 +98,13 @@ __device__ __forceinline__ uint32_t bwd_setup(uint32_t smem_base, uint8_t *smem_
     if (threadIdx.x == 0) {
         *abort_flag = 0;
         mbar_init(bar0 + 8 * C::B_RES, 1);
-        for (int s = 0; s < C::STAGES; s++) {
-            mbar_init(bar0 + 8 * (C::B_FULL + s), 1);
-            mbar_init(bar0 + 8 * (C::B_EMPTY + s), 1);
+        for (int s = 0; s < C::NA; s++) {
+            mbar_init(bar0 + 8 * (C::B_FULLA + s), 1);
+            mbar_init(bar0 + 8 * (C::B_EMPTYA + s), 1);
+        }
+        for (int s = 0; s < C::NB; s++) {
+            mbar_init(bar0 + 8 * (C::B_FULLB + s), 1);
+            mbar_init(bar0 + 8 * (C::B_EMPTYB + s), 1);
         }
         mbar_init(bar0 + 8 * C::B_S, 1);
         mbar_init(bar0 + 8 * C::B_DP, 1);
@@ -119,13 +131,33 @@ __device__ __forceinline__ uint32_t bwd_setup(uint32_t smem_base, uint8_t *smem_
 
 // Bounded drain of the producer's outstanding copies before the CTA may exit.
 template <typename C>
-__device__ __forceinline__ void drain_copies(uint32_t bar0, int issued)
+__device__ __forceinline__ void drain_copies(uint32_t bar0, int issued_a, int issued_b)
 {
     const long long t0 = clock64();
-    for (int j = max(0, issued - C::STAGES); j < issued; j++)
-        while (!mbar_try_wait(bar0 + 8 * (C::B_FULL + j % C::STAGES), (j / C::STAGES) & 1) &&
+    for (int j = max(0, issued_a - C::NA); j < issued_a; j++)
+        while (!mbar_try_wait(bar0 + 8 * (C::B_FULLA + j % C::NA), (j / C::NA) & 1) &&
+               clock64() - t0 < kWaitLimitCycles) {}
+    for (int j = max(0, issued_b - C::NB); j < issued_b; j++)
+        while (!mbar_try_wait(bar0 + 8 * (C::B_FULLB + j % C::NB), (j / C::NB) & 1) &&
                clock64() - t0 < kWaitLimitCycles) {}
     while (!mbar_try_wait(bar0 + 8 * C::B_RES, 0) && clock64() - t0 < kWaitLimitCycles) {}
+}
+
+// The kernels round the dynamic shared memory base up to 1024 bytes; true when the rounded layout
+// still fits in what was allocated. Otherwise the CTA records the fact and returns at once (every
+// thread takes the same decision, before any barrier exists).
+template <typename C>
+__device__ __forceinline__ bool smem_layout_fits(uint32_t raw_base, uint32_t aligned_base, DeviceStatus *status)
+{
+    uint32_t dyn;
+    asm("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn));
+    if (aligned_base + C::USED_BYTES <= raw_base + dyn) return true;
+    if (threadIdx.x == 0 && atomicCAS(&status->code, 0, EMBER_ERR_UNSUPPORTED) == 0) {
+        status->where = WB_SMEM;
+        status->block = blockIdx.x;
+        status->extra = (int)(aligned_base - raw_base);
+    }
+    return false;
 }
 
 // acc (TMEM, fp32, 128 x HD) -> bf16 rows in global memory, times `mul`; thread (r, h) stores
@@ -206,9 +238,10 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
                           const BwdParams p)
 {
     using C = BwdCfg<HD>;
-    extern __shared__ uint8_t smem_raw[];
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    if (!smem_layout_fits<C>(smem_u32(smem_raw), smem_base, p.status)) return;
     const uint32_t bar0 = smem_base + C::OFF_BAR;
     auto BAR = [&](int i) { return bar0 + 8u * (uint32_t)i; };
     volatile int *abort_flag =
@@ -233,30 +266,34 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
                 tma_load_3d(smem_base + C::OFF_RES0 + s * C::SUB_BYTES, &tm_k, BAR(C::B_RES), s * 64, k0, bh);
                 tma_load_3d(smem_base + C::OFF_RES1 + s * C::SUB_BYTES, &tm_v, BAR(C::B_RES), s * 64, k0, bh);
             }
-            int issued = 0;
+            int issued_a = 0, issued_b = 0;
             for (int i = 0; i < n; i++) {
-                const int st = i % C::STAGES;
-                const uint32_t ph = (i / C::STAGES) & 1;
-                if (!mbar_wait(BAR(C::B_EMPTY + st), ph ^ 1, abort_flag, p.status, WB_EMPTY)) break;
-                mbar_arrive_expect_tx(BAR(C::B_FULL + st), 2 * C::TILE_BYTES);
-                const uint32_t dst = smem_base + C::OFF_STAGE + st * C::STAGE_BYTES;
+                const int sa = i % C::NA, sb = i % C::NB;
                 const int q0 = (i_begin + i) * 128;
-                for (int s = 0; s < C::NSUB; s++) {
-                    tma_load_3d(dst + s * C::SUB_BYTES, &tm_q, BAR(C::B_FULL + st), s * 64, q0, bh);
-                    tma_load_3d(dst + C::TILE_BYTES + s * C::SUB_BYTES, &tm_do, BAR(C::B_FULL + st), s * 64, q0, bh);
-                }
-                issued = i + 1;
+                if (!mbar_wait(BAR(C::B_EMPTYA + sa), ((i / C::NA) & 1) ^ 1, abort_flag, p.status, WB_EMPTY)) break;
+                mbar_arrive_expect_tx(BAR(C::B_FULLA + sa), C::TILE_BYTES);
+                for (int s = 0; s < C::NSUB; s++)
+                    tma_load_3d(smem_base + C::OFF_A + sa * C::TILE_BYTES + s * C::SUB_BYTES, &tm_q,
+                                BAR(C::B_FULLA + sa), s * 64, q0, bh);
+                issued_a = i + 1;
+                if (!mbar_wait(BAR(C::B_EMPTYB + sb), ((i / C::NB) & 1) ^ 1, abort_flag, p.status, WB_EMPTY)) break;
+                mbar_arrive_expect_tx(BAR(C::B_FULLB + sb), C::TILE_BYTES);
+                for (int s = 0; s < C::NSUB; s++)
+                    tma_load_3d(smem_base + C::OFF_B + sb * C::TILE_BYTES + s * C::SUB_BYTES, &tm_do,
+                                BAR(C::B_FULLB + sb), s * 64, q0, bh);
+                issued_b = i + 1;
             }
-            drain_copies<C>(bar0, issued);
+            drain_copies<C>(bar0, issued_a, issued_b);
         } else if (warp == 8) {  // all 32 lanes, converged; one elected lane issues
             // ---------------------------------------------------------------- MMA issue
             constexpr uint32_t IDESC_SS = idesc_bf16_f32(128, 128, 0, 0);
             constexpr uint32_t IDESC_TS = idesc_bf16_f32(128, HD, 0, 1);
             const uint32_t ka = smem_base + C::OFF_RES0, va = smem_base + C::OFF_RES1;
             const uint32_t k_lo = desc_lo(ka, 16), v_lo = desc_lo(va, 16);
-            auto stage_addr = [&](int i) { return smem_base + C::OFF_STAGE + (i % C::STAGES) * C::STAGE_BYTES; };
+            auto q_addr = [&](int i) { return smem_base + C::OFF_A + (i % C::NA) * C::TILE_BYTES; };
+            auto do_addr = [&](int i) { return smem_base + C::OFF_B + (i % C::NB) * C::TILE_BYTES; };
             auto issue_st = [&](int i) {  // S^T = K Q^T
-                const uint32_t q_lo = desc_lo(stage_addr(i), 16);
+                const uint32_t q_lo = desc_lo(q_addr(i), 16);
 #pragma unroll
                 for (int ks = 0; ks < HD / 16; ks++) {
                     const uint32_t o16 = ((ks / 4) * C::SUB_BYTES + (ks % 4) * 32) >> 4;
@@ -265,7 +302,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
                 tc_commit_elect(BAR(C::B_S));
             };
             auto issue_dpt = [&](int i) {  // dP^T = V dO^T
-                const uint32_t do_lo = desc_lo(stage_addr(i) + C::TILE_BYTES, 16);
+                const uint32_t do_lo = desc_lo(do_addr(i), 16);
 #pragma unroll
                 for (int ks = 0; ks < HD / 16; ks++) {
                     const uint32_t o16 = ((ks / 4) * C::SUB_BYTES + (ks % 4) * 32) >> 4;
@@ -274,22 +311,24 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
                 tc_commit_elect(BAR(C::B_DP));
             };
             bool ok = mbar_wait(BAR(C::B_RES), 0, abort_flag, p.status, WB_RES);
-            ok = ok && mbar_wait(BAR(C::B_FULL + 0), 0, abort_flag, p.status, WB_FULL);
+            ok = ok && mbar_wait(BAR(C::B_FULLA + 0), 0, abort_flag, p.status, WB_FULL);
             tc_fence_after();
             issue_st(0);
+            ok = ok && mbar_wait(BAR(C::B_FULLB + 0), 0, abort_flag, p.status, WB_FULL);
+            tc_fence_after();
             issue_dpt(0);
             for (int i = 0; i < n && ok; i++) {
-                const int st = i % C::STAGES;
-                const uint32_t domn_lo = desc_lo(stage_addr(i) + C::TILE_BYTES, C::SUB_BYTES);
-                const uint32_t qmn_lo = desc_lo(stage_addr(i), C::SUB_BYTES);
+                const uint32_t domn_lo = desc_lo(do_addr(i), C::SUB_BYTES);
+                const uint32_t qmn_lo = desc_lo(q_addr(i), C::SUB_BYTES);
                 ok = ok && mbar_wait(BAR(C::B_P), i & 1, abort_flag, p.status, WB_P);
                 tc_fence_after();
 #pragma unroll
                 for (int ks = 0; ks < 8; ks++)  // dV += P^T dO
                     mma_ts_lo(tmem + C::T_ACC0, tmem + C::T_S + ks * 8, domn_lo + ks * (2048 >> 4), IDESC_TS,
                               (i > 0 || ks > 0) ? 1u : 0u);
+                tc_commit_elect(BAR(C::B_EMPTYB + i % C::NB));  // dO(i) was last read by dV(i)
                 if (i + 1 < n) {
-                    ok = ok && mbar_wait(BAR(C::B_FULL + (i + 1) % C::STAGES), ((i + 1) / C::STAGES) & 1, abort_flag,
+                    ok = ok && mbar_wait(BAR(C::B_FULLA + (i + 1) % C::NA), ((i + 1) / C::NA) & 1, abort_flag,
                                          p.status, WB_FULL);
                     tc_fence_after();
                     issue_st(i + 1);  // overwrites P^T(i): ordered after dV(i) by issue order
@@ -300,8 +339,13 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
                 for (int ks = 0; ks < 8; ks++)  // dK += dS^T Q
                     mma_ts_lo(tmem + C::T_ACC1, tmem + C::T_DP + ks * 8, qmn_lo + ks * (2048 >> 4), IDESC_TS,
                               (i > 0 || ks > 0) ? 1u : 0u);
-                tc_commit_elect(BAR(C::B_EMPTY + st));
-                if (i + 1 < n) issue_dpt(i + 1);  // overwrites dS^T(i): ordered after dK(i)
+                tc_commit_elect(BAR(C::B_EMPTYA + i % C::NA));  // Q(i) was last read by dK(i)
+                if (i + 1 < n) {
+                    ok = ok && mbar_wait(BAR(C::B_FULLB + (i + 1) % C::NB), ((i + 1) / C::NB) & 1, abort_flag,
+                                         p.status, WB_FULL);
+                    tc_fence_after();
+                    issue_dpt(i + 1);  // overwrites dS^T(i): ordered after dK(i)
+                }
             }
             tc_commit_elect(BAR(C::B_ACC));
         }
@@ -317,16 +361,26 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
         const float *lse_g = p.lse + (size_t)bh * p.lq;
         const float *delta_g = p.delta + (size_t)bh * p.lq;
         bool ok = true;
+        // This thread's element of the next tile's row vectors (threads 0-127: lse, threads 128-255:
+        // delta) is fetched from global memory one tile ahead so that its latency is hidden. The load
+        // is a volatile asm (the compiler must not sink it next to its use) and its value is not
+        // touched until the next iteration (any arithmetic on it here would wait for the load).
+        const float *rowvec_src = (threadIdx.x < 128 ? lse_g : delta_g);
+        auto fetch_raw = [&](int i) -> float {
+            const int qrow = (i_begin + i) * 128 + (threadIdx.x & 127);
+            float v = 0.f;
+            if (i < n && qrow < p.lq) asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v) : "l"(rowvec_src + qrow));
+            return v;
+        };
+        float raw_next = fetch_raw(0);
         for (int i = 0; i < n; i++) {
             const int q0 = (i_begin + i) * 128;
             float *rv = rowvec + (i & 1) * 256;
             {
-                const int qrow = q0 + (threadIdx.x & 127);
-                if (threadIdx.x < 128)
-                    rv[threadIdx.x] = qrow < p.lq ? lse_g[qrow] * LOG2E_B : INFINITY;
-                else
-                    rv[threadIdx.x] = qrow < p.lq ? delta_g[qrow] : 0.f;
+                const bool in_range = q0 + (threadIdx.x & 127) < p.lq;
+                rv[threadIdx.x] = threadIdx.x < 128 ? (in_range ? -raw_next * LOG2E_B : -INFINITY) : (in_range ? raw_next : 0.f);
             }
+            raw_next = fetch_raw(i + 1);
             // ---- phase 1: P^T = exp2(S^T * c - lse2), bf16 into TMEM for dV += P^T dO
             ok = ok && mbar_wait(BAR(C::B_S), i & 1, abort_flag, p.status, WB_S);
             tc_fence_after();
@@ -335,7 +389,12 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
             // Every thread has read its scores (the bf16 P^T overwrites columns another thread of the
             // same lane still needs) and the lse/delta vectors are visible.
             named_bar_sync(1, 256);
-            const bool need_mask = p.causal && (k0 + 127 > q0 + off);
+            if (p.causal && (k0 + 127 > q0 + off)) {  // tile crossed by the diagonal: mask before the exp
+                const float masked = c > 0.f ? -INFINITY : INFINITY;
+#pragma unroll
+                for (int cc = 0; cc < 64; cc++)
+                    if (key > q0 + h * 64 + cc + off) pv[cc] = masked;
+            }
             const f32x2 c2 = pack2(c, c);
 #pragma unroll
             for (int ch = 0; ch < 4; ch++) {
@@ -344,14 +403,9 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
                 for (int x = 0; x < 8; x++) {
                     const int cc = ch * 16 + 2 * x;
                     const int qq = h * 64 + cc;
-                    const float2 l2 = *reinterpret_cast<const float2 *>(&rv[qq]);
-                    const f32x2 x2 = fma2(pack2(pv[cc], pv[cc + 1]), c2, pack2(-l2.x, -l2.y));
+                    const f32x2 x2 = fma2(pack2(pv[cc], pv[cc + 1]), c2, *reinterpret_cast<const f32x2 *>(&rv[qq]));
                     float p0, p1;
                     exp2_pair(x2, x, p0, p1);
-                    if (need_mask) {
-                        if (key > q0 + qq + off) p0 = 0.f;
-                        if (key > q0 + qq + 1 + off) p1 = 0.f;
-                    }
                     pv[cc] = p0;
                     pv[cc + 1] = p1;
                     pk[x] = pack_bf16(p0, p1);
@@ -373,8 +427,8 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
 #pragma unroll
                 for (int x = 0; x < 8; x++) {
                     const int cc = ch * 16 + 2 * x;
-                    const float2 d2 = *reinterpret_cast<const float2 *>(&rv[128 + h * 64 + cc]);
-                    const f32x2 ds2 = mul2(pack2(pv[cc], pv[cc + 1]), sub2(pack2(dp[cc], dp[cc + 1]), pack2(d2.x, d2.y)));
+                    const f32x2 ds2 = mul2(pack2(pv[cc], pv[cc + 1]),
+                                           sub2(pack2(dp[cc], dp[cc + 1]), *reinterpret_cast<const f32x2 *>(&rv[128 + h * 64 + cc])));
                     float d0, d1;
                     unpack2(ds2, d0, d1);
                     pk[x] = pack_bf16(d0, d1);
@@ -407,9 +461,10 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
                         const BwdParams p)
 {
     using C = BwdCfg<HD>;
-    extern __shared__ uint8_t smem_raw[];
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    if (!smem_layout_fits<C>(smem_u32(smem_raw), smem_base, p.status)) return;
     const uint32_t bar0 = smem_base + C::OFF_BAR;
     auto BAR = [&](int i) { return bar0 + 8u * (uint32_t)i; };
     volatile int *abort_flag =
@@ -433,28 +488,32 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
                 tma_load_3d(smem_base + C::OFF_RES0 + s * C::SUB_BYTES, &tm_q, BAR(C::B_RES), s * 64, q0, bh);
                 tma_load_3d(smem_base + C::OFF_RES1 + s * C::SUB_BYTES, &tm_do, BAR(C::B_RES), s * 64, q0, bh);
             }
-            int issued = 0;
+            int issued_a = 0, issued_b = 0;
             for (int j = 0; j < n; j++) {
-                const int st = j % C::STAGES;
-                const uint32_t ph = (j / C::STAGES) & 1;
-                if (!mbar_wait(BAR(C::B_EMPTY + st), ph ^ 1, abort_flag, p.status, WB_EMPTY)) break;
-                mbar_arrive_expect_tx(BAR(C::B_FULL + st), 2 * C::TILE_BYTES);
-                const uint32_t dst = smem_base + C::OFF_STAGE + st * C::STAGE_BYTES;
-                for (int s = 0; s < C::NSUB; s++) {
-                    tma_load_3d(dst + s * C::SUB_BYTES, &tm_k, BAR(C::B_FULL + st), s * 64, j * 128, bh);
-                    tma_load_3d(dst + C::TILE_BYTES + s * C::SUB_BYTES, &tm_v, BAR(C::B_FULL + st), s * 64, j * 128, bh);
-                }
-                issued = j + 1;
+                const int sa = j % C::NA, sb = j % C::NB;
+                if (!mbar_wait(BAR(C::B_EMPTYA + sa), ((j / C::NA) & 1) ^ 1, abort_flag, p.status, WB_EMPTY)) break;
+                mbar_arrive_expect_tx(BAR(C::B_FULLA + sa), C::TILE_BYTES);
+                for (int s = 0; s < C::NSUB; s++)
+                    tma_load_3d(smem_base + C::OFF_A + sa * C::TILE_BYTES + s * C::SUB_BYTES, &tm_k,
+                                BAR(C::B_FULLA + sa), s * 64, j * 128, bh);
+                issued_a = j + 1;
+                if (!mbar_wait(BAR(C::B_EMPTYB + sb), ((j / C::NB) & 1) ^ 1, abort_flag, p.status, WB_EMPTY)) break;
+                mbar_arrive_expect_tx(BAR(C::B_FULLB + sb), C::TILE_BYTES);
+                for (int s = 0; s < C::NSUB; s++)
+                    tma_load_3d(smem_base + C::OFF_B + sb * C::TILE_BYTES + s * C::SUB_BYTES, &tm_v,
+                                BAR(C::B_FULLB + sb), s * 64, j * 128, bh);
+                issued_b = j + 1;
             }
-            drain_copies<C>(bar0, issued);
+            drain_copies<C>(bar0, issued_a, issued_b);
         } else if (warp == 8) {  // all 32 lanes, converged; one elected lane issues
             constexpr uint32_t IDESC_SS = idesc_bf16_f32(128, 128, 0, 0);
             constexpr uint32_t IDESC_TS = idesc_bf16_f32(128, HD, 0, 1);
             const uint32_t qa = smem_base + C::OFF_RES0, doa = smem_base + C::OFF_RES1;
             const uint32_t q_lo = desc_lo(qa, 16), do_lo = desc_lo(doa, 16);
-            auto stage_addr = [&](int j) { return smem_base + C::OFF_STAGE + (j % C::STAGES) * C::STAGE_BYTES; };
+            auto k_addr = [&](int j) { return smem_base + C::OFF_A + (j % C::NA) * C::TILE_BYTES; };
+            auto v_addr = [&](int j) { return smem_base + C::OFF_B + (j % C::NB) * C::TILE_BYTES; };
             auto issue_s = [&](int j) {  // S = Q K^T
-                const uint32_t k_lo = desc_lo(stage_addr(j), 16);
+                const uint32_t k_lo = desc_lo(k_addr(j), 16);
 #pragma unroll
                 for (int ks = 0; ks < HD / 16; ks++) {
                     const uint32_t o16 = ((ks / 4) * C::SUB_BYTES + (ks % 4) * 32) >> 4;
@@ -463,24 +522,26 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
                 tc_commit_elect(BAR(C::B_S));
             };
             auto issue_dp = [&](int j) {  // dP = dO V^T
-                const uint32_t v_lo = desc_lo(stage_addr(j) + C::TILE_BYTES, 16);
+                const uint32_t v_lo = desc_lo(v_addr(j), 16);
 #pragma unroll
                 for (int ks = 0; ks < HD / 16; ks++) {
                     const uint32_t o16 = ((ks / 4) * C::SUB_BYTES + (ks % 4) * 32) >> 4;
                     mma_ss_lo(tmem + C::T_DP, do_lo + o16, v_lo + o16, IDESC_SS, ks > 0);
                 }
                 tc_commit_elect(BAR(C::B_DP));
+                tc_commit_elect(BAR(C::B_EMPTYB + j % C::NB));  // V(j) is only read by dP(j)
             };
             bool ok = mbar_wait(BAR(C::B_RES), 0, abort_flag, p.status, WB_RES);
-            ok = ok && mbar_wait(BAR(C::B_FULL + 0), 0, abort_flag, p.status, WB_FULL);
+            ok = ok && mbar_wait(BAR(C::B_FULLA + 0), 0, abort_flag, p.status, WB_FULL);
             tc_fence_after();
             issue_s(0);
+            ok = ok && mbar_wait(BAR(C::B_FULLB + 0), 0, abort_flag, p.status, WB_FULL);
+            tc_fence_after();
             issue_dp(0);
             for (int j = 0; j < n && ok; j++) {
-                const int st = j % C::STAGES;
-                const uint32_t kmn_lo = desc_lo(stage_addr(j), C::SUB_BYTES);
+                const uint32_t kmn_lo = desc_lo(k_addr(j), C::SUB_BYTES);
                 if (j + 1 < n) {
-                    ok = ok && mbar_wait(BAR(C::B_FULL + (j + 1) % C::STAGES), ((j + 1) / C::STAGES) & 1, abort_flag,
+                    ok = ok && mbar_wait(BAR(C::B_FULLA + (j + 1) % C::NA), ((j + 1) / C::NA) & 1, abort_flag,
                                          p.status, WB_FULL);
                     ok = ok && mbar_wait(BAR(C::B_P), j & 1, abort_flag, p.status, WB_P);  // S(j) has been read
                     tc_fence_after();
@@ -492,8 +553,13 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
                 for (int ks = 0; ks < 8; ks++)  // dQ += dS K
                     mma_ts_lo(tmem + C::T_ACC0, tmem + C::T_DP + ks * 8, kmn_lo + ks * (2048 >> 4), IDESC_TS,
                               (j > 0 || ks > 0) ? 1u : 0u);
-                tc_commit_elect(BAR(C::B_EMPTY + st));
-                if (j + 1 < n) issue_dp(j + 1);  // overwrites dS(j): ordered after dQ(j)
+                tc_commit_elect(BAR(C::B_EMPTYA + j % C::NA));  // K(j) was last read by dQ(j)
+                if (j + 1 < n) {
+                    ok = ok && mbar_wait(BAR(C::B_FULLB + (j + 1) % C::NB), ((j + 1) / C::NB) & 1, abort_flag,
+                                         p.status, WB_FULL);
+                    tc_fence_after();
+                    issue_dp(j + 1);  // overwrites dS(j): ordered after dQ(j)
+                }
             }
             tc_commit_elect(BAR(C::B_ACC));
         }
@@ -518,18 +584,19 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
             float pv[64];
             tmem_ld_64(t_s + h * 64, pv);
             warp_arrive(BAR(C::B_P), lane);
-            const bool need_mask = j * 128 + 127 > limit_tile;
-            const int kbase = j * 128 + h * 64;
+            if (j * 128 + 127 > limit_tile) {  // tile crossed by the diagonal or the end of the keys
+                const float masked = c > 0.f ? -INFINITY : INFINITY;
+                const int kbase = j * 128 + h * 64;
+#pragma unroll
+                for (int cc = 0; cc < 64; cc++)
+                    if (kbase + cc > limit_row) pv[cc] = masked;
+            }
             const f32x2 c2 = pack2(c, c), nl2 = pack2(-lse2, -lse2);
 #pragma unroll
             for (int x = 0; x < 32; x++) {
                 const f32x2 x2 = fma2(pack2(pv[2 * x], pv[2 * x + 1]), c2, nl2);
                 float p0, p1;
                 exp2_pair(x2, x, p0, p1);
-                if (need_mask) {
-                    if (kbase + 2 * x > limit_row) p0 = 0.f;
-                    if (kbase + 2 * x + 1 > limit_row) p1 = 0.f;
-                }
                 pv[2 * x] = p0;
                 pv[2 * x + 1] = p1;
             }
