@@ -539,20 +539,20 @@ def run_profile_case(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
-    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extra", action="store_true", help="skip the backward and decode extras at N=1")
     ap.add_argument("--profile", choices=["fwd", "bwd", "decode"], default=None,
                     help="run only a small single-kernel case (for ncu captures) and exit")
     args = ap.parse_args()
     if args.profile:
-        if args.steps == 200 and args.warmup == 10:
+        if args.steps == 100 and args.warmup == 5:
             args.steps, args.warmup = 3, 2
         run_profile_case(args)
         return
     if args.impl == "reference":
-        if args.steps == 200 and args.warmup == 10:  # defaults are sized for the GPU arm
+        if args.steps == 100 and args.warmup == 5:  # defaults are sized for the GPU arm
             args.steps, args.warmup = 5, 1
         run_reference_arm(args)
     else:

@@ -1,18 +1,25 @@
 // Prefill attention forward for sm_100a: bf16 in/out, float32 softmax and accumulation.
 //
-// One CTA owns 256 consecutive query rows of one (batch*head) as two 128-row tiles that
-// ping-pong: while the softmax warps of one tile work on their scores, the tensor core runs
-// the MMAs of the other tile.
+// One CTA owns 256 consecutive query rows of one (batch*head) as two 128-row tiles whose softmax
+// warpgroups run half a period apart, so that the tensor core always has the other tile's MMAs.
 //
 //   warps 0-3   softmax + epilogue of tile 0 (one thread per query row, row state in registers)
 //   warps 4-7   softmax + epilogue of tile 1
-//   warp  8     MMA issue (one lane): S = Q K^T and O += P V with tcgen05.mma, accumulators in TMEM
-//   warp  9     TMA producer (one lane): Q once, then K and V tiles through a 2-stage ring
-//   warp 10     TMEM allocation / release
+//   warp  8/9   MMA issue for tile 0 / tile 1 (warp-collective, one elected lane each): S = Q K^T and
+//               O += P V with tcgen05.mma, accumulators in TMEM. One issuing warp per tile, on
+//               different schedulers: an issuing warp shares its scheduler with two busy softmax
+//               warps and a single one could not keep up with both tiles.
+//   warp 10     TMA producer (one lane): Q once, then K (2-stage ring) and V (3-stage ring)
+//   warp 11     TMEM allocation / release
 //
-// Tensor memory (512 columns x 128 lanes of 32 bit): S0 [0,128) S1 [128,256) O0 [256,256+HD)
-// O1 [256+HD, 256+2HD). The bf16 probabilities P overwrite the first 64 columns of their S
-// and are read from there as the A operand of the PV MMA, so P never touches shared memory.
+// Tensor memory (512 columns x 128 lanes of 32 bit):
+//   P0 [0,64)  P1 [64,128)  S [128,256)  O0 [256,256+HD)  O1 [256+HD,256+2HD)
+// There is ONE score buffer S, used by the two tiles in turn: a softmax warpgroup copies its 128
+// scores per row into registers as soon as it is free (about 100 cycles), signals "S read", and the
+// MMA warp immediately computes the other tile's next scores into the same columns. The bf16
+// probabilities go to the tile's own P columns and are consumed from there as the A operand of the
+// PV MMA, so P never touches shared memory and the score MMAs never wait for a PV MMA: the next
+// scores of a tile are already waiting when its softmax finishes the current ones.
 // Softmax runs in the exp2 domain (scale*log2(e) folded into one FMA per score); the running
 // reference maximum is only moved, and O rescaled, when the row maximum grew by more than 2^8,
 // which after the first tiles is rare. Causal tiles above the diagonal are never loaded or
@@ -40,20 +47,29 @@ struct FwdCfg {
     static constexpr int NSUB = HD / 64;                 // 64-column (128-byte) sub-tiles per tile
     static constexpr int SUB_BYTES = 128 * 128;          // 128 rows x 128 bytes
     static constexpr int TILE_BYTES = NSUB * SUB_BYTES;  // one 128 x HD bf16 tile
-    static constexpr int STAGES = HD == 128 ? 2 : 3;
+    // K(j) is released as soon as both score MMAs of step j are issued; V(j) stays in use until the
+    // second tile's PV MMA one step later, so V gets the deeper ring.
+    static constexpr int KSTAGES = 2, VSTAGES = 3;
     static constexpr int OFF_Q = 0;
     static constexpr int OFF_K = OFF_Q + 2 * TILE_BYTES;
-    static constexpr int OFF_V = OFF_K + STAGES * TILE_BYTES;
-    static constexpr int OFF_BAR = OFF_V + STAGES * TILE_BYTES;
-    static constexpr int NUM_BARS = 1 + 4 * STAGES + 8;
-    static constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;  // barriers + misc, + alignment slack
-    static constexpr int TMEM_S = 0;
-    static constexpr int TMEM_O = 256;
+    static constexpr int OFF_V = OFF_K + KSTAGES * TILE_BYTES;
+    static constexpr int OFF_BAR = OFF_V + VSTAGES * TILE_BYTES;
+    static constexpr int USED_BYTES = OFF_BAR + 256;     // barriers + TMEM slot + abort flag
+    static constexpr int SMEM_BYTES = USED_BYTES + 1024; // + room to round the base up to 1024
+    static constexpr int TMEM_P = 0, TMEM_S = 128, TMEM_O = 256;
+    // barrier indices
+    static constexpr int B_Q = 0, B_KFULL = 1, B_KEMPTY = B_KFULL + KSTAGES, B_VFULL = B_KEMPTY + KSTAGES,
+                         B_VEMPTY = B_VFULL + VSTAGES,
+                         B_S = B_VEMPTY + VSTAGES,  // [2] scores of tile t are in TMEM
+                         B_R = B_S + 2,             // [2] tile t has copied its scores out (4 warp arrivals)
+                         B_P = B_R + 2,             // [2][2] P of tile t, keys [0,64) / [64,128) written
+                         B_O = B_P + 4,             // [2] PV MMA of tile t finished
+                         NUM_BARS = B_O + 2;
 };
 
 // Wait codes reported in the device status word.
 enum {
-    W_MMA_Q = 1, W_MMA_K, W_MMA_V, W_MMA_P, W_SM_S, W_SM_O, W_SM_OFINAL, W_TMA_KEMPTY, W_TMA_VEMPTY
+    W_MMA_Q = 1, W_MMA_K, W_MMA_V, W_MMA_P, W_MMA_R, W_SM_S, W_SM_O, W_SM_OFINAL, W_TMA_KEMPTY, W_TMA_VEMPTY
 };
 
 struct FwdParams {
@@ -79,9 +95,8 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
 
     const uint32_t bar0 = smem_base + C::OFF_BAR;
     auto BAR = [&](int i) { return bar0 + 8u * (uint32_t)i; };
-    const int B_Q = 0;
-    const int B_KFULL = 1, B_KEMPTY = B_KFULL + C::STAGES, B_VFULL = B_KEMPTY + C::STAGES,
-              B_VEMPTY = B_VFULL + C::STAGES, B_S = B_VEMPTY + C::STAGES, B_P = B_S + 2, B_O = B_P + 4;
+    constexpr int B_Q = C::B_Q, B_KFULL = C::B_KFULL, B_KEMPTY = C::B_KEMPTY, B_VFULL = C::B_VFULL,
+                  B_VEMPTY = C::B_VEMPTY, B_S = C::B_S, B_R = C::B_R, B_P = C::B_P, B_O = C::B_O;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem_gen + C::OFF_BAR + 8 * C::NUM_BARS);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
@@ -108,25 +123,28 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
     if (threadIdx.x == 0) {
         *abort_flag = 0;
         mbar_init(BAR(B_Q), 1);
-        for (int s = 0; s < C::STAGES; s++) {
+        for (int s = 0; s < C::KSTAGES; s++) {
             mbar_init(BAR(B_KFULL + s), 1);
-            mbar_init(BAR(B_KEMPTY + s), 1);
+            mbar_init(BAR(B_KEMPTY + s), 2);  // one commit from each MMA warp
+        }
+        for (int s = 0; s < C::VSTAGES; s++) {
             mbar_init(BAR(B_VFULL + s), 1);
-            mbar_init(BAR(B_VEMPTY + s), 1);
+            mbar_init(BAR(B_VEMPTY + s), 2);
         }
         for (int t = 0; t < 2; t++) {
             mbar_init(BAR(B_S + t), 1);
+            mbar_init(BAR(B_R + t), 4);          // one arrival per softmax warp
             mbar_init(BAR(B_P + 2 * t), 4);      // first 64 keys of P written (one arrival per warp)
             mbar_init(BAR(B_P + 2 * t + 1), 4);  // last 64 keys of P written
             mbar_init(BAR(B_O + t), 1);
         }
         fence_mbar_init();
     }
-    if (warp == 10) {
+    if (warp == 11) {
         tmem_alloc(smem_u32(tmem_slot), 512);
         tmem_relinquish();
     }
-    if (warp == 9 && lane == 0) {
+    if (warp == 10 && lane == 0) {
         prefetch_tensormap(&tm_q);
         prefetch_tensormap(&tm_k);
         prefetch_tensormap(&tm_v);
@@ -138,7 +156,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
 
     if (warp >= 8) {
         reg_dealloc_40();
-        if (warp == 9 && lane == 0) {
+        if (warp == 10 && lane == 0) {
             // ------------------------------------------------------------ TMA producer
             const int ntiles_q = (n_t[1] > 0) ? 2 : 1;
             mbar_arrive_expect_tx(BAR(B_Q), ntiles_q * C::TILE_BYTES);
@@ -148,92 +166,97 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
                                 BAR(B_Q), s * 64, q_base + t * 128, bh);
             int k_issued = 0, v_issued = 0;
             for (int j = 0; j < n; j++) {
-                const int st = j % C::STAGES;
-                const uint32_t ph = (j / C::STAGES) & 1;
-                if (!mbar_wait(BAR(B_KEMPTY + st), ph ^ 1, abort_flag, p.status, W_TMA_KEMPTY)) break;
-                mbar_arrive_expect_tx(BAR(B_KFULL + st), C::TILE_BYTES);
+                const int ks = j % C::KSTAGES, vs = j % C::VSTAGES;
+                if (!mbar_wait(BAR(B_KEMPTY + ks), ((j / C::KSTAGES) & 1) ^ 1, abort_flag, p.status, W_TMA_KEMPTY)) break;
+                mbar_arrive_expect_tx(BAR(B_KFULL + ks), C::TILE_BYTES);
                 for (int s = 0; s < C::NSUB; s++)
-                    tma_load_3d(smem_base + C::OFF_K + st * C::TILE_BYTES + s * C::SUB_BYTES, &tm_k,
-                                BAR(B_KFULL + st), s * 64, j * 128, bh);
+                    tma_load_3d(smem_base + C::OFF_K + ks * C::TILE_BYTES + s * C::SUB_BYTES, &tm_k,
+                                BAR(B_KFULL + ks), s * 64, j * 128, bh);
                 k_issued = j + 1;
-                if (!mbar_wait(BAR(B_VEMPTY + st), ph ^ 1, abort_flag, p.status, W_TMA_VEMPTY)) break;
-                mbar_arrive_expect_tx(BAR(B_VFULL + st), C::TILE_BYTES);
+                if (!mbar_wait(BAR(B_VEMPTY + vs), ((j / C::VSTAGES) & 1) ^ 1, abort_flag, p.status, W_TMA_VEMPTY)) break;
+                mbar_arrive_expect_tx(BAR(B_VFULL + vs), C::TILE_BYTES);
                 for (int s = 0; s < C::NSUB; s++)
-                    tma_load_3d(smem_base + C::OFF_V + st * C::TILE_BYTES + s * C::SUB_BYTES, &tm_v,
-                                BAR(B_VFULL + st), s * 64, j * 128, bh);
+                    tma_load_3d(smem_base + C::OFF_V + vs * C::TILE_BYTES + s * C::SUB_BYTES, &tm_v,
+                                BAR(B_VFULL + vs), s * 64, j * 128, bh);
                 v_issued = j + 1;
             }
             // Do not leave the CTA while one of its own copies is still landing in shared memory:
             // a bounded poll (ignoring the abort flag; a copy that was issued always completes) on
             // the full-barrier of every stage still in flight.
             const long long t0 = clock64();
-            for (int j = max(0, k_issued - C::STAGES); j < k_issued; j++)
-                while (!mbar_try_wait(BAR(B_KFULL + j % C::STAGES), (j / C::STAGES) & 1) &&
+            for (int j = max(0, k_issued - C::KSTAGES); j < k_issued; j++)
+                while (!mbar_try_wait(BAR(B_KFULL + j % C::KSTAGES), (j / C::KSTAGES) & 1) &&
                        clock64() - t0 < kWaitLimitCycles) {}
-            for (int j = max(0, v_issued - C::STAGES); j < v_issued; j++)
-                while (!mbar_try_wait(BAR(B_VFULL + j % C::STAGES), (j / C::STAGES) & 1) &&
+            for (int j = max(0, v_issued - C::VSTAGES); j < v_issued; j++)
+                while (!mbar_try_wait(BAR(B_VFULL + j % C::VSTAGES), (j / C::VSTAGES) & 1) &&
                        clock64() - t0 < kWaitLimitCycles) {}
             while (!mbar_try_wait(BAR(B_Q), 0) && clock64() - t0 < kWaitLimitCycles) {}
-        } else if (warp == 8) {  // all 32 lanes, converged; one elected lane issues
-            // ------------------------------------------------------------ MMA issue
+        } else if (warp == 8 || warp == 9) {  // all 32 lanes, converged; one elected lane issues
+            // ------------------------------------------------------------ MMA issue for tile t
+            const int t = warp - 8;
             constexpr uint32_t IDESC_S = idesc_bf16_f32(128, 128, 0, 0);
             constexpr uint32_t IDESC_O = idesc_bf16_f32(128, HD, 0, 1);
-            auto issue_s = [&](int t, int st) {
-                const uint32_t q_lo = desc_lo(smem_base + C::OFF_Q + t * C::TILE_BYTES, 16);
-                const uint32_t k_lo = desc_lo(smem_base + C::OFF_K + st * C::TILE_BYTES, 16);
+            const int nt = n_t[t], no = n_t[1 - t];  // key tiles of this tile / of the other tile
+            const uint32_t q_lo = desc_lo(smem_base + C::OFF_Q + t * C::TILE_BYTES, 16);
+            bool ok = mbar_wait(BAR(B_Q), 0, abort_flag, p.status, W_MMA_Q);
+            // The score buffer is used in the order S0(0) S1(0) S0(1) S1(1) ...; each user waits until
+            // the softmax warps of the previous user have copied their scores out.
+            auto issue_s = [&](int j) {
+                if (t == 0) {
+                    if (j >= 1) {  // previous user: S1(j-1) if the other tile has it, else our own S0(j-1)
+                        const int pt = (j - 1 < no) ? 1 : 0;
+                        ok = ok && mbar_wait(BAR(B_R + pt), (j - 1) & 1, abort_flag, p.status, W_MMA_R);
+                    }
+                } else {           // previous user: S0(j) if the other tile has it, else our own S1(j-1)
+                    if (j < no)
+                        ok = ok && mbar_wait(BAR(B_R + 0), j & 1, abort_flag, p.status, W_MMA_R);
+                    else if (j >= 1)
+                        ok = ok && mbar_wait(BAR(B_R + 1), (j - 1) & 1, abort_flag, p.status, W_MMA_R);
+                }
+                tc_fence_after();
+                const uint32_t k_lo = desc_lo(smem_base + C::OFF_K + (j % C::KSTAGES) * C::TILE_BYTES, 16);
 #pragma unroll
                 for (int ks = 0; ks < HD / 16; ks++) {
                     const uint32_t o16 = ((ks / 4) * C::SUB_BYTES + (ks % 4) * 32) >> 4;
-                    mma_ss_lo(tmem + C::TMEM_S + t * 128, q_lo + o16, k_lo + o16, IDESC_S, ks > 0);
+                    mma_ss_lo(tmem + C::TMEM_S, q_lo + o16, k_lo + o16, IDESC_S, ks > 0);
                 }
                 tc_commit_elect(BAR(B_S + t));
             };
-            // O_t += P_t V for keys [64*half, 64*half + 64) of the tile
-            auto issue_pv_half = [&](int t, int st, int half, bool first) {
-                const uint32_t v_lo = desc_lo(smem_base + C::OFF_V + st * C::TILE_BYTES, C::SUB_BYTES);
+            // O_t += P_t(j) V_j for keys [64*half, 64*half + 64) of the tile
+            auto issue_pv_half = [&](int j, int half) {
+                ok = ok && mbar_wait(BAR(B_P + 2 * t + half), j & 1, abort_flag, p.status, W_MMA_P);
+                tc_fence_after();
+                const uint32_t v_lo = desc_lo(smem_base + C::OFF_V + (j % C::VSTAGES) * C::TILE_BYTES, C::SUB_BYTES);
 #pragma unroll
                 for (int k4 = 0; k4 < 4; k4++) {
                     const int ks = half * 4 + k4;
-                    mma_ts_lo(tmem + C::TMEM_O + t * HD, tmem + C::TMEM_S + t * 128 + ks * 8, v_lo + ks * (2048 >> 4),
-                              IDESC_O, (!first || ks > 0) ? 1u : 0u);
+                    mma_ts_lo(tmem + C::TMEM_O + t * HD, tmem + C::TMEM_P + t * 64 + ks * 8, v_lo + ks * (2048 >> 4),
+                              IDESC_O, (j > 0 || ks > 0) ? 1u : 0u);
                 }
                 if (half == 1) tc_commit_elect(BAR(B_O + t));
             };
-
-            bool ok = mbar_wait(BAR(B_Q), 0, abort_flag, p.status, W_MMA_Q);
+            // Both MMA warps release every K and V stage (the "empty" barriers count two commits), also
+            // for key tiles this query tile does not visit; a warp waits for the stage to be full
+            // before it commits, so that its arrival can never land in an earlier phase of the barrier.
             ok = ok && mbar_wait(BAR(B_KFULL + 0), 0, abort_flag, p.status, W_MMA_K);
-            tc_fence_after();
-            if (n_t[0] > 0) issue_s(0, 0);
-            if (n_t[1] > 0) issue_s(1, 0);
+            if (nt > 0) issue_s(0);
             tc_commit_elect(BAR(B_KEMPTY + 0));
+            // Step j of this tile: S_t(j+1), then the two halves of PV_t(j). The score MMA comes
+            // first: its buffer is free (the other tile copied out) about half a period before this
+            // tile's probabilities are ready.
             for (int j = 0; j < n && ok; j++) {
-                const int st = j % C::STAGES;
-                const uint32_t ph = (j / C::STAGES) & 1;
-                const int st1 = (j + 1) % C::STAGES;
-                const uint32_t ph1 = ((j + 1) / C::STAGES) & 1;
-                ok = ok && mbar_wait(BAR(B_VFULL + st), ph, abort_flag, p.status, W_MMA_V);
-                bool k_next_ready = false;
-#pragma unroll
-                for (int t = 0; t < 2; t++) {
-                    if (j < n_t[t]) {
-                        ok = ok && mbar_wait(BAR(B_P + 2 * t), j & 1, abort_flag, p.status, W_MMA_P);
-                        tc_fence_after();
-                        issue_pv_half(t, st, 0, j == 0);
-                        ok = ok && mbar_wait(BAR(B_P + 2 * t + 1), j & 1, abort_flag, p.status, W_MMA_P);
-                        tc_fence_after();
-                        issue_pv_half(t, st, 1, j == 0);
-                    }
-                    if (j + 1 < n_t[t]) {
-                        if (!k_next_ready) {
-                            ok = ok && mbar_wait(BAR(B_KFULL + st1), ph1, abort_flag, p.status, W_MMA_K);
-                            tc_fence_after();
-                            k_next_ready = true;
-                        }
-                        issue_s(t, st1);
-                    }
+                if (j + 1 < n) {
+                    ok = ok && mbar_wait(BAR(B_KFULL + (j + 1) % C::KSTAGES), ((j + 1) / C::KSTAGES) & 1, abort_flag,
+                                         p.status, W_MMA_K);
+                    if (j + 1 < nt) issue_s(j + 1);
+                    tc_commit_elect(BAR(B_KEMPTY + (j + 1) % C::KSTAGES));  // our reads of K(j+1) are issued
                 }
-                tc_commit_elect(BAR(B_VEMPTY + st));
-                if (j + 1 < n) tc_commit_elect(BAR(B_KEMPTY + st1));
+                ok = ok && mbar_wait(BAR(B_VFULL + j % C::VSTAGES), (j / C::VSTAGES) & 1, abort_flag, p.status, W_MMA_V);
+                if (j < nt) {
+                    issue_pv_half(j, 0);
+                    issue_pv_half(j, 1);
+                }
+                tc_commit_elect(BAR(B_VEMPTY + j % C::VSTAGES));  // our reads of V(j) are issued
             }
         }
     } else {
@@ -243,7 +266,8 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
         const int r = threadIdx.x % 128;          // row inside the tile == TMEM lane
         const int row = q_base + t * 128 + r;     // query row
         const uint32_t lane_sel = (uint32_t)((warp % 4) * 32) << 16;
-        const uint32_t ts = tmem + lane_sel + C::TMEM_S + t * 128;
+        const uint32_t ts = tmem + lane_sel + C::TMEM_S;           // the shared score buffer
+        const uint32_t tp = tmem + lane_sel + C::TMEM_P + t * 64;  // this tile's probabilities
         const uint32_t to = tmem + lane_sel + C::TMEM_O + t * HD;
         const int nk = n_t[t];
         const float c = p.scale_log2;
@@ -264,6 +288,10 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
                 for (int i = 0; i < 32; i++) s[ch * 32 + i] = __uint_as_float(u[i]);
             }
             tmem_wait_ld();
+            // The scores are in registers: hand the buffer to the other tile.
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(BAR(B_R + t));
 
             if (j * 128 + 127 > limit_tile) {
 #pragma unroll
@@ -293,6 +321,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
             }
             const float mx = mx8[0];
             const float m_new = fmaxf(m_ref, mx * c);
+            bool o_done = (j == 0);  // P(j-1) consumed by the PV MMA, so the P columns may be overwritten
             if (j == 0) {
                 m_ref = m_new;  // finite: key 0 is visible to every row
             } else {
@@ -302,6 +331,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
                     m_ref = m_new;
                     l *= alpha;
                     ok = ok && mbar_wait(BAR(B_O + t), (j - 1) & 1, abort_flag, p.status, W_SM_O);
+                    o_done = true;
                     tc_fence_after();
 #pragma unroll
                     for (int ch = 0; ch < HD / 32; ch++) {
@@ -337,7 +367,12 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
                         sum2[i & 3] = add2(sum2[i & 3], pack2(p0, p1));
                         pk[i] = pack_bf16(p0, p1);
                     }
-                    tmem_st_32x32b_x16(ts + ch * 16, pk);
+                    if (!o_done) {  // before the first store: PV(j-1) must have read the old P
+                        ok = ok && mbar_wait(BAR(B_O + t), (j - 1) & 1, abort_flag, p.status, W_SM_O);
+                        tc_fence_after();
+                        o_done = true;
+                    }
+                    tmem_st_32x32b_x16(tp + ch * 16, pk);
                 }
                 tmem_wait_st();
                 tc_fence_before();
@@ -380,7 +415,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
 
     tc_fence_before();
     __syncthreads();
-    if (warp == 10) tmem_dealloc(tmem, 512);
+    if (warp == 11) tmem_dealloc(tmem, 512);
 }
 
 template <int HD, int EMU>
