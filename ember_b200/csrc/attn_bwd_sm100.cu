@@ -24,7 +24,11 @@
 // exponentials are evaluated as a polynomial on the FMA pipe to keep the MUFU off the critical path.
 //
 //   warps 0-7   compute: thread (row r, half h) owns TMEM lane r and 64 of the 128 score columns
-//   warp  8     MMA issue (one lane)      warp 9   TMA producer (one lane)      warp 10  TMEM alloc
+//   warp  8     MMA issue, score chain:    S^T(i+1) and dV(i)   (dQ kernel: S(j+1))
+//   warp  9     MMA issue, gradient chain: dP^T(i+1) and dK(i)  (dQ kernel: dQ(j) and dP(j+1))
+//               Two issuing warps on different schedulers: each chain only orders MMAs that share
+//               TMEM columns, and one warp's barrier waits no longer delay the other chain.
+//   warp 10     TMA producer (one lane)       warp 11  TMEM allocation
 #include <math.h>
 
 #include "common.cuh"
@@ -90,7 +94,7 @@ __device__ __forceinline__ void named_bar_sync(int id, int count)
 template <typename C>
 __device__ __forceinline__ uint32_t bwd_setup(uint32_t smem_base, uint8_t *smem_gen, int warp, int lane,
                                               const CUtensorMap *m0, const CUtensorMap *m1,
-                                              const CUtensorMap *m2, const CUtensorMap *m3)
+                                              const CUtensorMap *m2, const CUtensorMap *m3, int empty_b_count)
 {
     const uint32_t bar0 = smem_base + C::OFF_BAR;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem_gen + C::OFF_BAR + 8 * C::NUM_BARS);
@@ -100,24 +104,24 @@ __device__ __forceinline__ uint32_t bwd_setup(uint32_t smem_base, uint8_t *smem_
         mbar_init(bar0 + 8 * C::B_RES, 1);
         for (int s = 0; s < C::NA; s++) {
             mbar_init(bar0 + 8 * (C::B_FULLA + s), 1);
-            mbar_init(bar0 + 8 * (C::B_EMPTYA + s), 1);
+            mbar_init(bar0 + 8 * (C::B_EMPTYA + s), 2);  // released by both MMA warps
         }
         for (int s = 0; s < C::NB; s++) {
             mbar_init(bar0 + 8 * (C::B_FULLB + s), 1);
-            mbar_init(bar0 + 8 * (C::B_EMPTYB + s), 1);
+            mbar_init(bar0 + 8 * (C::B_EMPTYB + s), empty_b_count);
         }
         mbar_init(bar0 + 8 * C::B_S, 1);
         mbar_init(bar0 + 8 * C::B_DP, 1);
         mbar_init(bar0 + 8 * C::B_P, 8);
         mbar_init(bar0 + 8 * C::B_DS, 8);
-        mbar_init(bar0 + 8 * C::B_ACC, 1);
+        mbar_init(bar0 + 8 * C::B_ACC, 2);  // one commit from each MMA warp
         fence_mbar_init();
     }
-    if (warp == 10) {
+    if (warp == 11) {
         tmem_alloc(smem_u32(tmem_slot), 512);
         tmem_relinquish();
     }
-    if (warp == 9 && lane == 0) {
+    if (warp == 10 && lane == 0) {
         prefetch_tensormap(m0);
         prefetch_tensormap(m1);
         prefetch_tensormap(m2);
@@ -238,6 +242,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
                           const BwdParams p)
 {
     using C = BwdCfg<HD>;
+    constexpr int EMPTY_B = 2;  // dO is read by both MMA chains (dP^T and dV)
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -255,11 +260,11 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
     const int i_begin = p.causal ? max(0, k0 - off) / 128 : 0;  // first query tile that sees key k0
     const int n = (p.lq + 127) / 128 - i_begin;
 
-    const uint32_t tmem = bwd_setup<C>(smem_base, smem_gen, warp, lane, &tm_q, &tm_k, &tm_v, &tm_do);
+    const uint32_t tmem = bwd_setup<C>(smem_base, smem_gen, warp, lane, &tm_q, &tm_k, &tm_v, &tm_do, EMPTY_B);
 
     if (warp >= 8) {
         reg_dealloc_40();
-        if (warp == 9 && lane == 0) {
+        if (warp == 10 && lane == 0) {
             // ---------------------------------------------------------------- TMA producer
             mbar_arrive_expect_tx(BAR(C::B_RES), 2 * C::TILE_BYTES);
             for (int s = 0; s < C::NSUB; s++) {
@@ -284,7 +289,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
                 issued_b = i + 1;
             }
             drain_copies<C>(bar0, issued_a, issued_b);
-        } else if (warp == 8) {  // all 32 lanes, converged; one elected lane issues
+        } else if (warp == 8 || warp == 9) {  // all 32 lanes, converged; one elected lane issues
             // ---------------------------------------------------------------- MMA issue
             constexpr uint32_t IDESC_SS = idesc_bf16_f32(128, 128, 0, 0);
             constexpr uint32_t IDESC_TS = idesc_bf16_f32(128, HD, 0, 1);
@@ -311,43 +316,55 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
                 tc_commit_elect(BAR(C::B_DP));
             };
             bool ok = mbar_wait(BAR(C::B_RES), 0, abort_flag, p.status, WB_RES);
-            ok = ok && mbar_wait(BAR(C::B_FULLA + 0), 0, abort_flag, p.status, WB_FULL);
-            tc_fence_after();
-            issue_st(0);
-            ok = ok && mbar_wait(BAR(C::B_FULLB + 0), 0, abort_flag, p.status, WB_FULL);
-            tc_fence_after();
-            issue_dpt(0);
-            for (int i = 0; i < n && ok; i++) {
-                const uint32_t domn_lo = desc_lo(do_addr(i), C::SUB_BYTES);
-                const uint32_t qmn_lo = desc_lo(q_addr(i), C::SUB_BYTES);
-                ok = ok && mbar_wait(BAR(C::B_P), i & 1, abort_flag, p.status, WB_P);
+            if (warp == 8) {
+                // score chain: S^T(0); then per tile dV(i) (reads P^T, dO) and S^T(i+1) (overwrites P^T)
+                ok = ok && mbar_wait(BAR(C::B_FULLA + 0), 0, abort_flag, p.status, WB_FULL);
                 tc_fence_after();
-#pragma unroll
-                for (int ks = 0; ks < 8; ks++)  // dV += P^T dO
-                    mma_ts_lo(tmem + C::T_ACC0, tmem + C::T_S + ks * 8, domn_lo + ks * (2048 >> 4), IDESC_TS,
-                              (i > 0 || ks > 0) ? 1u : 0u);
-                tc_commit_elect(BAR(C::B_EMPTYB + i % C::NB));  // dO(i) was last read by dV(i)
-                if (i + 1 < n) {
-                    ok = ok && mbar_wait(BAR(C::B_FULLA + (i + 1) % C::NA), ((i + 1) / C::NA) & 1, abort_flag,
-                                         p.status, WB_FULL);
+                issue_st(0);
+                for (int i = 0; i < n && ok; i++) {
+                    const uint32_t domn_lo = desc_lo(do_addr(i), C::SUB_BYTES);
+                    ok = ok && mbar_wait(BAR(C::B_FULLB + i % C::NB), (i / C::NB) & 1, abort_flag, p.status, WB_FULL);
+                    ok = ok && mbar_wait(BAR(C::B_P), i & 1, abort_flag, p.status, WB_P);
                     tc_fence_after();
-                    issue_st(i + 1);  // overwrites P^T(i): ordered after dV(i) by issue order
+#pragma unroll
+                    for (int ks = 0; ks < 8; ks++)  // dV += P^T dO
+                        mma_ts_lo(tmem + C::T_ACC0, tmem + C::T_S + ks * 8, domn_lo + ks * (2048 >> 4), IDESC_TS,
+                                  (i > 0 || ks > 0) ? 1u : 0u);
+                    tc_commit_elect(BAR(C::B_EMPTYB + i % C::NB));  // this chain's last read of dO(i)
+                    if (i + 1 < n) {
+                        ok = ok && mbar_wait(BAR(C::B_FULLA + (i + 1) % C::NA), ((i + 1) / C::NA) & 1, abort_flag,
+                                             p.status, WB_FULL);
+                        tc_fence_after();
+                        issue_st(i + 1);  // overwrites P^T(i): ordered after dV(i) by issue order
+                    }
+                    tc_commit_elect(BAR(C::B_EMPTYA + i % C::NA));  // this chain's last read of Q(i) was S^T(i)
                 }
-                ok = ok && mbar_wait(BAR(C::B_DS), i & 1, abort_flag, p.status, WB_DS);
+                tc_commit_elect(BAR(C::B_ACC));
+            } else {
+                // gradient chain: dP^T(0); then per tile dK(i) (reads dS^T, Q) and dP^T(i+1) (overwrites dS^T)
+                ok = ok && mbar_wait(BAR(C::B_FULLB + 0), 0, abort_flag, p.status, WB_FULL);
                 tc_fence_after();
-#pragma unroll
-                for (int ks = 0; ks < 8; ks++)  // dK += dS^T Q
-                    mma_ts_lo(tmem + C::T_ACC1, tmem + C::T_DP + ks * 8, qmn_lo + ks * (2048 >> 4), IDESC_TS,
-                              (i > 0 || ks > 0) ? 1u : 0u);
-                tc_commit_elect(BAR(C::B_EMPTYA + i % C::NA));  // Q(i) was last read by dK(i)
-                if (i + 1 < n) {
-                    ok = ok && mbar_wait(BAR(C::B_FULLB + (i + 1) % C::NB), ((i + 1) / C::NB) & 1, abort_flag,
-                                         p.status, WB_FULL);
+                issue_dpt(0);
+                for (int i = 0; i < n && ok; i++) {
+                    const uint32_t qmn_lo = desc_lo(q_addr(i), C::SUB_BYTES);
+                    ok = ok && mbar_wait(BAR(C::B_FULLA + i % C::NA), (i / C::NA) & 1, abort_flag, p.status, WB_FULL);
+                    ok = ok && mbar_wait(BAR(C::B_DS), i & 1, abort_flag, p.status, WB_DS);
                     tc_fence_after();
-                    issue_dpt(i + 1);  // overwrites dS^T(i): ordered after dK(i)
+#pragma unroll
+                    for (int ks = 0; ks < 8; ks++)  // dK += dS^T Q
+                        mma_ts_lo(tmem + C::T_ACC1, tmem + C::T_DP + ks * 8, qmn_lo + ks * (2048 >> 4), IDESC_TS,
+                                  (i > 0 || ks > 0) ? 1u : 0u);
+                    tc_commit_elect(BAR(C::B_EMPTYA + i % C::NA));  // this chain's last read of Q(i)
+                    if (i + 1 < n) {
+                        ok = ok && mbar_wait(BAR(C::B_FULLB + (i + 1) % C::NB), ((i + 1) / C::NB) & 1, abort_flag,
+                                             p.status, WB_FULL);
+                        tc_fence_after();
+                        issue_dpt(i + 1);  // overwrites dS^T(i): ordered after dK(i)
+                    }
+                    tc_commit_elect(BAR(C::B_EMPTYB + i % C::NB));  // this chain's last read of dO(i) was dP^T(i)
                 }
+                tc_commit_elect(BAR(C::B_ACC));
             }
-            tc_commit_elect(BAR(C::B_ACC));
         }
     } else {
         // -------------------------------------------------------------------- compute
@@ -448,7 +465,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
 
     tc_fence_before();
     __syncthreads();
-    if (warp == 10) tmem_dealloc(tmem, 512);
+    if (warp == 11) tmem_dealloc(tmem, 512);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -461,6 +478,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
                         const BwdParams p)
 {
     using C = BwdCfg<HD>;
+    constexpr int EMPTY_B = 1;  // V is read by the gradient chain only (dP)
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -478,11 +496,11 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
     const int visible = p.causal ? min(p.lk, q0 + 128 + off) : p.lk;
     const int n = (visible + 127) / 128;
 
-    const uint32_t tmem = bwd_setup<C>(smem_base, smem_gen, warp, lane, &tm_q, &tm_k, &tm_v, &tm_do);
+    const uint32_t tmem = bwd_setup<C>(smem_base, smem_gen, warp, lane, &tm_q, &tm_k, &tm_v, &tm_do, EMPTY_B);
 
     if (warp >= 8) {
         reg_dealloc_40();
-        if (warp == 9 && lane == 0) {
+        if (warp == 10 && lane == 0) {
             mbar_arrive_expect_tx(BAR(C::B_RES), 2 * C::TILE_BYTES);
             for (int s = 0; s < C::NSUB; s++) {
                 tma_load_3d(smem_base + C::OFF_RES0 + s * C::SUB_BYTES, &tm_q, BAR(C::B_RES), s * 64, q0, bh);
@@ -505,7 +523,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
                 issued_b = j + 1;
             }
             drain_copies<C>(bar0, issued_a, issued_b);
-        } else if (warp == 8) {  // all 32 lanes, converged; one elected lane issues
+        } else if (warp == 8 || warp == 9) {  // all 32 lanes, converged; one elected lane issues
             constexpr uint32_t IDESC_SS = idesc_bf16_f32(128, 128, 0, 0);
             constexpr uint32_t IDESC_TS = idesc_bf16_f32(128, HD, 0, 1);
             const uint32_t qa = smem_base + C::OFF_RES0, doa = smem_base + C::OFF_RES1;
@@ -532,36 +550,46 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
                 tc_commit_elect(BAR(C::B_EMPTYB + j % C::NB));  // V(j) is only read by dP(j)
             };
             bool ok = mbar_wait(BAR(C::B_RES), 0, abort_flag, p.status, WB_RES);
-            ok = ok && mbar_wait(BAR(C::B_FULLA + 0), 0, abort_flag, p.status, WB_FULL);
-            tc_fence_after();
-            issue_s(0);
-            ok = ok && mbar_wait(BAR(C::B_FULLB + 0), 0, abort_flag, p.status, WB_FULL);
-            tc_fence_after();
-            issue_dp(0);
-            for (int j = 0; j < n && ok; j++) {
-                const uint32_t kmn_lo = desc_lo(k_addr(j), C::SUB_BYTES);
-                if (j + 1 < n) {
-                    ok = ok && mbar_wait(BAR(C::B_FULLA + (j + 1) % C::NA), ((j + 1) / C::NA) & 1, abort_flag,
-                                         p.status, WB_FULL);
-                    ok = ok && mbar_wait(BAR(C::B_P), j & 1, abort_flag, p.status, WB_P);  // S(j) has been read
-                    tc_fence_after();
-                    issue_s(j + 1);
-                }
-                ok = ok && mbar_wait(BAR(C::B_DS), j & 1, abort_flag, p.status, WB_DS);
+            if (warp == 8) {
+                // score chain: S(j+1) as soon as the compute warps have copied S(j) out
+                ok = ok && mbar_wait(BAR(C::B_FULLA + 0), 0, abort_flag, p.status, WB_FULL);
                 tc_fence_after();
-#pragma unroll
-                for (int ks = 0; ks < 8; ks++)  // dQ += dS K
-                    mma_ts_lo(tmem + C::T_ACC0, tmem + C::T_DP + ks * 8, kmn_lo + ks * (2048 >> 4), IDESC_TS,
-                              (j > 0 || ks > 0) ? 1u : 0u);
-                tc_commit_elect(BAR(C::B_EMPTYA + j % C::NA));  // K(j) was last read by dQ(j)
-                if (j + 1 < n) {
-                    ok = ok && mbar_wait(BAR(C::B_FULLB + (j + 1) % C::NB), ((j + 1) / C::NB) & 1, abort_flag,
-                                         p.status, WB_FULL);
-                    tc_fence_after();
-                    issue_dp(j + 1);  // overwrites dS(j): ordered after dQ(j)
+                issue_s(0);
+                for (int j = 0; j < n && ok; j++) {
+                    if (j + 1 < n) {
+                        ok = ok && mbar_wait(BAR(C::B_FULLA + (j + 1) % C::NA), ((j + 1) / C::NA) & 1, abort_flag,
+                                             p.status, WB_FULL);
+                        ok = ok && mbar_wait(BAR(C::B_P), j & 1, abort_flag, p.status, WB_P);  // S(j) has been read
+                        tc_fence_after();
+                        issue_s(j + 1);
+                    }
+                    tc_commit_elect(BAR(C::B_EMPTYA + j % C::NA));  // this chain's last read of K(j) was S(j)
                 }
+                tc_commit_elect(BAR(C::B_ACC));
+            } else {
+                // gradient chain: dP(0); then per tile dQ(j) (reads dS, K) and dP(j+1) (overwrites dS)
+                ok = ok && mbar_wait(BAR(C::B_FULLB + 0), 0, abort_flag, p.status, WB_FULL);
+                tc_fence_after();
+                issue_dp(0);
+                for (int j = 0; j < n && ok; j++) {
+                    const uint32_t kmn_lo = desc_lo(k_addr(j), C::SUB_BYTES);
+                    ok = ok && mbar_wait(BAR(C::B_FULLA + j % C::NA), (j / C::NA) & 1, abort_flag, p.status, WB_FULL);
+                    ok = ok && mbar_wait(BAR(C::B_DS), j & 1, abort_flag, p.status, WB_DS);
+                    tc_fence_after();
+#pragma unroll
+                    for (int ks = 0; ks < 8; ks++)  // dQ += dS K
+                        mma_ts_lo(tmem + C::T_ACC0, tmem + C::T_DP + ks * 8, kmn_lo + ks * (2048 >> 4), IDESC_TS,
+                                  (j > 0 || ks > 0) ? 1u : 0u);
+                    tc_commit_elect(BAR(C::B_EMPTYA + j % C::NA));  // this chain's last read of K(j)
+                    if (j + 1 < n) {
+                        ok = ok && mbar_wait(BAR(C::B_FULLB + (j + 1) % C::NB), ((j + 1) / C::NB) & 1, abort_flag,
+                                             p.status, WB_FULL);
+                        tc_fence_after();
+                        issue_dp(j + 1);  // overwrites dS(j): ordered after dQ(j); also releases V(j+1)
+                    }
+                }
+                tc_commit_elect(BAR(C::B_ACC));
             }
-            tc_commit_elect(BAR(C::B_ACC));
         }
     } else {
         reg_alloc_232();
@@ -630,7 +658,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
 
     tc_fence_before();
     __syncthreads();
-    if (warp == 10) tmem_dealloc(tmem, 512);
+    if (warp == 11) tmem_dealloc(tmem, 512);
 }
 
 template <int HD>
