@@ -177,13 +177,12 @@ __device__ __forceinline__ void store_acc(uint32_t tacc, __nv_bfloat16 *grow, in
         tmem_wait_ld();
         if (store) {
 #pragma unroll
-            for (int v4 = 0; v4 < 4; v4++) {
-                uint4 w;
-                w.x = pack_bf16(__uint_as_float(o[v4 * 8 + 0]) * mul, __uint_as_float(o[v4 * 8 + 1]) * mul);
-                w.y = pack_bf16(__uint_as_float(o[v4 * 8 + 2]) * mul, __uint_as_float(o[v4 * 8 + 3]) * mul);
-                w.z = pack_bf16(__uint_as_float(o[v4 * 8 + 4]) * mul, __uint_as_float(o[v4 * 8 + 5]) * mul);
-                w.w = pack_bf16(__uint_as_float(o[v4 * 8 + 6]) * mul, __uint_as_float(o[v4 * 8 + 7]) * mul);
-                *reinterpret_cast<uint4 *>(grow + col + v4 * 8) = w;
+            for (int v8 = 0; v8 < 2; v8++) {  // 16 columns = 32 bytes per store
+                uint32_t w[8];
+#pragma unroll
+                for (int x = 0; x < 8; x++)
+                    w[x] = pack_bf16(__uint_as_float(o[v8 * 16 + 2 * x]) * mul, __uint_as_float(o[v8 * 16 + 2 * x + 1]) * mul);
+                st_global_256(grow + col + v8 * 16, w);
             }
         }
     }
@@ -703,9 +702,10 @@ bool sm100_bwd_supported(const AttnArgs &a)
     if (a.d != 64 && a.d != 128) return false;
     if (!isfinite(a.scale)) return false;
     if ((a.lq + 127) / 128 > 65535 || (a.lk + 127) / 128 > 65535) return false;
-    const uintptr_t bits = (uintptr_t)a.q | (uintptr_t)a.k | (uintptr_t)a.v | (uintptr_t)a.dout |
-                           (uintptr_t)a.dq | (uintptr_t)a.dk | (uintptr_t)a.dv;
-    return (bits & 15) == 0;
+    // TMA needs 16-byte aligned bases; the epilogues store 32-byte vectors.
+    const uintptr_t in_bits = (uintptr_t)a.q | (uintptr_t)a.k | (uintptr_t)a.v | (uintptr_t)a.dout;
+    const uintptr_t out_bits = (uintptr_t)a.dq | (uintptr_t)a.dk | (uintptr_t)a.dv;
+    return (in_bits & 15) == 0 && (out_bits & 31) == 0;
 }
 
 int sm100_attention_bwd(const AttnArgs &a, float *delta, DeviceState *st, cudaStream_t s)

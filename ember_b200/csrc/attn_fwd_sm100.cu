@@ -349,31 +349,34 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
             f32x2 sum2[4] = {0, 0, 0, 0};  // bit pattern of (0.f, 0.f)
 #pragma unroll
             for (int half = 0; half < 2; half++) {
+                uint32_t pk[2][16];
 #pragma unroll
-                for (int ch = 2 * half; ch < 2 * half + 2; ch++) {
-                    uint32_t pk[16];
+                for (int c2i = 0; c2i < 2; c2i++) {
+                    const int ch = 2 * half + c2i;
 #pragma unroll
                     for (int i = 0; i < 16; i++) {
                         const f32x2 x2 = fma2(pack2(s[ch * 32 + 2 * i], s[ch * 32 + 2 * i + 1]), c2, negm2);
                         float p0, p1;
                         if (i % 4 < EMU) {  // polynomial on the FMA pipe
                             exp2_poly2(x2, p0, p1);
-                        } else {                        // MUFU
+                        } else {            // MUFU
                             float x0, x1;
                             unpack2(x2, x0, x1);
                             p0 = ex2(x0);
                             p1 = ex2(x1);
                         }
                         sum2[i & 3] = add2(sum2[i & 3], pack2(p0, p1));
-                        pk[i] = pack_bf16(p0, p1);
+                        pk[c2i][i] = pack_bf16(p0, p1);
                     }
-                    if (!o_done) {  // before the first store: PV(j-1) must have read the old P
-                        ok = ok && mbar_wait(BAR(B_O + t), (j - 1) & 1, abort_flag, p.status, W_SM_O);
-                        tc_fence_after();
-                        o_done = true;
-                    }
-                    tmem_st_32x32b_x16(tp + ch * 16, pk);
                 }
+                if (!o_done) {  // before the first store: PV(j-1) must have read the old P (waited for as
+                                // late as possible: the 64 probabilities of this half are already computed)
+                    ok = ok && mbar_wait(BAR(B_O + t), (j - 1) & 1, abort_flag, p.status, W_SM_O);
+                    tc_fence_after();
+                    o_done = true;
+                }
+                tmem_st_32x32b_x16(tp + (2 * half) * 16, pk[0]);
+                tmem_st_32x32b_x16(tp + (2 * half + 1) * 16, pk[1]);
                 tmem_wait_st();
                 tc_fence_before();
                 __syncwarp();
@@ -399,13 +402,12 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
                 tmem_wait_ld();
                 if (store) {
 #pragma unroll
-                    for (int v4 = 0; v4 < 4; v4++) {
-                        uint4 w;
-                        w.x = pack_bf16(__uint_as_float(o[v4 * 8 + 0]) * inv, __uint_as_float(o[v4 * 8 + 1]) * inv);
-                        w.y = pack_bf16(__uint_as_float(o[v4 * 8 + 2]) * inv, __uint_as_float(o[v4 * 8 + 3]) * inv);
-                        w.z = pack_bf16(__uint_as_float(o[v4 * 8 + 4]) * inv, __uint_as_float(o[v4 * 8 + 5]) * inv);
-                        w.w = pack_bf16(__uint_as_float(o[v4 * 8 + 6]) * inv, __uint_as_float(o[v4 * 8 + 7]) * inv);
-                        *reinterpret_cast<uint4 *>(orow + ch * 32 + v4 * 8) = w;
+                    for (int v8 = 0; v8 < 2; v8++) {  // 16 columns = 32 bytes per store
+                        uint32_t w[8];
+#pragma unroll
+                        for (int x = 0; x < 8; x++)
+                            w[x] = pack_bf16(__uint_as_float(o[v8 * 16 + 2 * x]) * inv, __uint_as_float(o[v8 * 16 + 2 * x + 1]) * inv);
+                        st_global_256(orow + ch * 32 + v8 * 16, w);
                     }
                 }
             }
@@ -451,9 +453,9 @@ bool sm100_fwd_supported(const AttnArgs &a)
     if (a.d != 64 && a.d != 128) return false;
     if (!(a.scale != 0.f) || !isfinite(a.scale)) return false;
     if ((a.lq + 255) / 256 > 65535) return false;
-    // TMA needs 16-byte aligned bases; the epilogue stores 16-byte vectors.
-    const uintptr_t bits = (uintptr_t)a.q | (uintptr_t)a.k | (uintptr_t)a.v | (uintptr_t)a.out;
-    return (bits & 15) == 0;
+    // TMA needs 16-byte aligned bases; the epilogue stores 32-byte vectors.
+    const uintptr_t bits = (uintptr_t)a.q | (uintptr_t)a.k | (uintptr_t)a.v;
+    return (bits & 15) == 0 && ((uintptr_t)a.out & 31) == 0;
 }
 
 // Debugging knob: EMBER_FWD_EMU=0..2 overrides the share of polynomial exponentials (read once).
