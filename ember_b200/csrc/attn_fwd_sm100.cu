@@ -394,21 +394,44 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
             tc_fence_after();
             const float inv = 1.f / l;
             const bool store = ok && row < p.lq;
-            __nv_bfloat16 *orow = p.out + ((size_t)bh * p.lq + row) * HD;
+            // O / l as bf16 goes through shared memory so that the global stores are coalesced (a
+            // thread owns a whole row; storing rows directly makes every store instruction touch 32
+            // different lines, which clogs the load/store pipe also for the MMA warps' barrier
+            // traffic). The tile's Q buffer is free by now (its last score MMA has completed) and each
+            // warp stages only its own 32 rows, so a __syncwarp is all the synchronisation needed.
+            // 16-byte chunks are XOR-swizzled by the row to keep both phases free of bank conflicts.
+            constexpr int ROWB = HD * 2, CHUNKS = ROWB / 16;
+            uint8_t *stage = smem_gen + C::OFF_Q + t * C::TILE_BYTES;
 #pragma unroll
             for (int ch = 0; ch < HD / 32; ch++) {
                 uint32_t o[32];
                 tmem_ld_32x32b_x32(to + ch * 32, o);
                 tmem_wait_ld();
-                if (store) {
 #pragma unroll
-                    for (int v8 = 0; v8 < 2; v8++) {  // 16 columns = 32 bytes per store
-                        uint32_t w[8];
+                for (int q4 = 0; q4 < 4; q4++) {  // 8 columns = one 16-byte chunk
+                    uint4 wv;
+                    wv.x = pack_bf16(__uint_as_float(o[q4 * 8 + 0]) * inv, __uint_as_float(o[q4 * 8 + 1]) * inv);
+                    wv.y = pack_bf16(__uint_as_float(o[q4 * 8 + 2]) * inv, __uint_as_float(o[q4 * 8 + 3]) * inv);
+                    wv.z = pack_bf16(__uint_as_float(o[q4 * 8 + 4]) * inv, __uint_as_float(o[q4 * 8 + 5]) * inv);
+                    wv.w = pack_bf16(__uint_as_float(o[q4 * 8 + 6]) * inv, __uint_as_float(o[q4 * 8 + 7]) * inv);
+                    const int chunk = ch * 4 + q4;
+                    const int sw = (chunk & ~7) | ((chunk ^ r) & 7);
+                    *reinterpret_cast<uint4 *>(stage + r * ROWB + sw * 16) = wv;
+                }
+            }
+            __syncwarp();
+            {
+                constexpr int ROWS_PER_ST = 32 / CHUNKS;  // rows covered by one warp-wide 16-byte store
+                const int wrow0 = (warp % 4) * 32;        // first row of this warp inside the tile
+                const int chunk = lane % CHUNKS;
 #pragma unroll
-                        for (int x = 0; x < 8; x++)
-                            w[x] = pack_bf16(__uint_as_float(o[v8 * 16 + 2 * x]) * inv, __uint_as_float(o[v8 * 16 + 2 * x + 1]) * inv);
-                        st_global_256(orow + ch * 32 + v8 * 16, w);
-                    }
+                for (int it = 0; it < 32 / ROWS_PER_ST; it++) {
+                    const int rr = wrow0 + it * ROWS_PER_ST + lane / CHUNKS;
+                    const int sw = (chunk & ~7) | ((chunk ^ rr) & 7);
+                    const uint4 wv = *reinterpret_cast<const uint4 *>(stage + rr * ROWB + sw * 16);
+                    const int grow = q_base + t * 128 + rr;
+                    if (ok && grow < p.lq)
+                        *reinterpret_cast<uint4 *>(p.out + ((size_t)bh * p.lq + grow) * HD + chunk * 8) = wv;
                 }
             }
             if (store && p.lse) p.lse[(size_t)bh * p.lq + row] = (m_ref + log2f(l)) * LN2_F;
@@ -453,9 +476,9 @@ bool sm100_fwd_supported(const AttnArgs &a)
     if (a.d != 64 && a.d != 128) return false;
     if (!(a.scale != 0.f) || !isfinite(a.scale)) return false;
     if ((a.lq + 255) / 256 > 65535) return false;
-    // TMA needs 16-byte aligned bases; the epilogue stores 32-byte vectors.
+    // TMA needs 16-byte aligned bases; the epilogue stores 16-byte vectors.
     const uintptr_t bits = (uintptr_t)a.q | (uintptr_t)a.k | (uintptr_t)a.v;
-    return (bits & 15) == 0 && ((uintptr_t)a.out & 31) == 0;
+    return (bits & 15) == 0 && ((uintptr_t)a.out & 15) == 0;
 }
 
 // Debugging knob: EMBER_FWD_EMU=0..2 overrides the share of polynomial exponentials (read once).
