@@ -164,27 +164,52 @@ __device__ __forceinline__ bool smem_layout_fits(uint32_t raw_base, uint32_t ali
     return false;
 }
 
-// acc (TMEM, fp32, 128 x HD) -> bf16 rows in global memory, times `mul`; thread (r, h) stores
-// columns [h*HD/2, (h+1)*HD/2) of row r when `store` is set.
+// Epilogue helpers. A thread owns a whole accumulator row, and storing rows straight to global
+// memory makes every store instruction touch 32 different lines; the results therefore go through
+// shared memory (a resident operand tile that is no longer needed) and leave as coalesced rows.
+// 16-byte chunks are XOR-swizzled by the row so that neither phase has bank conflicts.
+//
+// stage_acc: accumulator (TMEM, fp32, 128 x HD) times `mul` -> bf16 rows of a 128 x (HD*2 bytes)
+// shared tile; thread (r, h) writes columns [h*HD/2, (h+1)*HD/2) of row r.
 template <int HD>
-__device__ __forceinline__ void store_acc(uint32_t tacc, __nv_bfloat16 *grow, int h, float mul, bool store)
+__device__ __forceinline__ void stage_acc(uint32_t tacc, uint8_t *stage, int r, int h, float mul)
 {
+    constexpr int ROWB = HD * 2;
 #pragma unroll
     for (int ch = 0; ch < HD / 64; ch++) {
         const int col = h * (HD / 2) + ch * 32;
         uint32_t o[32];
         tmem_ld_32x32b_x32(tacc + col, o);
         tmem_wait_ld();
-        if (store) {
 #pragma unroll
-            for (int v8 = 0; v8 < 2; v8++) {  // 16 columns = 32 bytes per store
-                uint32_t w[8];
-#pragma unroll
-                for (int x = 0; x < 8; x++)
-                    w[x] = pack_bf16(__uint_as_float(o[v8 * 16 + 2 * x]) * mul, __uint_as_float(o[v8 * 16 + 2 * x + 1]) * mul);
-                st_global_256(grow + col + v8 * 16, w);
-            }
+        for (int q4 = 0; q4 < 4; q4++) {  // 8 columns = one 16-byte chunk
+            uint4 wv;
+            wv.x = pack_bf16(__uint_as_float(o[q4 * 8 + 0]) * mul, __uint_as_float(o[q4 * 8 + 1]) * mul);
+            wv.y = pack_bf16(__uint_as_float(o[q4 * 8 + 2]) * mul, __uint_as_float(o[q4 * 8 + 3]) * mul);
+            wv.z = pack_bf16(__uint_as_float(o[q4 * 8 + 4]) * mul, __uint_as_float(o[q4 * 8 + 5]) * mul);
+            wv.w = pack_bf16(__uint_as_float(o[q4 * 8 + 6]) * mul, __uint_as_float(o[q4 * 8 + 7]) * mul);
+            const int chunk = col / 8 + q4;
+            const int sw = (chunk & ~7) | ((chunk ^ r) & 7);
+            *reinterpret_cast<uint4 *>(stage + r * ROWB + sw * 16) = wv;
         }
+    }
+}
+
+// store_staged: after all 256 compute threads have staged (caller synchronises), compute warp w8
+// (0..7) copies rows [16*w8, 16*w8 + 16) of the tile to global memory, whole rows per instruction.
+// gtile points at row 0 of the tile in the (rows x HD) global matrix; rows >= rows_valid are skipped.
+template <int HD>
+__device__ __forceinline__ void store_staged(const uint8_t *stage, __nv_bfloat16 *gtile, int rows_valid, int w8,
+                                             int lane)
+{
+    constexpr int ROWB = HD * 2, CHUNKS = ROWB / 16, ROWS_PER_ST = 32 / CHUNKS;
+    const int chunk = lane % CHUNKS;
+#pragma unroll
+    for (int it = 0; it < 16 / ROWS_PER_ST; it++) {
+        const int rr = w8 * 16 + it * ROWS_PER_ST + lane / CHUNKS;
+        const int sw = (chunk & ~7) | ((chunk ^ rr) & 7);
+        const uint4 wv = *reinterpret_cast<const uint4 *>(stage + rr * ROWB + sw * 16);
+        if (rr < rows_valid) *reinterpret_cast<uint4 *>(gtile + (size_t)rr * HD + chunk * 8) = wv;
     }
 }
 
@@ -456,10 +481,15 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
         }
         ok = ok && mbar_wait(BAR(C::B_ACC), 0, abort_flag, p.status, WB_ACC);
         tc_fence_after();
-        const bool store = ok && key < p.lk;
-        const size_t grow = ((size_t)bh * p.lk + key) * HD;
-        store_acc<HD>(tmem + lane_sel + C::T_ACC0, p.dv + grow, h, 1.f, store);
-        store_acc<HD>(tmem + lane_sel + C::T_ACC1, p.dk + grow, h, p.scale, store);
+        // dV through the V tile's buffer, dK (times the softmax scale) through the K tile's: both
+        // resident tiles are dead once the last MMAs have completed.
+        stage_acc<HD>(tmem + lane_sel + C::T_ACC0, smem_gen + C::OFF_RES1, r, h, 1.f);
+        stage_acc<HD>(tmem + lane_sel + C::T_ACC1, smem_gen + C::OFF_RES0, r, h, p.scale);
+        named_bar_sync(3, 256);
+        const int rows_valid = ok ? min(128, p.lk - k0) : 0;
+        const size_t gtile = ((size_t)bh * p.lk + k0) * HD;
+        store_staged<HD>(smem_gen + C::OFF_RES1, p.dv + gtile, rows_valid, warp, lane);
+        store_staged<HD>(smem_gen + C::OFF_RES0, p.dk + gtile, rows_valid, warp, lane);
     }
 
     tc_fence_before();
@@ -652,7 +682,11 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
         }
         ok = ok && mbar_wait(BAR(C::B_ACC), 0, abort_flag, p.status, WB_ACC);
         tc_fence_after();
-        store_acc<HD>(tmem + lane_sel + C::T_ACC0, p.dq + ((size_t)bh * p.lq + row) * HD, h, p.scale, ok && row_ok);
+        // dQ (times the softmax scale) through the Q tile's buffer, which is dead by now.
+        stage_acc<HD>(tmem + lane_sel + C::T_ACC0, smem_gen + C::OFF_RES0, r, h, p.scale);
+        named_bar_sync(3, 256);
+        store_staged<HD>(smem_gen + C::OFF_RES0, p.dq + ((size_t)bh * p.lq + q0) * HD, ok ? min(128, p.lq - q0) : 0, warp,
+                         lane);
     }
 
     tc_fence_before();
@@ -702,10 +736,10 @@ bool sm100_bwd_supported(const AttnArgs &a)
     if (a.d != 64 && a.d != 128) return false;
     if (!isfinite(a.scale)) return false;
     if ((a.lq + 127) / 128 > 65535 || (a.lk + 127) / 128 > 65535) return false;
-    // TMA needs 16-byte aligned bases; the epilogues store 32-byte vectors.
-    const uintptr_t in_bits = (uintptr_t)a.q | (uintptr_t)a.k | (uintptr_t)a.v | (uintptr_t)a.dout;
-    const uintptr_t out_bits = (uintptr_t)a.dq | (uintptr_t)a.dk | (uintptr_t)a.dv;
-    return (in_bits & 15) == 0 && (out_bits & 31) == 0;
+    // TMA needs 16-byte aligned bases; the epilogues store 16-byte vectors.
+    const uintptr_t bits = (uintptr_t)a.q | (uintptr_t)a.k | (uintptr_t)a.v | (uintptr_t)a.dout |
+                           (uintptr_t)a.dq | (uintptr_t)a.dk | (uintptr_t)a.dv;
+    return (bits & 15) == 0;
 }
 
 int sm100_attention_bwd(const AttnArgs &a, float *delta, DeviceState *st, cudaStream_t s)
