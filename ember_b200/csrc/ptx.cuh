@@ -362,13 +362,6 @@ __device__ __forceinline__ float min3(float a, float b, float c)
     return r;
 }
 
-// 32 bytes (16 bf16 values) to global memory in one instruction; the address must be 32-byte aligned.
-__device__ __forceinline__ void st_global_256(void *ptr, const uint32_t (&w)[8])
-{
-    asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(ptr), "r"(w[0]), "r"(w[1]), "r"(w[2]),
-                 "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
-                 : "memory");
-}
 
 __device__ __forceinline__ float ex2(float x)
 {
