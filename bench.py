@@ -379,15 +379,73 @@ def run_gpu_arm(args):
         "clocks": clocks,
     }
 
+    sweep = None
+    if not args.no_extra:
+        sweep = run_c5_sweep(L, _lib, torch, dist, dev, sptr, stream, rank, world)
     if rank == 0 and world == 1:
         cb, _ = cpu_baseline_value(rows=1024, threads=min(host_threads(), 64), repeats=1)
         line["cpu_baseline"] = cb
         if not args.no_extra:
             line["extra"] = run_extras(L, _lib, torch, dev, sptr, stream, peaks)
+    if sweep is not None:
+        line.setdefault("extra", {})["scaling_sweep_fwd_bwd_128_heads"] = {
+            "scaling": "strong", "note": "causal fwd+bwd, bf16, D=128, 128 (batch*head) units split over the GPUs",
+            **sweep}
     if world > 1:
         dist.destroy_process_group()
     if rank == 0:
         print(json.dumps(line), flush=True)
+
+
+def run_c5_sweep(L, _lib, torch, dist, dev, sptr, stream, rank, world):
+    """BASELINE configs[4]: causal forward+backward, bf16, 128 (batch*head) units with D=128 split over
+    the ranks (strong scaling: the total work is fixed), L in {2048, 8192, 16384}. Every rank owns
+    the contiguous slab shard_range(128, rank, world); no collective on the data path. Returns, per
+    L, the whole-job TFLOP/s from the slowest rank's device time."""
+    from ember_b200.shard import shard_range
+
+    out = {}
+    D = 128
+    b, e = shard_range(128, rank, world)
+    bh = e - b
+    for S in (2048, 8192, 16384):
+        scale = 1.0 / math.sqrt(D)
+        gen = torch.Generator(device=dev).manual_seed(500 + rank)
+        q, k, v = ((torch.randn((bh, S, D), generator=gen, device=dev) * 0.5).to(torch.bfloat16) for _ in range(3))
+        do = torch.randn((bh, S, D), generator=gen, device=dev).to(torch.bfloat16)
+        o, dq, dk, dv = (torch.empty_like(q) for _ in range(4))
+        lse = torch.empty((bh, S), device=dev, dtype=torch.float32)
+        wsn = L.ember_attention_workspace_bytes(_lib.EMBER_OP_BWD, bh, S, S, D, 1, 0)
+        ws = torch.empty(max(wsn, 256), device=dev, dtype=torch.uint8)
+
+        def step():
+            _lib.check(L.ember_attention_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), bh,
+                                             S, S, D, scale, 1, 1, sptr))
+            _lib.check(L.ember_attention_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(),
+                                             do.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), bh, S, S, D,
+                                             scale, 1, 1, ws.data_ptr(), wsn, sptr))
+
+        steps = 10 if S <= 8192 else 4
+        for _ in range(3):
+            step()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        a, c = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        for _ in range(steps):
+            step()
+        c.record(stream)
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(c) / steps
+        if world > 1:
+            t = torch.tensor([ms], dtype=torch.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        total_flops = 3.5 * 4.0 * 128 * S * S * D / 2.0
+        out[f"L{S}"] = {"ms_fwd_bwd": ms, "tflops_total": total_flops / ms / 1e9, "bh_per_gpu": bh}
+        del q, k, v, do, o, dq, dk, dv, ws
+    return out
 
 
 def run_extras(L, _lib, torch, dev, sptr, stream, peaks):

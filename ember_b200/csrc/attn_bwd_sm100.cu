@@ -20,7 +20,7 @@
 // Each kernel is software-pipelined over its tiles in two phases so that the tensor core works
 // while the compute warps do: in the dK/dV kernel the exponentials of tile i+1 run while
 // dK(i) and dP^T(i+1) are multiplied, and dS^T(i+1) is formed while dV(i+1) and S^T(i+2) are; the
-// dQ kernel issues S(j+1) as soon as S(j) has been read into registers. A quarter of the
+// dQ kernel issues S(j+1) as soon as S(j) has been read into registers. Half of the
 // exponentials are evaluated as a polynomial on the FMA pipe to keep the MUFU off the critical path.
 //
 //   warps 0-7   compute: thread (row r, half h) owns TMEM lane r and 64 of the 128 score columns
@@ -213,7 +213,9 @@ __device__ __forceinline__ void store_staged(const uint8_t *stage, __nv_bfloat16
     }
 }
 
-constexpr int BWD_EMU_PAIRS_OF_4 = 1;  // pairs per group of 4 whose exponentials avoid the MUFU
+#ifndef BWD_EMU_PAIRS_OF_4
+#define BWD_EMU_PAIRS_OF_4 2  // pairs per group of 4 whose exponentials avoid the MUFU
+#endif
 
 // p = 2^x for a pair, through the MUFU or the FMA-pipe polynomial depending on the pair's position
 __device__ __forceinline__ void exp2_pair(f32x2 x2, int pair_index, float &p0, float &p1)
