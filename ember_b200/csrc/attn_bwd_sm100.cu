@@ -23,12 +23,12 @@
 // dQ kernel issues S(j+1) as soon as S(j) has been read into registers. Half of the
 // exponentials are evaluated as a polynomial on the FMA pipe to keep the MUFU off the critical path.
 //
-//   warps 0-7   compute: thread (row r, half h) owns TMEM lane r and 64 of the 128 score columns
+//   warps 0-7   compute: thread (row r, slice h) owns TMEM lane r and 64 of the 128 score columns
 //   warp  8     MMA issue, score chain:    S^T(i+1) and dV(i)   (dQ kernel: S(j+1))
 //   warp  9     MMA issue, gradient chain: dP^T(i+1) and dK(i)  (dQ kernel: dQ(j) and dP(j+1))
 //               Two issuing warps on different schedulers: each chain only orders MMAs that share
 //               TMEM columns, and one warp's barrier waits no longer delay the other chain.
-//   warp 10     TMA producer (one lane)       warp 11  TMEM allocation
+//   warp  10    TMA producer (one lane)       warp 11  TMEM allocation
 #include <math.h>
 
 #include "common.cuh"
@@ -41,7 +41,17 @@ namespace {
 
 using namespace ptx;
 
-constexpr int BWD_THREADS = 384;
+// Compute warps: every TMEM lane quarter is served by NCW/4 warps, each thread owning CPT of the 128
+// score columns of its lane. Eight warps (two per scheduler, 64 columns per thread) and sixteen
+// (four per scheduler, 32 columns) measured the same; eight is the default.
+#ifndef BWD_COMPUTE_WARPS
+#define BWD_COMPUTE_WARPS 8
+#endif
+constexpr int NCW = BWD_COMPUTE_WARPS;
+constexpr int CPT = 128 / (NCW / 4);   // score columns per thread: 64 or 32
+constexpr int NCT = NCW * 32;          // compute threads
+constexpr int BWD_THREADS = (NCW + 4) * 32;
+constexpr int W_MMA_A = NCW, W_MMA_B = NCW + 1, W_TMA = NCW + 2, W_ALLOC = NCW + 3;
 constexpr float LOG2E_B = 1.4426950408889634f;
 
 template <int HD>
@@ -112,16 +122,16 @@ __device__ __forceinline__ uint32_t bwd_setup(uint32_t smem_base, uint8_t *smem_
         }
         mbar_init(bar0 + 8 * C::B_S, 1);
         mbar_init(bar0 + 8 * C::B_DP, 1);
-        mbar_init(bar0 + 8 * C::B_P, 8);
-        mbar_init(bar0 + 8 * C::B_DS, 8);
+        mbar_init(bar0 + 8 * C::B_P, NCW);   // one arrival per compute warp
+        mbar_init(bar0 + 8 * C::B_DS, NCW);
         mbar_init(bar0 + 8 * C::B_ACC, 2);  // one commit from each MMA warp
         fence_mbar_init();
     }
-    if (warp == 11) {
+    if (warp == W_ALLOC) {
         tmem_alloc(smem_u32(tmem_slot), 512);
         tmem_relinquish();
     }
-    if (warp == 10 && lane == 0) {
+    if (warp == W_TMA && lane == 0) {
         prefetch_tensormap(m0);
         prefetch_tensormap(m1);
         prefetch_tensormap(m2);
@@ -164,6 +174,46 @@ __device__ __forceinline__ bool smem_layout_fits(uint32_t raw_base, uint32_t ali
     return false;
 }
 
+__device__ __forceinline__ void compute_reg_alloc()
+{
+    if constexpr (NCW == 8)
+        reg_alloc_232();
+    else
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 104;");  // 16 x 32 x 104 + 4 x 32 x 40 <= 65536
+}
+
+__device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)[16])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+
+// Loads N (16, 32 or 64) consecutive float32 columns of this thread's TMEM lane.
+template <int N>
+__device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, float (&v)[N])
+{
+    if constexpr (N == 16) {
+        uint32_t u[16];
+        tmem_ld_32x32b_x16(taddr, u);
+#pragma unroll
+        for (int x = 0; x < 16; x++) v[x] = __uint_as_float(u[x]);
+    } else {
+#pragma unroll
+        for (int ch = 0; ch < N / 32; ch++) {
+            uint32_t u[32];
+            tmem_ld_32x32b_x32(taddr + ch * 32, u);
+#pragma unroll
+            for (int x = 0; x < 32; x++) v[ch * 32 + x] = __uint_as_float(u[x]);
+        }
+    }
+    tmem_wait_ld();
+}
+
 // Epilogue helpers. A thread owns a whole accumulator row, and storing rows straight to global
 // memory makes every store instruction touch 32 different lines; the results therefore go through
 // shared memory (a resident operand tile that is no longer needed) and leave as coalesced rows.
@@ -174,39 +224,34 @@ __device__ __forceinline__ bool smem_layout_fits(uint32_t raw_base, uint32_t ali
 template <int HD>
 __device__ __forceinline__ void stage_acc(uint32_t tacc, uint8_t *stage, int r, int h, float mul)
 {
-    constexpr int ROWB = HD * 2;
+    constexpr int ROWB = HD * 2, COLS = HD / (NCW / 4);  // columns of this thread: 64, 32 or 16
+    float o[COLS];
+    tmem_ld_cols<COLS>(tacc + h * COLS, o);
 #pragma unroll
-    for (int ch = 0; ch < HD / 64; ch++) {
-        const int col = h * (HD / 2) + ch * 32;
-        uint32_t o[32];
-        tmem_ld_32x32b_x32(tacc + col, o);
-        tmem_wait_ld();
-#pragma unroll
-        for (int q4 = 0; q4 < 4; q4++) {  // 8 columns = one 16-byte chunk
-            uint4 wv;
-            wv.x = pack_bf16(__uint_as_float(o[q4 * 8 + 0]) * mul, __uint_as_float(o[q4 * 8 + 1]) * mul);
-            wv.y = pack_bf16(__uint_as_float(o[q4 * 8 + 2]) * mul, __uint_as_float(o[q4 * 8 + 3]) * mul);
-            wv.z = pack_bf16(__uint_as_float(o[q4 * 8 + 4]) * mul, __uint_as_float(o[q4 * 8 + 5]) * mul);
-            wv.w = pack_bf16(__uint_as_float(o[q4 * 8 + 6]) * mul, __uint_as_float(o[q4 * 8 + 7]) * mul);
-            const int chunk = col / 8 + q4;
-            const int sw = (chunk & ~7) | ((chunk ^ r) & 7);
-            *reinterpret_cast<uint4 *>(stage + r * ROWB + sw * 16) = wv;
-        }
+    for (int q4 = 0; q4 < COLS / 8; q4++) {  // 8 columns = one 16-byte chunk
+        uint4 wv;
+        wv.x = pack_bf16(o[q4 * 8 + 0] * mul, o[q4 * 8 + 1] * mul);
+        wv.y = pack_bf16(o[q4 * 8 + 2] * mul, o[q4 * 8 + 3] * mul);
+        wv.z = pack_bf16(o[q4 * 8 + 4] * mul, o[q4 * 8 + 5] * mul);
+        wv.w = pack_bf16(o[q4 * 8 + 6] * mul, o[q4 * 8 + 7] * mul);
+        const int chunk = h * (COLS / 8) + q4;
+        const int sw = (chunk & ~7) | ((chunk ^ r) & 7);
+        *reinterpret_cast<uint4 *>(stage + r * ROWB + sw * 16) = wv;
     }
 }
 
-// store_staged: after all 256 compute threads have staged (caller synchronises), compute warp w8
-// (0..7) copies rows [16*w8, 16*w8 + 16) of the tile to global memory, whole rows per instruction.
+// store_staged: after all compute threads have staged (caller synchronises), compute warp w8 copies
+// its 128/NCW rows of the tile to global memory, whole rows per instruction.
 // gtile points at row 0 of the tile in the (rows x HD) global matrix; rows >= rows_valid are skipped.
 template <int HD>
 __device__ __forceinline__ void store_staged(const uint8_t *stage, __nv_bfloat16 *gtile, int rows_valid, int w8,
                                              int lane)
 {
-    constexpr int ROWB = HD * 2, CHUNKS = ROWB / 16, ROWS_PER_ST = 32 / CHUNKS;
+    constexpr int ROWB = HD * 2, CHUNKS = ROWB / 16, ROWS_PER_ST = 32 / CHUNKS, ROWS_PER_WARP = 128 / NCW;
     const int chunk = lane % CHUNKS;
 #pragma unroll
-    for (int it = 0; it < 16 / ROWS_PER_ST; it++) {
-        const int rr = w8 * 16 + it * ROWS_PER_ST + lane / CHUNKS;
+    for (int it = 0; it < ROWS_PER_WARP / ROWS_PER_ST; it++) {
+        const int rr = w8 * ROWS_PER_WARP + it * ROWS_PER_ST + lane / CHUNKS;
         const int sw = (chunk & ~7) | ((chunk ^ rr) & 7);
         const uint4 wv = *reinterpret_cast<const uint4 *>(stage + rr * ROWB + sw * 16);
         if (rr < rows_valid) *reinterpret_cast<uint4 *>(gtile + (size_t)rr * HD + chunk * 8) = wv;
@@ -235,19 +280,6 @@ __device__ __forceinline__ void tmem_st_x8(uint32_t taddr, const uint32_t (&r)[8
     asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr), "r"(r[0]),
                  "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
                  : "memory");
-}
-
-// Loads 64 consecutive float32 columns of this thread's TMEM lane.
-__device__ __forceinline__ void tmem_ld_64(uint32_t taddr, float (&v)[64])
-{
-#pragma unroll
-    for (int ch = 0; ch < 2; ch++) {
-        uint32_t u[32];
-        tmem_ld_32x32b_x32(taddr + ch * 32, u);
-#pragma unroll
-        for (int x = 0; x < 32; x++) v[ch * 32 + x] = __uint_as_float(u[x]);
-    }
-    tmem_wait_ld();
 }
 
 // After this warp's TMEM stores (or loads) are complete: one arrival per warp on `bar`.
@@ -288,9 +320,9 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
 
     const uint32_t tmem = bwd_setup<C>(smem_base, smem_gen, warp, lane, &tm_q, &tm_k, &tm_v, &tm_do, EMPTY_B);
 
-    if (warp >= 8) {
+    if (warp >= NCW) {
         reg_dealloc_40();
-        if (warp == 10 && lane == 0) {
+        if (warp == W_TMA && lane == 0) {
             // ---------------------------------------------------------------- TMA producer
             mbar_arrive_expect_tx(BAR(C::B_RES), 2 * C::TILE_BYTES);
             for (int s = 0; s < C::NSUB; s++) {
@@ -315,7 +347,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
                 issued_b = i + 1;
             }
             drain_copies<C>(bar0, issued_a, issued_b);
-        } else if (warp == 8 || warp == 9) {  // all 32 lanes, converged; one elected lane issues
+        } else if (warp == W_MMA_A || warp == W_MMA_B) {  // all 32 lanes, converged; one elected lane issues
             // ---------------------------------------------------------------- MMA issue
             constexpr uint32_t IDESC_SS = idesc_bf16_f32(128, 128, 0, 0);
             constexpr uint32_t IDESC_TS = idesc_bf16_f32(128, HD, 0, 1);
@@ -342,7 +374,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
                 tc_commit_elect(BAR(C::B_DP));
             };
             bool ok = mbar_wait(BAR(C::B_RES), 0, abort_flag, p.status, WB_RES);
-            if (warp == 8) {
+            if (warp == W_MMA_A) {
                 // score chain: S^T(0); then per tile dV(i) (reads P^T, dO) and S^T(i+1) (overwrites P^T)
                 ok = ok && mbar_wait(BAR(C::B_FULLA + 0), 0, abort_flag, p.status, WB_FULL);
                 tc_fence_after();
@@ -394,8 +426,8 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
         }
     } else {
         // -------------------------------------------------------------------- compute
-        reg_alloc_232();
-        const int h = warp / 4;                // which half of the 128 score columns
+        compute_reg_alloc();
+        const int h = warp / 4;                // which CPT-column slice of the 128 score columns
         const int r = threadIdx.x % 128;       // TMEM lane == key row inside the tile
         const int key = k0 + r;
         const uint32_t lane_sel = (uint32_t)((warp % 4) * 32) << 16;
@@ -412,7 +444,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
         auto fetch_raw = [&](int i) -> float {
             const int qrow = (i_begin + i) * 128 + (threadIdx.x & 127);
             float v = 0.f;
-            if (i < n && qrow < p.lq) asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v) : "l"(rowvec_src + qrow));
+            if (threadIdx.x < 256 && i < n && qrow < p.lq) asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v) : "l"(rowvec_src + qrow));
             return v;
         };
         float raw_next = fetch_raw(0);
@@ -421,31 +453,32 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
             float *rv = rowvec + (i & 1) * 256;
             {
                 const bool in_range = q0 + (threadIdx.x & 127) < p.lq;
-                rv[threadIdx.x] = threadIdx.x < 128 ? (in_range ? -raw_next * LOG2E_B : -INFINITY) : (in_range ? raw_next : 0.f);
+                if (threadIdx.x < 256)
+                    rv[threadIdx.x] = threadIdx.x < 128 ? (in_range ? -raw_next * LOG2E_B : -INFINITY) : (in_range ? raw_next : 0.f);
             }
             raw_next = fetch_raw(i + 1);
             // ---- phase 1: P^T = exp2(S^T * c - lse2), bf16 into TMEM for dV += P^T dO
             ok = ok && mbar_wait(BAR(C::B_S), i & 1, abort_flag, p.status, WB_S);
             tc_fence_after();
-            float pv[64];
-            tmem_ld_64(t_s + h * 64, pv);
+            float pv[CPT];
+            tmem_ld_cols<CPT>(t_s + h * CPT, pv);
             // Every thread has read its scores (the bf16 P^T overwrites columns another thread of the
             // same lane still needs) and the lse/delta vectors are visible.
-            named_bar_sync(1, 256);
+            named_bar_sync(1, NCT);
             if (p.causal && (k0 + 127 > q0 + off)) {  // tile crossed by the diagonal: mask before the exp
                 const float masked = c > 0.f ? -INFINITY : INFINITY;
 #pragma unroll
-                for (int cc = 0; cc < 64; cc++)
-                    if (key > q0 + h * 64 + cc + off) pv[cc] = masked;
+                for (int cc = 0; cc < CPT; cc++)
+                    if (key > q0 + h * CPT + cc + off) pv[cc] = masked;
             }
             const f32x2 c2 = pack2(c, c);
 #pragma unroll
-            for (int ch = 0; ch < 4; ch++) {
+            for (int ch = 0; ch < CPT / 16; ch++) {
                 uint32_t pk[8];
 #pragma unroll
                 for (int x = 0; x < 8; x++) {
                     const int cc = ch * 16 + 2 * x;
-                    const int qq = h * 64 + cc;
+                    const int qq = h * CPT + cc;
                     const f32x2 x2 = fma2(pack2(pv[cc], pv[cc + 1]), c2, *reinterpret_cast<const f32x2 *>(&rv[qq]));
                     float p0, p1;
                     exp2_pair(x2, x, p0, p1);
@@ -453,7 +486,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
                     pv[cc + 1] = p1;
                     pk[x] = pack_bf16(p0, p1);
                 }
-                tmem_st_x8(t_s + h * 32 + ch * 8, pk);  // 16 score columns -> 8 packed columns
+                tmem_st_x8(t_s + h * (CPT / 2) + ch * 8, pk);  // 16 score columns -> 8 packed columns
             }
             tmem_wait_st();
             warp_arrive(BAR(C::B_P), lane);
@@ -461,22 +494,22 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
             // ---- phase 2: dS^T = P^T * (dP^T - delta), bf16 into TMEM for dK += dS^T Q
             ok = ok && mbar_wait(BAR(C::B_DP), i & 1, abort_flag, p.status, WB_DP);
             tc_fence_after();
-            float dp[64];
-            tmem_ld_64(t_dp + h * 64, dp);
-            named_bar_sync(2, 256);  // all of dP^T is read before any thread overwrites it with dS^T
+            float dp[CPT];
+            tmem_ld_cols<CPT>(t_dp + h * CPT, dp);
+            named_bar_sync(2, NCT);  // all of dP^T is read before any thread overwrites it with dS^T
 #pragma unroll
-            for (int ch = 0; ch < 4; ch++) {
+            for (int ch = 0; ch < CPT / 16; ch++) {
                 uint32_t pk[8];
 #pragma unroll
                 for (int x = 0; x < 8; x++) {
                     const int cc = ch * 16 + 2 * x;
                     const f32x2 ds2 = mul2(pack2(pv[cc], pv[cc + 1]),
-                                           sub2(pack2(dp[cc], dp[cc + 1]), *reinterpret_cast<const f32x2 *>(&rv[128 + h * 64 + cc])));
+                                           sub2(pack2(dp[cc], dp[cc + 1]), *reinterpret_cast<const f32x2 *>(&rv[128 + h * CPT + cc])));
                     float d0, d1;
                     unpack2(ds2, d0, d1);
                     pk[x] = pack_bf16(d0, d1);
                 }
-                tmem_st_x8(t_dp + h * 32 + ch * 8, pk);
+                tmem_st_x8(t_dp + h * (CPT / 2) + ch * 8, pk);
             }
             tmem_wait_st();
             warp_arrive(BAR(C::B_DS), lane);
@@ -487,7 +520,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
         // resident tiles are dead once the last MMAs have completed.
         stage_acc<HD>(tmem + lane_sel + C::T_ACC0, smem_gen + C::OFF_RES1, r, h, 1.f);
         stage_acc<HD>(tmem + lane_sel + C::T_ACC1, smem_gen + C::OFF_RES0, r, h, p.scale);
-        named_bar_sync(3, 256);
+        named_bar_sync(3, NCT);
         const int rows_valid = ok ? min(128, p.lk - k0) : 0;
         const size_t gtile = ((size_t)bh * p.lk + k0) * HD;
         store_staged<HD>(smem_gen + C::OFF_RES1, p.dv + gtile, rows_valid, warp, lane);
@@ -496,7 +529,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
 
     tc_fence_before();
     __syncthreads();
-    if (warp == 11) tmem_dealloc(tmem, 512);
+    if (warp == W_ALLOC) tmem_dealloc(tmem, 512);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -529,9 +562,9 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
 
     const uint32_t tmem = bwd_setup<C>(smem_base, smem_gen, warp, lane, &tm_q, &tm_k, &tm_v, &tm_do, EMPTY_B);
 
-    if (warp >= 8) {
+    if (warp >= NCW) {
         reg_dealloc_40();
-        if (warp == 10 && lane == 0) {
+        if (warp == W_TMA && lane == 0) {
             mbar_arrive_expect_tx(BAR(C::B_RES), 2 * C::TILE_BYTES);
             for (int s = 0; s < C::NSUB; s++) {
                 tma_load_3d(smem_base + C::OFF_RES0 + s * C::SUB_BYTES, &tm_q, BAR(C::B_RES), s * 64, q0, bh);
@@ -554,7 +587,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
                 issued_b = j + 1;
             }
             drain_copies<C>(bar0, issued_a, issued_b);
-        } else if (warp == 8 || warp == 9) {  // all 32 lanes, converged; one elected lane issues
+        } else if (warp == W_MMA_A || warp == W_MMA_B) {  // all 32 lanes, converged; one elected lane issues
             constexpr uint32_t IDESC_SS = idesc_bf16_f32(128, 128, 0, 0);
             constexpr uint32_t IDESC_TS = idesc_bf16_f32(128, HD, 0, 1);
             const uint32_t qa = smem_base + C::OFF_RES0, doa = smem_base + C::OFF_RES1;
@@ -581,7 +614,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
                 tc_commit_elect(BAR(C::B_EMPTYB + j % C::NB));  // V(j) is only read by dP(j)
             };
             bool ok = mbar_wait(BAR(C::B_RES), 0, abort_flag, p.status, WB_RES);
-            if (warp == 8) {
+            if (warp == W_MMA_A) {
                 // score chain: S(j+1) as soon as the compute warps have copied S(j) out
                 ok = ok && mbar_wait(BAR(C::B_FULLA + 0), 0, abort_flag, p.status, WB_FULL);
                 tc_fence_after();
@@ -623,7 +656,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
             }
         }
     } else {
-        reg_alloc_232();
+        compute_reg_alloc();
         const int h = warp / 4;
         const int r = threadIdx.x % 128;
         const int row = q0 + r;
@@ -640,19 +673,19 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
             // ---- phase 1: P = exp2(S * c - lse2) in registers; S is released as soon as it is read
             ok = ok && mbar_wait(BAR(C::B_S), j & 1, abort_flag, p.status, WB_S);
             tc_fence_after();
-            float pv[64];
-            tmem_ld_64(t_s + h * 64, pv);
+            float pv[CPT];
+            tmem_ld_cols<CPT>(t_s + h * CPT, pv);
             warp_arrive(BAR(C::B_P), lane);
             if (j * 128 + 127 > limit_tile) {  // tile crossed by the diagonal or the end of the keys
                 const float masked = c > 0.f ? -INFINITY : INFINITY;
-                const int kbase = j * 128 + h * 64;
+                const int kbase = j * 128 + h * CPT;
 #pragma unroll
-                for (int cc = 0; cc < 64; cc++)
+                for (int cc = 0; cc < CPT; cc++)
                     if (kbase + cc > limit_row) pv[cc] = masked;
             }
             const f32x2 c2 = pack2(c, c), nl2 = pack2(-lse2, -lse2);
 #pragma unroll
-            for (int x = 0; x < 32; x++) {
+            for (int x = 0; x < CPT / 2; x++) {
                 const f32x2 x2 = fma2(pack2(pv[2 * x], pv[2 * x + 1]), c2, nl2);
                 float p0, p1;
                 exp2_pair(x2, x, p0, p1);
@@ -662,12 +695,12 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
             // ---- phase 2: dS = P * (dP - delta), bf16 into TMEM for dQ += dS K
             ok = ok && mbar_wait(BAR(C::B_DP), j & 1, abort_flag, p.status, WB_DP);
             tc_fence_after();
-            float dp[64];
-            tmem_ld_64(t_dp + h * 64, dp);
-            named_bar_sync(1, 256);  // all of dP is read before any thread overwrites it with dS
+            float dp[CPT];
+            tmem_ld_cols<CPT>(t_dp + h * CPT, dp);
+            named_bar_sync(1, NCT);  // all of dP is read before any thread overwrites it with dS
             const f32x2 dl2 = pack2(dl, dl);
 #pragma unroll
-            for (int ch = 0; ch < 4; ch++) {
+            for (int ch = 0; ch < CPT / 16; ch++) {
                 uint32_t pk[8];
 #pragma unroll
                 for (int x = 0; x < 8; x++) {
@@ -677,7 +710,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
                     unpack2(ds2, d0, d1);
                     pk[x] = pack_bf16(d0, d1);
                 }
-                tmem_st_x8(t_dp + h * 32 + ch * 8, pk);
+                tmem_st_x8(t_dp + h * (CPT / 2) + ch * 8, pk);
             }
             tmem_wait_st();
             warp_arrive(BAR(C::B_DS), lane);
@@ -686,14 +719,14 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
         tc_fence_after();
         // dQ (times the softmax scale) through the Q tile's buffer, which is dead by now.
         stage_acc<HD>(tmem + lane_sel + C::T_ACC0, smem_gen + C::OFF_RES0, r, h, p.scale);
-        named_bar_sync(3, 256);
+        named_bar_sync(3, NCT);
         store_staged<HD>(smem_gen + C::OFF_RES0, p.dq + ((size_t)bh * p.lq + q0) * HD, ok ? min(128, p.lq - q0) : 0, warp,
                          lane);
     }
 
     tc_fence_before();
     __syncthreads();
-    if (warp == 11) tmem_dealloc(tmem, 512);
+    if (warp == W_ALLOC) tmem_dealloc(tmem, 512);
 }
 
 template <int HD>
