@@ -35,6 +35,7 @@ SIGNATURES = {
     "ember_status_string": (ctypes.c_char_p, [_i]),
     "ember_last_error": (ctypes.c_char_p, []),
     "ember_check_device_status": (_i, [_vp, ctypes.POINTER(_i)]),
+    "ember_selftest_wait_timeout": (_i, [_vp]),
     "ember_attention_fwd": (_i, [_vp] * 5 + [_i] * 4 + [_f, _i, _i, _vp]),
     "ember_attention_bwd": (_i, [_vp] * 9 + [_i] * 4 + [_f, _i, _i, _vp, _sz, _vp]),
     "ember_attention_decode": (_i, [_vp] * 5 + [_i] * 3 + [_f, _i, _i, _vp, _sz, _vp]),

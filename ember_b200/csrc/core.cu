@@ -5,6 +5,7 @@
 #include <string.h>
 
 #include "common.cuh"
+#include "ptx.cuh"
 
 namespace ember {
 
@@ -71,6 +72,23 @@ __global__ void convert_kernel(const In *__restrict__ src, Out *__restrict__ dst
         else
             dst[i] = __bfloat162float(src[i]);
     }
+}
+
+// One warp waits on an mbarrier that nothing ever arrives at, with a limit of about a millisecond:
+// the bounded wait gives up, records EMBER_ERR_TIMEOUT with wait code 9001 in the status word and
+// the kernel returns normally. Exercises the failure path of every kernel's waits without a fault.
+__global__ void selftest_wait_timeout_kernel(DeviceStatus *status)
+{
+    __shared__ __align__(8) unsigned long long bar_storage;
+    __shared__ int abort_flag;
+    const uint32_t bar = ptx::smem_u32(&bar_storage);
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        ptx::mbar_init(bar, 1);
+        ptx::fence_mbar_init();
+    }
+    __syncthreads();
+    ptx::mbar_wait(bar, 0, &abort_flag, status, 9001, 2LL * 1000 * 1000);
 }
 
 }  // namespace ember
@@ -187,6 +205,15 @@ const char *ember_status_string(int status)
 }
 
 const char *ember_last_error(void) { return g_err; }
+
+int ember_selftest_wait_timeout(void *stream)
+{
+    DeviceState *st = device_state();
+    if (!st) return EMBER_ERR_CUDA;
+    selftest_wait_timeout_kernel<<<1, 32, 0, pick_stream(stream, st)>>>(st->status);
+    EMBER_CUDA_TRY(cudaGetLastError());
+    return EMBER_OK;
+}
 
 int ember_check_device_status(void *stream, int *where)
 {

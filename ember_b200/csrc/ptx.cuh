@@ -76,14 +76,15 @@ constexpr long long kWaitLimitCycles = 400LL * 1000 * 1000;
 // already gave up, signalled through *abort_flag in shared memory) records the failure and
 // returns false; the caller carries on so that the CTA still reaches its common exit.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag,
-                                          DeviceStatus *status, int where)
+                                          DeviceStatus *status, int where,
+                                          long long limit_cycles = kWaitLimitCycles)
 {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     for (;;) {
         if (mbar_try_wait(bar, parity)) return true;
         if (*abort_flag) return false;
-        if (clock64() - t0 > kWaitLimitCycles) {
+        if (clock64() - t0 > limit_cycles) {
             *abort_flag = 1;
             if (atomicCAS(&status->code, 0, EMBER_ERR_TIMEOUT) == 0) {
                 status->where = where;

@@ -84,6 +84,12 @@ EMBER_API const char *ember_last_error(void);
  * the code of the wait that gave up (0 if none). */
 EMBER_API int ember_check_device_status(void *stream, int *where);
 
+/* Self-test of the failure path (no counterpart in the reference): launches one warp that waits on
+ * a barrier nobody arrives at; its bounded wait gives up after about a millisecond and reports
+ * through the status word, so the next ember_check_device_status returns EMBER_ERR_TIMEOUT with
+ * *where == 9001. Nothing faults or hangs and the context stays usable. */
+EMBER_API int ember_selftest_wait_timeout(void *stream);
+
 /* ---- attention forward (prefill, optionally causal). Replaces the composed
  *      reference path  softmax((q @ kT) * scale [+ mask]) @ v :
  *      ember/tensor/tensor.py:163-197 (__matmul__) -> src/tensor/tensor_api.c:330-354

@@ -207,3 +207,22 @@ def test_layer_forward_backward_contract():
     layer.reset()
     with pytest.raises(RuntimeError):
         layer.backward(em.Tensor(g))
+
+
+# ---------------------------------------------------------------- failure detection (no GPU fault)
+def test_bounded_wait_reports_timeout_and_context_survives():
+    L = _lib.lib()
+    where = _lib.ctypes.c_int(0)
+    assert L.ember_check_device_status(None, _lib.ctypes.byref(where)) == 0  # clean to begin with
+    _lib.check(L.ember_selftest_wait_timeout(None))  # a wait on a barrier that nothing sets
+    rc = L.ember_check_device_status(None, _lib.ctypes.byref(where))
+    assert rc == _lib.EMBER_ERR_TIMEOUT and where.value == 9001
+    assert b"device-side wait gave up" in L.ember_last_error()
+    with pytest.raises(RuntimeError):
+        _lib.check(rc)
+    # the status word was cleared and the context is still usable
+    assert L.ember_check_device_status(None, _lib.ctypes.byref(where)) == 0
+    q, k, v = (bf16_round(seeded((1, 1, 256, 128), s, 0.5)) for s in (1, 2, 3))
+    ro, _ = cpu_oracle.attention_fwd(q, k, v, None, True)
+    o, _ = run_fwd(q, k, v, None, True, "bfloat16")
+    assert np.abs(o - ro).max() <= BF16_TOL
