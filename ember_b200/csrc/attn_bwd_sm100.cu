@@ -93,6 +93,7 @@ struct BwdParams {
     int lq, lk, causal;
     float scale, scale_log2;
     DeviceStatus *status;
+    WorkOrder order;  // set per launch
 };
 
 __device__ __forceinline__ void named_bar_sync(int id, int count)
@@ -312,8 +313,9 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
     float *rowvec = reinterpret_cast<float *>(smem_gen + C::OFF_ROWVEC);
 
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
-    const int bh = blockIdx.x;
-    const int k0 = blockIdx.y * 128;
+    int bh, rank;
+    work_item(p.order, blockIdx.x, bh, rank);
+    const int k0 = rank * 128;  // under a causal mask the first key blocks are seen by the most queries
     const int off = p.lk - p.lq;
     const int i_begin = p.causal ? max(0, k0 - off) / 128 : 0;  // first query tile that sees key k0
     const int n = (p.lq + 127) / 128 - i_begin;
@@ -553,8 +555,9 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
         reinterpret_cast<volatile int *>(smem_gen + C::OFF_BAR + 8 * C::NUM_BARS + 4);
 
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
-    const int bh = blockIdx.x;
-    const int qtile = gridDim.y - 1 - blockIdx.y;  // heaviest causal tiles first
+    int bh, rank;
+    work_item(p.order, blockIdx.x, bh, rank);
+    const int qtile = p.order.blocks - 1 - rank;  // heaviest causal tiles first
     const int q0 = qtile * 128;
     const int off = p.lk - p.lq;
     const int visible = p.causal ? min(p.lk, q0 + 128 + off) : p.lk;
@@ -756,9 +759,11 @@ int launch(const AttnArgs &a, float *delta, DeviceState *st, cudaStream_t s)
     auto k2 = sm100_bwd_dq_kernel<HD>;
     EMBER_CUDA_TRY(cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
     EMBER_CUDA_TRY(cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
-    k1<<<dim3(a.bh, (a.lk + 127) / 128), BWD_THREADS, C::SMEM_BYTES, s>>>(tq, tk, tv, tdo, p);
+    p.order = make_work_order(a.bh, (a.lk + 127) / 128, st->sm_count);
+    k1<<<dim3((unsigned)(p.order.units * p.order.blocks)), BWD_THREADS, C::SMEM_BYTES, s>>>(tq, tk, tv, tdo, p);
     EMBER_CUDA_TRY(cudaGetLastError());
-    k2<<<dim3(a.bh, (a.lq + 127) / 128), BWD_THREADS, C::SMEM_BYTES, s>>>(tq, tk, tv, tdo, p);
+    p.order = make_work_order(a.bh, (a.lq + 127) / 128, st->sm_count);
+    k2<<<dim3((unsigned)(p.order.units * p.order.blocks)), BWD_THREADS, C::SMEM_BYTES, s>>>(tq, tk, tv, tdo, p);
     EMBER_CUDA_TRY(cudaGetLastError());
     return EMBER_OK;
 }
@@ -770,7 +775,8 @@ bool sm100_bwd_supported(const AttnArgs &a)
     if (a.dtype != EMBER_BF16) return false;
     if (a.d != 64 && a.d != 128) return false;
     if (!isfinite(a.scale)) return false;
-    if ((a.lq + 127) / 128 > 65535 || (a.lk + 127) / 128 > 65535) return false;
+    if ((long long)a.bh * ((a.lq + 127) / 128) > 0x7fffffffLL || (long long)a.bh * ((a.lk + 127) / 128) > 0x7fffffffLL)
+        return false;
     // TMA needs 16-byte aligned bases; the epilogues store 16-byte vectors.
     const uintptr_t bits = (uintptr_t)a.q | (uintptr_t)a.k | (uintptr_t)a.v | (uintptr_t)a.dout |
                            (uintptr_t)a.dq | (uintptr_t)a.dk | (uintptr_t)a.dv;

@@ -79,6 +79,7 @@ struct FwdParams {
     int causal;
     float scale_log2;  // scale * log2(e)
     DeviceStatus *status;
+    WorkOrder order;
 };
 
 // EMU: of every 4 pairs of exponentials, how many are evaluated as a polynomial on the FMA pipe
@@ -101,8 +102,9 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
-    const int bh = blockIdx.x;
-    const int qblock = gridDim.y - 1 - blockIdx.y;  // heaviest (latest) causal rows first
+    int bh, rank;
+    work_item(p.order, blockIdx.x, bh, rank);
+    const int qblock = p.order.blocks - 1 - rank;  // heaviest (latest) causal rows first
     const int q_base = qblock * 256;
     const int off = p.lk - p.lq;
 
@@ -462,7 +464,8 @@ int launch(const AttnArgs &a, DeviceState *st, cudaStream_t s)
     p.status = st->status;
     auto kern = sm100_fwd_kernel<HD, EMU>;
     EMBER_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
-    dim3 grid(a.bh, (a.lq + 255) / 256);
+    p.order = make_work_order(a.bh, (a.lq + 255) / 256, st->sm_count);
+    dim3 grid((unsigned)(p.order.units * p.order.blocks));
     kern<<<grid, FWD_THREADS, C::SMEM_BYTES, s>>>(tq, tk, tv, p);
     EMBER_CUDA_TRY(cudaGetLastError());
     return EMBER_OK;
@@ -475,7 +478,7 @@ bool sm100_fwd_supported(const AttnArgs &a)
     if (a.dtype != EMBER_BF16) return false;
     if (a.d != 64 && a.d != 128) return false;
     if (!(a.scale != 0.f) || !isfinite(a.scale)) return false;
-    if ((a.lq + 255) / 256 > 65535) return false;
+    if ((long long)a.bh * ((a.lq + 255) / 256) > 0x7fffffffLL) return false;
     // TMA needs 16-byte aligned bases; the epilogue stores 16-byte vectors.
     const uintptr_t bits = (uintptr_t)a.q | (uintptr_t)a.k | (uintptr_t)a.v;
     return (bits & 15) == 0 && ((uintptr_t)a.out & 15) == 0;
