@@ -367,9 +367,9 @@ def run_gpu_arm(args):
         "roofline": {"bound": "tensor", "achieved": flops_step / (ms_step * 1e-3) / 1e12, "peak": peaks["bf16_tflops"],
                      "unit": "TFLOP/s", "frac": flops_step / (ms_step * 1e-3) / 1e12 / peaks["bf16_tflops"],
                      # dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of the B=2 H=32 case
-                     # (592.4 MB), scaled by the (batch*head) units of this launch: traffic grows in
+                     # (252.1 MB), scaled by the (batch*head) units of this launch: traffic grows in
                      # proportion because every head is an independent problem.
-                     "traffic": 592.4e6 * (B * H) / 64.0, "traffic_unit": "bytes/launch",
+                     "traffic": 252.1e6 * (B * H) / 64.0, "traffic_unit": "bytes/launch",
                      "algorithmic_bytes": 4 * B * H * S * D * 2 + B * H * S * 4, "peak_source": peaks["source"] + " burst cuBLAS bf16",
                      "frac_of_nominal_2250": flops_step / (ms_step * 1e-3) / 1e12 / NOMINAL_BF16_TFLOPS,
                      "frac_of_sustained": flops_step / (ms_step * 1e-3) / 1e12 / peaks["bf16_tflops_sustained"]},

@@ -759,10 +759,11 @@ int launch(const AttnArgs &a, float *delta, DeviceState *st, cudaStream_t s)
     auto k2 = sm100_bwd_dq_kernel<HD>;
     EMBER_CUDA_TRY(cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
     EMBER_CUDA_TRY(cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
-    p.order = make_work_order(a.bh, (a.lk + 127) / 128, st->sm_count);
+    const size_t touched = ((size_t)a.lq + a.lk) * HD * 2 * 4;  // Q, dO, dQ, K, V, dK, dV and the row vectors
+    p.order = make_work_order(a.bh, (a.lk + 127) / 128, st->sm_count, touched, a.causal != 0);
     k1<<<dim3((unsigned)(p.order.units * p.order.blocks)), BWD_THREADS, C::SMEM_BYTES, s>>>(tq, tk, tv, tdo, p);
     EMBER_CUDA_TRY(cudaGetLastError());
-    p.order = make_work_order(a.bh, (a.lq + 127) / 128, st->sm_count);
+    p.order = make_work_order(a.bh, (a.lq + 127) / 128, st->sm_count, touched, a.causal != 0);
     k2<<<dim3((unsigned)(p.order.units * p.order.blocks)), BWD_THREADS, C::SMEM_BYTES, s>>>(tq, tk, tv, tdo, p);
     EMBER_CUDA_TRY(cudaGetLastError());
     return EMBER_OK;

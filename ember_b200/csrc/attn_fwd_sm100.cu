@@ -464,7 +464,8 @@ int launch(const AttnArgs &a, DeviceState *st, cudaStream_t s)
     p.status = st->status;
     auto kern = sm100_fwd_kernel<HD, EMU>;
     EMBER_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
-    p.order = make_work_order(a.bh, (a.lq + 255) / 256, st->sm_count);
+    p.order = make_work_order(a.bh, (a.lq + 255) / 256, st->sm_count, ((size_t)a.lq + a.lk) * HD * 2 * 2,  // Q, O, K, V
+                              a.causal != 0);
     dim3 grid((unsigned)(p.order.units * p.order.blocks));
     kern<<<grid, FWD_THREADS, C::SMEM_BYTES, s>>>(tq, tk, tv, p);
     EMBER_CUDA_TRY(cudaGetLastError());

@@ -54,25 +54,37 @@ inline cudaStream_t pick_stream(void *stream, DeviceState *st)
 
 // Order in which the CTAs of the tensor-core kernels take their work. A work item is one block of
 // rows (query rows, or key rows in the dK/dV pass) of one (batch*head) unit. Units are taken in
-// groups that fill the SMs about once; inside a group the heaviest blocks of every unit come first
-// (rank 0 = heaviest under a causal mask). CTAs that run at the same time then belong to a few
-// units, whose K and V (a few MB) stay in L2 while all the blocks of the unit stream them, instead
-// of every resident CTA streaming a different unit's tensors from HBM.
+// groups; inside a group the heaviest blocks of every unit come first (rank 0 = heaviest under a
+// causal mask), so a group behaves like a longest-job-first schedule. CTAs that run at the same
+// time then belong to a few units whose tensors stay in L2 (126 MB) while all the blocks of the unit
+// read them, instead of every resident CTA pulling a different unit's K and V from HBM.
+// A group always has enough units to fill the SMs once. Without a mask all blocks weigh the same
+// and that minimum is used. Under a causal mask larger groups balance better (the heavy blocks of
+// the last group start that much earlier), so a group takes as many units as touch about 64 MB, and
+// a short last group is merged into the one before it.
 struct WorkOrder {
-    int units;   // batch * heads
-    int blocks;  // blocks per unit
-    int group;   // units per group
+    int units;    // batch * heads
+    int blocks;   // blocks per unit
+    int group;    // units per group (the last group has units - (ngroups - 1) * group)
+    int ngroups;
 };
 
-inline WorkOrder make_work_order(int units, int blocks, int sm_count)
+inline WorkOrder make_work_order(int units, int blocks, int sm_count, size_t touched_bytes_per_unit, bool causal)
 {
     WorkOrder w;
     w.units = units;
     w.blocks = blocks;
     const int sms = sm_count > 0 ? sm_count : 148;
-    w.group = (sms + blocks - 1) / blocks;
-    if (w.group < 1) w.group = 1;
-    if (w.group > units) w.group = units;
+    long long g = (sms + blocks - 1) / blocks;
+    if (causal) {
+        const long long by_l2 = (long long)((64ull << 20) / (touched_bytes_per_unit ? touched_bytes_per_unit : 1));
+        if (by_l2 > g) g = by_l2;
+    }
+    if (g < 1) g = 1;
+    if (g > units) g = units;
+    w.group = (int)g;
+    // the last group holds the remainder: merged into the one before it under a causal mask
+    w.ngroups = causal ? units / w.group : (units + w.group - 1) / w.group;
     return w;
 }
 
@@ -80,8 +92,9 @@ inline WorkOrder make_work_order(int units, int blocks, int sm_count)
 __device__ __forceinline__ void work_item(const WorkOrder &w, int idx, int &unit, int &rank)
 {
     const int per_group = w.group * w.blocks;
-    const int g = idx / per_group, rem = idx - g * per_group;
-    const int units_here = min(w.group, w.units - g * w.group);
+    const int g = min(idx / per_group, w.ngroups - 1);
+    const int rem = idx - g * per_group;
+    const int units_here = (g == w.ngroups - 1) ? w.units - g * w.group : w.group;
     rank = rem / units_here;
     unit = g * w.group + (rem - rank * units_here);
 }
