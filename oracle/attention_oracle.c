@@ -250,3 +250,62 @@ void oracle_attention_bwd(const float *q, const float *k, const float *v, const 
     args_t a = {q, k, v, dout, NULL, NULL, NULL, dq, dk, dv, lq, lk, d, causal, scale};
     for_each_slice(bh, bwd_one, &a);
 }
+
+/* ------------------------------------------------------------------------
+ * The layer either side of attention: the reference's Linear
+ * (ember/nn/layers.py:45-56).
+ *
+ *     forward   y      = b + x @ w             x (m,k), w (k,n), b (n)
+ *     backward  grad_w = x^T @ grad_y          transpose on the host, then matmul
+ *               grad_b = sum(grad_y, axis=0)   fp32, rows added top to bottom
+ *               grad_x = grad_y @ w^T
+ *
+ * matmul: src/tensor/operators_cpu.c:47-60 (double accumulator); broadcast add:
+ * src/tensor/operators.def:65; sum over axis 0: src/tensor/operators_cpu.c:92-105.
+ * Rows of the result are independent, so the worker pool splits them in blocks.
+ * ------------------------------------------------------------------------ */
+typedef struct {
+    const float *a, *b, *bias;
+    float *out;
+    int n, m, k, rows_per_block;
+} mm_args_t;
+
+static void mm_block(int blk, void *ctx)
+{
+    const mm_args_t *g = (const mm_args_t *)ctx;
+    const int r0 = blk * g->rows_per_block;
+    const int r1 = r0 + g->rows_per_block < g->n ? r0 + g->rows_per_block : g->n;
+    mm(g->a + (size_t)r0 * g->k, g->b, g->out + (size_t)r0 * g->m, r1 - r0, g->m, g->k);
+    if (g->bias)
+        for (int i = r0; i < r1; i++)
+            for (int j = 0; j < g->m; j++) g->out[(size_t)i * g->m + j] = g->bias[j] + g->out[(size_t)i * g->m + j];
+}
+
+static void mm_threaded(const float *a, const float *b, const float *bias, float *out, int n, int m, int k)
+{
+    mm_args_t g = {a, b, bias, out, n, m, k, 8};
+    for_each_slice((n + g.rows_per_block - 1) / g.rows_per_block, mm_block, &g);
+}
+
+void oracle_linear_fwd(const float *x, const float *w, const float *b, float *y, int m, int n, int k)
+{
+    mm_threaded(x, w, b, y, m, n, k);
+}
+
+void oracle_linear_bwd(const float *x, const float *w, const float *dy, float *dx, float *dw, float *db,
+                       int m, int n, int k)
+{
+    float *xt = (float *)malloc((size_t)m * k * sizeof(float));
+    float *wt = (float *)malloc((size_t)k * n * sizeof(float));
+    tr(x, xt, m, k);                      /* (k, m) */
+    tr(w, wt, k, n);                      /* (n, k) */
+    mm_threaded(xt, dy, NULL, dw, k, n, m);
+    for (int j = 0; j < n; j++) {
+        float s = 0.0f;
+        for (int r = 0; r < m; r++) s += dy[(size_t)r * n + j];
+        db[j] = s;
+    }
+    mm_threaded(dy, wt, NULL, dx, m, k, n);
+    free(xt);
+    free(wt);
+}

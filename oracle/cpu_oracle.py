@@ -36,6 +36,10 @@ def lib() -> ctypes.CDLL:
         L.oracle_attention_fwd.restype = None
         L.oracle_attention_bwd.argtypes = [_f32p] * 7 + [ctypes.c_int] * 4 + [ctypes.c_float, ctypes.c_int]
         L.oracle_attention_bwd.restype = None
+        L.oracle_linear_fwd.argtypes = [_f32p] * 4 + [ctypes.c_int] * 3
+        L.oracle_linear_fwd.restype = None
+        L.oracle_linear_bwd.argtypes = [_f32p] * 6 + [ctypes.c_int] * 3
+        L.oracle_linear_bwd.restype = None
         L.oracle_set_threads.argtypes = [ctypes.c_int]
         _LIB = L
     return _LIB
@@ -82,3 +86,24 @@ def attention_bwd(q, k, v, dout, scale=None, causal=False):
     lib().oracle_attention_bwd(_p(q), _p(k), _p(v), _p(dout), _p(dq), _p(dk), _p(dv), bh, lq, lk, d,
                                float(scale), int(bool(causal)))
     return dq, dk, dv
+
+
+def linear_fwd(x, w, b=None):
+    """y = b + x @ w of the reference's Linear layer; x (m,k), w (k,n), b (n) or None."""
+    x, w = _prep(x), _prep(w)
+    m, k = x.shape
+    n = w.shape[1]
+    bb = _prep(b).reshape(n) if b is not None else None
+    y = np.empty((m, n), dtype=np.float32)
+    lib().oracle_linear_fwd(_p(x), _p(w), _p(bb), _p(y), m, n, k)
+    return y
+
+
+def linear_bwd(x, w, dy):
+    """Returns (grad_x, grad_w, grad_b) of the reference's Linear.backward."""
+    x, w, dy = _prep(x), _prep(w), _prep(dy)
+    m, k = x.shape
+    n = w.shape[1]
+    dx, dw, db = np.empty((m, k), np.float32), np.empty((k, n), np.float32), np.empty((n,), np.float32)
+    lib().oracle_linear_bwd(_p(x), _p(w), _p(dy), _p(dx), _p(dw), _p(db), m, n, k)
+    return dx, dw, db

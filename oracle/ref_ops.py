@@ -146,3 +146,28 @@ def attention_bwd(q, k, v, dout, scale=None, causal=False):
         dq[b] = _mm(ds, k2[b])
         dk[b] = _mm(np.ascontiguousarray(ds.T), q2[b])
     return dq.reshape(q.shape), dk.reshape(k.shape), dv.reshape(v.shape)
+
+
+def linear_fwd(x, w, b=None):
+    """The reference's Linear.forward (ember/nn/layers.py:45-48) on its compiled C operators."""
+    x, w = (np.ascontiguousarray(t, np.float32) for t in (x, w))
+    y = _mm(x, w)
+    if b is None:
+        return y
+    b2 = np.ascontiguousarray(b, np.float32).reshape(1, -1)
+    m, n = y.shape
+    out = np.empty_like(y)
+    # b + (x @ w): the bias is the first operand, broadcast over the rows
+    lib().add_broadcasted(_p(b2), _p(y), _p(out), _ia((m, n)), _ia((0, 1)), _ia((n, 1)), 2)
+    return out
+
+
+def linear_bwd(x, w, dy):
+    """The reference's Linear.backward (ember/nn/layers.py:50-56): host transposes, C matmuls, sum over axis 0."""
+    x, w, dy = (np.ascontiguousarray(t, np.float32) for t in (x, w, dy))
+    m, n = dy.shape
+    dw = _mm(np.ascontiguousarray(x.T), dy)
+    db = np.empty((n,), np.float32)
+    lib().sum_axis(_p(dy), _p(db), 1, n, m)
+    dx = _mm(dy, np.ascontiguousarray(w.T))
+    return dx, dw, db

@@ -26,6 +26,22 @@ def golden():
     return np.load(os.path.join(ROOT, "tests", "golden", "attention_golden.npz"))
 
 
+@pytest.fixture(scope="session")
+def linear_golden():
+    return np.load(os.path.join(ROOT, "tests", "golden", "linear_golden.npz"))
+
+
+def linear_golden_inputs(meta):
+    """x, w, b (None when the case has no bias), upstream gradient of one linear_golden.npz case."""
+    from inputs import normal
+
+    m, k, n, seed, with_bias = (int(x) for x in meta)
+    x = normal(seed, (m, k))
+    w = normal(seed + 1, (k, n)) * np.float32(0.1)
+    b = normal(seed + 2, (n,)) if with_bias else None
+    return x, w, b, normal(seed + 3, (m, n))
+
+
 def golden_inputs(meta, with_dout=False):
     from inputs import normal
 

@@ -44,6 +44,15 @@ CASES = {
 }
 
 
+LINEAR_CASES = {
+    # name: (m, k, n, seed, with_bias) -- the reference's own Linear layer (ember/nn/layers.py:9-56)
+    "lin_small": (5, 7, 3, 11, True),
+    "lin_tile": (128, 64, 256, 12, True),
+    "lin_ragged": (130, 257, 66, 13, True),
+    "lin_nobias": (96, 160, 72, 14, False),
+}
+
+
 def import_reference():
     tmp = tempfile.mkdtemp(prefix="ember_ref_")
     shutil.copytree(os.path.join(REF, "ember"), os.path.join(tmp, "ember"))
@@ -96,6 +105,23 @@ def main():
             out[name + "/dq"], out[name + "/dk"], out[name + "/dv"] = dq.to_np(), dk.to_np(), dv.to_np()
         print(name, "ok", out[name + "/out"].shape)
     np.savez_compressed(os.path.join(HERE, "attention_golden.npz"), **out)
+
+    # The reference's Linear layer: weights w = 0.1*N(0,1) (seed+1), bias N(0,1) (seed+2, or the
+    # layer's own zeros), input N(0,1) (seed), upstream gradient N(0,1) (seed+3).
+    lin = {}
+    for name, (m, k, n, seed, with_bias) in LINEAR_CASES.items():
+        layer = em.nn.Linear(k, n)
+        layer.w = T(normal(seed + 1, (k, n)) * np.float32(0.1))
+        if with_bias:
+            layer.b = T(normal(seed + 2, (n,)))
+        y = layer(T(normal(seed, (m, k))), True)
+        gx = layer.backward(T(normal(seed + 3, (m, n))))
+        gw, gb = layer.gradients()
+        lin[name + "/meta"] = np.array([m, k, n, seed, int(with_bias)], np.int64)
+        lin[name + "/y"], lin[name + "/gx"], lin[name + "/gw"], lin[name + "/gb"] = (
+            y.to_np(), gx.to_np(), gw.to_np(), gb.to_np())
+        print(name, "ok", lin[name + "/y"].shape)
+    np.savez_compressed(os.path.join(HERE, "linear_golden.npz"), **lin)
 
 
 if __name__ == "__main__":

@@ -3,7 +3,7 @@ own compiled operators (when that build is present) and against float64 NumPy.""
 import numpy as np
 import pytest
 
-from conftest import golden_inputs, seeded
+from conftest import golden_inputs, linear_golden_inputs, seeded
 from oracle import cpu_oracle, ref_ops
 
 CASES = ["c1_fwd_f32", "c1_causal", "ragged_causal", "ragged_noncausal", "decode", "d128"]
@@ -77,3 +77,28 @@ def test_oracle_threads_do_not_change_bits():
     finally:
         cpu_oracle.set_threads(1)
     assert np.array_equal(a, b)
+
+
+LINEAR_CASES = ["lin_small", "lin_tile", "lin_ragged", "lin_nobias"]
+
+
+@pytest.mark.parametrize("name", LINEAR_CASES)
+def test_linear_oracle_matches_golden_bit_for_bit(linear_golden, name):
+    """The golden file was produced by the reference's own Linear layer (forward, backward, gradients)."""
+    x, w, b, dy = linear_golden_inputs(linear_golden[name + "/meta"])
+    y = cpu_oracle.linear_fwd(x, w, b)
+    assert np.array_equal(y, linear_golden[name + "/y"])
+    dx, dw, db = cpu_oracle.linear_bwd(x, w, dy)
+    assert np.array_equal(dx, linear_golden[name + "/gx"])
+    assert np.array_equal(dw, linear_golden[name + "/gw"])
+    assert np.array_equal(db, linear_golden[name + "/gb"])
+
+
+@pytest.mark.skipif(not ref_ops.available(), reason="oracle/_ref not built (needs the reference checkout)")
+@pytest.mark.parametrize("mkn", [(1, 1, 1), (33, 65, 17), (64, 128, 96)])
+def test_linear_oracle_matches_compiled_reference_ops(mkn):
+    m, k, n = mkn
+    x, w, b, dy = seeded((m, k), 1), seeded((k, n), 2, 0.1), seeded((n,), 3), seeded((m, n), 4)
+    assert np.array_equal(cpu_oracle.linear_fwd(x, w, b), ref_ops.linear_fwd(x, w, b))
+    for a, c in zip(cpu_oracle.linear_bwd(x, w, dy), ref_ops.linear_bwd(x, w, dy)):
+        assert np.array_equal(a, c)
