@@ -9,9 +9,11 @@ without the built CUDA library raises ImportError with the build command.
 """
 import importlib
 
-__all__ = ["Tensor", "attention", "attention_forward", "attention_backward", "attention_decode", "nn"]
+__all__ = ["Tensor", "attention", "attention_forward", "attention_backward", "attention_decode", "linear_forward",
+           "linear_backward", "nn"]
 
-_TENSOR_NAMES = {"Tensor", "attention", "attention_forward", "attention_backward", "attention_decode"}
+_TENSOR_NAMES = {"Tensor", "attention", "attention_forward", "attention_backward", "attention_decode", "linear_forward",
+                 "linear_backward"}
 
 
 def __getattr__(name):

@@ -96,11 +96,6 @@ struct BwdParams {
     WorkOrder order;  // set per launch
 };
 
-__device__ __forceinline__ void named_bar_sync(int id, int count)
-{
-    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
-}
-
 // Common prologue: barriers, TMEM allocation, tensor-map prefetch. Returns the TMEM base.
 template <typename C>
 __device__ __forceinline__ uint32_t bwd_setup(uint32_t smem_base, uint8_t *smem_gen, int warp, int lane,

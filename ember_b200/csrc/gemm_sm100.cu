@@ -1,0 +1,319 @@
+// Projection GEMM for sm_100a: C (m x n) = op(A) * op(B) [+ bias], bf16 in and out, float32
+// accumulation in tensor memory. It serves the Linear layers either side of attention:
+//   forward          y  = x * w + b          (NN; y may be written head-major: the layout attention reads)
+//   input gradient   dx = dy * w^T           (NT)
+//   weight gradient  dw = x^T * dy           (TN)
+// where x, dy and y may lie head-major (parts, batch, heads, seq, dim) instead of row-major, so that
+// no transpose kernel runs between a projection and attention.
+//
+// Persistent kernel, one CTA per SM, 128 x 256 output tiles, K in steps of 64:
+//   warps 0-3  epilogue: accumulator (TMEM) + bias -> bf16 -> shared memory -> coalesced rows
+//   warp  4    TMEM allocation, then MMA issue (warp-collective, one elected lane):
+//              tcgen05.mma M=128 N=256 K=16, four per K step
+//   warp  5    TMA producer (one lane): a ring of 4 stages of A (16 KB) and B (32 KB) tiles
+// Two accumulators of 256 columns (all 512 TMEM columns): the MMAs of the next tile run while the
+// epilogue drains the previous one.
+// Operand tiles in shared memory use the 128-byte swizzle. An operand whose contraction index runs
+// along its memory rows (K-major: A of NN/NT, B of NT) is one TMA box of 64 k x (128 | 256) rows;
+// one whose contraction index runs across rows (MN-major: A of TN, B of NN/TN) is stored as
+// sub-tiles of 64 k-rows x 64 columns, 8 KB apart.
+#include "common.cuh"
+#include "kernels.cuh"
+#include "ptx.cuh"
+
+namespace ember {
+
+namespace {
+
+using namespace ptx;
+
+constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
+constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int SUB_BYTES = 64 * 128;                   // 64 rows x 128 bytes
+constexpr int OFF_OUT = STAGES * STAGE_BYTES;         // 128 rows x 128 columns of bf16 for the epilogue
+constexpr int OFF_BIAS = OFF_OUT + BM * 128 * 2;      // 256 floats
+constexpr int OFF_BAR = OFF_BIAS + BN * 4;
+constexpr int USED_BYTES = OFF_BAR + 128;
+constexpr int SMEM_BYTES = 232448;                    // the whole opt-in limit; the base is checked in the kernel
+constexpr int GEMM_THREADS = 192;
+constexpr int GROUP_M = 16;                           // tiles that share B columns run together
+
+enum { B_FULL = 0, B_EMPTY = B_FULL + STAGES, B_ACCFULL = B_EMPTY + STAGES, B_ACCEMPTY = B_ACCFULL + 2, NUM_BARS = B_ACCEMPTY + 2 };
+enum { WG_EMPTY = 201, WG_FULL, WG_ACCEMPTY, WG_ACCFULL, WG_SMEM };
+
+struct ViewGeom {
+    int heads, seq, dim;
+};
+
+struct GemmParams {
+    long long m;
+    int n, k;
+    int tiles_m, tiles_n;
+    ViewGeom a, b;
+    MatView c;
+    const __nv_bfloat16 *bias;
+    DeviceStatus *status;
+};
+
+// TMA coordinates of the box whose first element is (row0, col0) of a view.
+__device__ __forceinline__ void load_box(uint32_t dst, const CUtensorMap *map, uint32_t bar, const ViewGeom &g,
+                                         long long row0, int col0)
+{
+    if (g.heads == 0) {
+        tma_load_5d(dst, map, bar, col0, (int)row0, 0, 0, 0);
+    } else {
+        const int b = (int)(row0 / g.seq), l = (int)(row0 - (long long)b * g.seq);
+        const int ph = col0 / g.dim, d = col0 - ph * g.dim;
+        const int part = ph / g.heads, h = ph - part * g.heads;
+        tma_load_5d(dst, map, bar, d, l, h, b, part);
+    }
+}
+
+__device__ __forceinline__ void tile_coords(const GemmParams &p, int tile, int &tm, int &tn)
+{
+    const int per_group = GROUP_M * p.tiles_n;
+    const int g = tile / per_group, rem = tile - g * per_group;
+    const int rows_here = min(GROUP_M, p.tiles_m - g * GROUP_M);
+    tn = rem / rows_here;
+    tm = g * GROUP_M + (rem - tn * rows_here);
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+    sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                      const GemmParams p)
+{
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    {   // every thread takes the same decision, before any barrier exists
+        uint32_t dyn;
+        asm("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn));
+        if (smem_base + USED_BYTES > smem_u32(smem_raw) + dyn) {
+            if (threadIdx.x == 0 && atomicCAS(&p.status->code, 0, EMBER_ERR_UNSUPPORTED) == 0) {
+                p.status->where = WG_SMEM;
+                p.status->block = blockIdx.x;
+                p.status->extra = (int)(smem_base - smem_u32(smem_raw));
+            }
+            return;
+        }
+    }
+    const uint32_t bar0 = smem_base + OFF_BAR;
+    auto BAR = [&](int i) { return bar0 + 8u * (uint32_t)i; };
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem_gen + OFF_BAR + 8 * NUM_BARS);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    float *bias_s = reinterpret_cast<float *>(smem_gen + OFF_BIAS);
+
+    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const int num_tiles = p.tiles_m * p.tiles_n;
+    const int kblocks = (p.k + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(BAR(B_FULL + s), 1);
+            mbar_init(BAR(B_EMPTY + s), 1);
+        }
+        for (int b = 0; b < 2; b++) {
+            mbar_init(BAR(B_ACCFULL + b), 1);
+            mbar_init(BAR(B_ACCEMPTY + b), 4);  // one arrival per epilogue warp
+        }
+        fence_mbar_init();
+    }
+    if (warp == 4) {
+        tmem_alloc(smem_u32(tmem_slot), 512);
+        tmem_relinquish();
+    }
+    if (warp == 5 && lane == 0) {
+        prefetch_tensormap(&tm_a);
+        prefetch_tensormap(&tm_b);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 5) {
+        if (lane == 0) {
+            // ------------------------------------------------------------ TMA producer
+            int it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                int tm, tn;
+                tile_coords(p, tile, tm, tn);
+                for (int kb = 0; kb < kblocks; kb++, it++) {
+                    const int s = it % STAGES;
+                    if (!(ok = mbar_wait(BAR(B_EMPTY + s), ((it / STAGES) & 1) ^ 1, abort_flag, p.status, WG_EMPTY))) break;
+                    const uint32_t a_dst = smem_base + s * STAGE_BYTES, b_dst = a_dst + A_BYTES;
+                    mbar_arrive_expect_tx(BAR(B_FULL + s), STAGE_BYTES);
+                    if (MODE == GEMM_TN) {  // A view is (k x m): two boxes of 64 k-rows x 64 m-columns
+                        for (int sub = 0; sub < BM / 64; sub++)
+                            load_box(a_dst + sub * SUB_BYTES, &tm_a, BAR(B_FULL + s), p.a, (long long)kb * BK,
+                                     tm * BM + sub * 64);
+                    } else {                // A view is (m x k): one box of 128 rows x 64 k
+                        load_box(a_dst, &tm_a, BAR(B_FULL + s), p.a, (long long)tm * BM, kb * BK);
+                    }
+                    if (MODE == GEMM_NT) {  // B view is (n x k): one box of 256 rows x 64 k
+                        load_box(b_dst, &tm_b, BAR(B_FULL + s), p.b, (long long)tn * BN, kb * BK);
+                    } else {                // B view is (k x n): four boxes of 64 k-rows x 64 n-columns
+                        for (int sub = 0; sub < BN / 64; sub++)
+                            load_box(b_dst + sub * SUB_BYTES, &tm_b, BAR(B_FULL + s), p.b, (long long)kb * BK,
+                                     tn * BN + sub * 64);
+                    }
+                }
+            }
+            // Do not leave while a copy of this CTA is still landing in shared memory.
+            const long long t0 = clock64();
+            for (int j = max(0, it - STAGES); j < it; j++)
+                while (!mbar_try_wait(BAR(B_FULL + j % STAGES), (j / STAGES) & 1) && clock64() - t0 < kWaitLimitCycles) {}
+        }
+    } else if (warp == 4) {
+        // ---------------------------------------------------------------- MMA issue
+        constexpr uint32_t IDESC = idesc_bf16_f32(BM, BN, MODE == GEMM_TN ? 1 : 0, MODE == GEMM_NT ? 0 : 1);
+        constexpr uint32_t A_LBO = MODE == GEMM_TN ? SUB_BYTES : 16, A_STEP = (MODE == GEMM_TN ? 2048 : 32) >> 4;
+        constexpr uint32_t B_LBO = MODE == GEMM_NT ? 16 : SUB_BYTES, B_STEP = (MODE == GEMM_NT ? 32 : 2048) >> 4;
+        int it = 0, tcount = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, tcount++) {
+            const int buf = tcount & 1;
+            ok = ok && mbar_wait(BAR(B_ACCEMPTY + buf), ((tcount >> 1) & 1) ^ 1, abort_flag, p.status, WG_ACCEMPTY);
+            tc_fence_after();
+            for (int kb = 0; kb < kblocks; kb++, it++) {
+                const int s = it % STAGES;
+                ok = ok && mbar_wait(BAR(B_FULL + s), (it / STAGES) & 1, abort_flag, p.status, WG_FULL);
+                tc_fence_after();
+                const uint32_t a_lo = desc_lo(smem_base + s * STAGE_BYTES, A_LBO);
+                const uint32_t b_lo = desc_lo(smem_base + s * STAGE_BYTES + A_BYTES, B_LBO);
+#pragma unroll
+                for (int k16 = 0; k16 < BK / 16; k16++)
+                    mma_ss_lo(tmem + buf * BN, a_lo + k16 * A_STEP, b_lo + k16 * B_STEP, IDESC, (kb > 0 || k16 > 0) ? 1u : 0u);
+                tc_commit_elect(BAR(B_EMPTY + s));
+            }
+            tc_commit_elect(BAR(B_ACCFULL + buf));
+        }
+    } else {
+        // -------------------------------------------------------------------- epilogue (warps 0-3)
+        const int r = threadIdx.x;  // row inside the tile == TMEM lane
+        const uint32_t lane_sel = (uint32_t)(warp * 32) << 16;
+        uint8_t *stage = smem_gen + OFF_OUT;
+        __nv_bfloat16 *cptr = (__nv_bfloat16 *)p.c.ptr;
+        int tcount = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, tcount++) {
+            int tm, tn;
+            tile_coords(p, tile, tm, tn);
+            const int buf = tcount & 1;
+            const long long m0 = (long long)tm * BM;
+            const int n0 = tn * BN;
+            named_bar_sync(1, 128);  // the previous tile's bias has been read by every thread
+            for (int j = r; j < BN; j += 128)
+                bias_s[j] = (p.bias && n0 + j < p.n) ? __bfloat162float(p.bias[n0 + j]) : 0.f;
+            named_bar_sync(1, 128);
+            ok = ok && mbar_wait(BAR(B_ACCFULL + buf), (tcount >> 1) & 1, abort_flag, p.status, WG_ACCFULL);
+            tc_fence_after();
+            const uint32_t tacc = tmem + lane_sel + buf * BN;
+#pragma unroll 1
+            for (int half = 0; half < 2; half++) {
+#pragma unroll
+                for (int ch = 0; ch < 4; ch++) {
+                    uint32_t u[32];
+                    tmem_ld_32x32b_x32(tacc + half * 128 + ch * 32, u);
+                    tmem_wait_ld();
+                    if (half == 1 && ch == 3) {  // the accumulator is in registers: the next tile may use it
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(BAR(B_ACCEMPTY + buf));
+                    }
+                    const float *bs = bias_s + half * 128 + ch * 32;
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; q4++) {  // 8 columns = one 16-byte chunk
+                        uint4 wv;
+                        wv.x = pack_bf16(__uint_as_float(u[q4 * 8 + 0]) + bs[q4 * 8 + 0], __uint_as_float(u[q4 * 8 + 1]) + bs[q4 * 8 + 1]);
+                        wv.y = pack_bf16(__uint_as_float(u[q4 * 8 + 2]) + bs[q4 * 8 + 2], __uint_as_float(u[q4 * 8 + 3]) + bs[q4 * 8 + 3]);
+                        wv.z = pack_bf16(__uint_as_float(u[q4 * 8 + 4]) + bs[q4 * 8 + 4], __uint_as_float(u[q4 * 8 + 5]) + bs[q4 * 8 + 5]);
+                        wv.w = pack_bf16(__uint_as_float(u[q4 * 8 + 6]) + bs[q4 * 8 + 6], __uint_as_float(u[q4 * 8 + 7]) + bs[q4 * 8 + 7]);
+                        const int chunk = ch * 4 + q4;
+                        const int sw = (chunk & ~7) | ((chunk ^ r) & 7);
+                        *reinterpret_cast<uint4 *>(stage + r * 256 + sw * 16) = wv;
+                    }
+                }
+                __syncwarp();
+                // Each warp copies its own 32 rows: two rows of 16 chunks per instruction.
+                const int chunk = lane % 16;
+                const int col = n0 + half * 128 + chunk * 8;
+#pragma unroll 4
+                for (int it2 = 0; it2 < 16; it2++) {
+                    const int rr = warp * 32 + it2 * 2 + lane / 16;
+                    const int sw = (chunk & ~7) | ((chunk ^ rr) & 7);
+                    const uint4 wv = *reinterpret_cast<const uint4 *>(stage + rr * 256 + sw * 16);
+                    const long long grow = m0 + rr;
+                    if (ok && grow < p.m && col < p.n) *reinterpret_cast<uint4 *>(cptr + view_offset(p.c, grow, col)) = wv;
+                }
+                __syncwarp();
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 4) tmem_dealloc(tmem, 512);
+}
+
+bool view_ok(const MatView &v, int row_box)
+{
+    if (((uintptr_t)v.ptr & 15) != 0) return false;
+    if (v.heads == 0) return v.cols % 8 == 0;
+    // head-major: a box of 64 columns must stay inside one head and a box of rows inside one batch entry
+    return v.dim % 64 == 0 && v.seq % row_box == 0 && v.rows % v.seq == 0 && v.cols % (v.heads * v.dim) == 0;
+}
+
+template <int MODE>
+int launch(const GemmArgs &g, DeviceState *st, cudaStream_t s)
+{
+    CUtensorMap ta, tb;
+    int rc;
+    if ((rc = make_tensor_map_bf16_view(&ta, g.a, 64, MODE == GEMM_TN ? 64 : BM)) != EMBER_OK) return rc;
+    if ((rc = make_tensor_map_bf16_view(&tb, g.b, 64, MODE == GEMM_NT ? BN : 64)) != EMBER_OK) return rc;
+    GemmParams p;
+    p.m = g.m;
+    p.n = g.n;
+    p.k = g.k;
+    p.tiles_m = (int)((g.m + BM - 1) / BM);
+    p.tiles_n = (g.n + BN - 1) / BN;
+    p.a = {g.a.heads, g.a.seq, g.a.dim};
+    p.b = {g.b.heads, g.b.seq, g.b.dim};
+    p.c = g.c;
+    p.bias = (const __nv_bfloat16 *)g.bias;
+    p.status = st->status;
+    auto kern = sm100_gemm_kernel<MODE>;
+    EMBER_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    const long long tiles = (long long)p.tiles_m * p.tiles_n;
+    const int sms = st->sm_count > 0 ? st->sm_count : 148;
+    const int grid = (int)(tiles < sms ? tiles : sms);
+    kern<<<grid, GEMM_THREADS, SMEM_BYTES, s>>>(ta, tb, p);
+    EMBER_CUDA_TRY(cudaGetLastError());
+    return EMBER_OK;
+}
+
+}  // namespace
+
+bool sm100_gemm_supported(const GemmArgs &g)
+{
+    if (g.dtype != EMBER_BF16 || g.m <= 0 || g.n <= 0 || g.k <= 0) return false;
+    if ((g.m + BM - 1) / BM * (long long)((g.n + BN - 1) / BN) > 0x7fffffffLL) return false;
+    if (g.n % 8 != 0 || ((uintptr_t)g.c.ptr & 15) != 0) return false;       // 16-byte output chunks
+    if (g.c.heads > 0 && g.c.dim % 8 != 0) return false;
+    const int a_rows = g.mode == GEMM_TN ? 64 : BM, b_rows = g.mode == GEMM_NT ? BN : 64;
+    return view_ok(g.a, a_rows) && view_ok(g.b, b_rows);
+}
+
+int sm100_gemm(const GemmArgs &g, DeviceState *st, cudaStream_t s)
+{
+    switch (g.mode) {
+    case GEMM_NN: return launch<GEMM_NN>(g, st, s);
+    case GEMM_NT: return launch<GEMM_NT>(g, st, s);
+    default: return launch<GEMM_TN>(g, st, s);
+    }
+}
+
+}  // namespace ember

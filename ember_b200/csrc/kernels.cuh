@@ -1,6 +1,8 @@
 // Internal interface between the C-ABI dispatcher and the kernel families.
 #pragma once
 
+#include <cuda.h>
+
 #include "common.cuh"
 
 namespace ember {
@@ -32,5 +34,50 @@ int sm100_attention_bwd(const AttnArgs &a, float *delta, DeviceState *st, cudaSt
 int decode_pick_splits(int bh, int lk, int d, int dtype, int sm_count);
 size_t decode_workspace_bytes(int bh, int d, int splits);
 int decode_attention(const AttnArgs &a, int splits, void *workspace, DeviceState *st, cudaStream_t s);
+
+// ---------------------------------------------------------------- projections either side of attention
+// A logical (rows x cols) matrix and how it lies in memory.
+//   heads == 0: row-major, leading dimension = cols.
+//   heads  > 0: head-major (parts, batch, heads, seq, dim), the layout attention consumes:
+//               row = b * seq + l, col = (part * heads + h) * dim + d, batch = rows / seq,
+//               parts = cols / (heads * dim).
+struct MatView {
+    const void *ptr = nullptr;
+    long long rows = 0;
+    int cols = 0;
+    int heads = 0, seq = 0, dim = 0;
+};
+
+__host__ __device__ inline size_t view_offset(const MatView &v, long long row, int col)
+{
+    if (v.heads == 0) return (size_t)row * v.cols + col;
+    const long long b = row / v.seq, batch = v.rows / v.seq;
+    const int l = (int)(row - b * v.seq), ph = col / v.dim, d = col - ph * v.dim;
+    const int part = ph / v.heads, h = ph - part * v.heads;
+    return ((((size_t)part * batch + b) * v.heads + h) * v.seq + l) * v.dim + d;
+}
+
+// C (m x n) = op(A) * op(B) [+ bias], bf16 or f32 storage, float32 accumulation.
+enum GemmMode {
+    GEMM_NN = 0,  // A view (m x k), B view (k x n)
+    GEMM_NT = 1,  // A view (m x k), B view (n x k)
+    GEMM_TN = 2   // A view (k x m), B view (k x n)
+};
+struct GemmArgs {
+    int mode = GEMM_NN;
+    MatView a, b, c;
+    const void *bias = nullptr;  // n values of the storage dtype, or null
+    long long m = 0;
+    int n = 0, k = 0;
+    int dtype = EMBER_F32;
+};
+
+// CUDA-core kernels (gemm_simt.cu): float32 math, any shape and view.
+int simt_gemm(const GemmArgs &g, cudaStream_t s);
+int column_sums(const MatView &a, void *out, int dtype, cudaStream_t s);  // out[j] = sum over rows of a(:, j)
+// tcgen05 kernel (gemm_sm100.cu): bf16 storage; see sm100_gemm_supported for the shapes it takes.
+bool sm100_gemm_supported(const GemmArgs &g);
+int sm100_gemm(const GemmArgs &g, DeviceState *st, cudaStream_t s);
+int make_tensor_map_bf16_view(CUtensorMap *map, const MatView &v, uint32_t box_cols, uint32_t box_rows);
 
 }  // namespace ember

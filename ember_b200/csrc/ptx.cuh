@@ -112,6 +112,17 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst_smem, const CUtensorMap
         : "memory");
 }
 
+// 5-D tile load (matrix views: column, row, head, batch, part).
+__device__ __forceinline__ void tma_load_5d(uint32_t dst_smem, const CUtensorMap *m, uint32_t bar, int c0, int c1,
+                                            int c2, int c3, int c4)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+        ::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
+        : "memory");
+}
+
 // ---------------------------------------------------------------- tcgen05: tensor memory
 // Allocates ncols (power of two, 32..512) TMEM columns; the base address lands in *dst_smem.
 // Must be executed by one full warp.
@@ -299,6 +310,12 @@ __device__ __forceinline__ void mma_ts_lo(uint32_t d_tmem, uint32_t a_tmem, uint
         "}\n"
         ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(kDescHiSw128)
         : "memory");
+}
+
+// Named barrier (ids 1..15; 0 is __syncthreads) over `count` threads, a multiple of 32.
+__device__ __forceinline__ void named_bar_sync(int id, int count)
+{
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
 }
 
 __device__ __forceinline__ void reg_alloc_232() { asm volatile("setmaxnreg.inc.sync.aligned.u32 232;"); }

@@ -21,6 +21,7 @@ typedef struct {
     int size;            /* element count, saturated at INT_MAX (reference field) */
     int dtype;           /* EMBER_F32 / EMBER_BF16 */
     long long size64;    /* exact element count */
+    PyObject *base;      /* owner of the memory when this tensor is a view (else NULL) */
 } _Tensor;
 
 static PyTypeObject _TensorType;
@@ -44,6 +45,7 @@ static _Tensor *alloc_result(long long n, int dtype)
     t->size64 = n;
     t->size = n > 2147483647LL ? 2147483647 : (int)n;
     t->dtype = dtype;
+    t->base = NULL;
     t->d_ptr = alloc_memory((size_t)(n > 0 ? n : 1) * elem_size(dtype));
     if (!t->d_ptr) {
         Py_DECREF(t);
@@ -55,7 +57,10 @@ static _Tensor *alloc_result(long long n, int dtype)
 
 static void _Tensor_dealloc(_Tensor *self)
 {
-    if (self->d_ptr) free_memory(self->d_ptr);
+    if (self->base)
+        Py_DECREF(self->base); /* a view: the owner frees the memory */
+    else if (self->d_ptr)
+        free_memory(self->d_ptr);
     Py_TYPE(self)->tp_free((PyObject *)self);
 }
 
@@ -71,6 +76,7 @@ static int _Tensor_init(_Tensor *self, PyObject *args, PyObject *kwds)
     self->size64 = n;
     self->size = n > 2147483647LL ? 2147483647 : (int)n;
     self->dtype = dtype;
+    self->base = NULL;
     self->d_ptr = alloc_memory((size_t)(n > 0 ? n : 1) * elem_size(dtype));
     if (!self->d_ptr) {
         PyErr_Format(PyExc_MemoryError, "Failed to allocate device memory: %s", ember_last_error());
@@ -241,14 +247,18 @@ static PyObject *_attention_fwd(PyObject *module, PyObject *args)
     return Py_BuildValue("(NN)", out, lse);
 }
 
-/* _attention_bwd(q, k, v, out, lse, dout, B, H, Lq, Lk, D, scale, causal) -> (dq, dk, dv) */
+/* _attention_bwd(q, k, v, out, lse, dout, B, H, Lq, Lk, D, scale, causal[, (dq, dk, dv)]) -> (dq, dk, dv)
+ * The optional last argument supplies the three result tensors (for instance views of one buffer,
+ * so that the gradients lie back to back); without it they are allocated. */
 static PyObject *_attention_bwd(PyObject *module, PyObject *args)
 {
     _Tensor *q, *k, *v, *o, *lse, *g;
     int B, H, lq, lk, d, causal;
     float scale;
-    if (!PyArg_ParseTuple(args, "O!O!O!O!O!O!iiiiifi", &_TensorType, &q, &_TensorType, &k, &_TensorType, &v,
-                          &_TensorType, &o, &_TensorType, &lse, &_TensorType, &g, &B, &H, &lq, &lk, &d, &scale, &causal))
+    PyObject *outs = NULL;
+    if (!PyArg_ParseTuple(args, "O!O!O!O!O!O!iiiiifi|O", &_TensorType, &q, &_TensorType, &k, &_TensorType, &v,
+                          &_TensorType, &o, &_TensorType, &lse, &_TensorType, &g, &B, &H, &lq, &lk, &d, &scale, &causal,
+                          &outs))
         return NULL;
     const long long bh = (long long)B * H;
     if (check_sizes("attention_backward", q, k, v, bh, lq, lk, d) < 0) return NULL;
@@ -261,10 +271,23 @@ static PyObject *_attention_bwd(PyObject *module, PyObject *args)
         PyErr_SetString(PyExc_TypeError, "attention_backward: out/dout must have q's dtype and lse must be float32");
         return NULL;
     }
-    _Tensor *dq = alloc_result(q->size64, q->dtype), *dk = NULL, *dv = NULL;
+    _Tensor *dq = NULL, *dk = NULL, *dv = NULL;
     void *ws = NULL;
-    if (dq) dk = alloc_result(k->size64, q->dtype);
-    if (dk) dv = alloc_result(v->size64, q->dtype);
+    if (outs && outs != Py_None) {
+        if (!PyArg_ParseTuple(outs, "O!O!O!", &_TensorType, &dq, &_TensorType, &dk, &_TensorType, &dv)) return NULL;
+        if (dq->size64 != q->size64 || dk->size64 != k->size64 || dv->size64 != v->size64 || dq->dtype != q->dtype ||
+            dk->dtype != q->dtype || dv->dtype != q->dtype) {
+            PyErr_SetString(PyExc_ValueError, "attention_backward: the supplied result tensors do not match q, k and v");
+            return NULL;
+        }
+        Py_INCREF(dq);
+        Py_INCREF(dk);
+        Py_INCREF(dv);
+    } else {
+        dq = alloc_result(q->size64, q->dtype);
+        if (dq) dk = alloc_result(k->size64, q->dtype);
+        if (dk) dv = alloc_result(v->size64, q->dtype);
+    }
     const size_t wsn = ember_attention_workspace_bytes(EMBER_OP_BWD, (int)bh, lq, lk, d, q->dtype, 0);
     if (dv) {
         ws = alloc_memory(wsn);
@@ -328,6 +351,107 @@ static PyObject *_attention_decode(PyObject *module, PyObject *args)
     return Py_BuildValue("(NN)", out, lse);
 }
 
+/* t._view(offset, size) -> a tensor over elements [offset, offset + size) of t's memory. The view
+ * keeps t alive and never frees; it lets the three (B, H, L, D) tensors a fused q/k/v projection
+ * writes back to back be handed to attention without a copy. */
+static PyObject *_Tensor_view(_Tensor *self, PyObject *args)
+{
+    long long off, n;
+    if (!PyArg_ParseTuple(args, "LL", &off, &n)) return NULL;
+    if (off < 0 || n < 0 || off + n > self->size64) {
+        PyErr_Format(PyExc_ValueError, "_view: [%lld, %lld) is outside a tensor of %lld elements", off, off + n,
+                     self->size64);
+        return NULL;
+    }
+    _Tensor *t = (_Tensor *)_TensorType.tp_alloc(&_TensorType, 0);
+    if (!t) return NULL;
+    t->size64 = n;
+    t->size = n > 2147483647LL ? 2147483647 : (int)n;
+    t->dtype = self->dtype;
+    t->d_ptr = (char *)self->d_ptr + (size_t)off * elem_size(self->dtype);
+    t->base = self->base ? self->base : (PyObject *)self;
+    Py_INCREF(t->base);
+    return (PyObject *)t;
+}
+
+/* _linear_fwd(x, w, bias | None, m, n, k, x_heads, y_heads, seq, head_dim) -> y
+ * The reference's Linear.forward (ember/nn/layers.py:45-48) as one call. */
+static PyObject *_linear_fwd(PyObject *module, PyObject *args)
+{
+    _Tensor *x, *w;
+    PyObject *bias_o;
+    long long m;
+    int n, k, xh, yh, seq, hd;
+    if (!PyArg_ParseTuple(args, "O!O!OLiiiiii", &_TensorType, &x, &_TensorType, &w, &bias_o, &m, &n, &k, &xh, &yh, &seq, &hd))
+        return NULL;
+    _Tensor *bias = NULL;
+    if (bias_o != Py_None) {
+        if (!PyObject_TypeCheck(bias_o, &_TensorType)) {
+            PyErr_SetString(PyExc_TypeError, "linear: bias must be a _Tensor or None");
+            return NULL;
+        }
+        bias = (_Tensor *)bias_o;
+    }
+    if (m <= 0 || n <= 0 || k <= 0 || x->size64 != m * k || w->size64 != (long long)k * n || (bias && bias->size64 != n)) {
+        PyErr_Format(PyExc_ValueError, "linear: size mismatch: x %lld (expected %lld), w %lld (expected %lld), bias %lld (expected %d)",
+                     x->size64, m * k, w->size64, (long long)k * n, bias ? bias->size64 : (long long)n, n);
+        return NULL;
+    }
+    if (w->dtype != x->dtype || (bias && bias->dtype != x->dtype)) {
+        PyErr_SetString(PyExc_TypeError, "linear: x, w and bias must share a dtype");
+        return NULL;
+    }
+    _Tensor *y = alloc_result(m * n, x->dtype);
+    if (!y) return NULL;
+    int rc = ember_linear_fwd(x->d_ptr, w->d_ptr, bias ? bias->d_ptr : NULL, y->d_ptr, m, n, k, x->dtype, xh, yh, seq, hd, NULL);
+    if (rc) {
+        Py_DECREF(y);
+        return raise_status(rc);
+    }
+    return (PyObject *)y;
+}
+
+/* _linear_bwd(x, w, grad_y, m, n, k, x_heads, y_heads, seq, head_dim, need_grad_x, need_grad_b)
+ *   -> (grad_x | None, grad_w, grad_b | None): the reference's Linear.backward (layers.py:50-56). */
+static PyObject *_linear_bwd(PyObject *module, PyObject *args)
+{
+    _Tensor *x, *w, *g;
+    long long m;
+    int n, k, xh, yh, seq, hd, need_dx, need_db;
+    if (!PyArg_ParseTuple(args, "O!O!O!Liiiiiiii", &_TensorType, &x, &_TensorType, &w, &_TensorType, &g, &m, &n, &k, &xh,
+                          &yh, &seq, &hd, &need_dx, &need_db))
+        return NULL;
+    if (m <= 0 || n <= 0 || k <= 0 || x->size64 != m * k || w->size64 != (long long)k * n || g->size64 != m * n) {
+        PyErr_Format(PyExc_ValueError, "linear_backward: size mismatch: x %lld (expected %lld), w %lld (expected %lld), grad_y %lld (expected %lld)",
+                     x->size64, m * k, w->size64, (long long)k * n, g->size64, m * n);
+        return NULL;
+    }
+    if (w->dtype != x->dtype || g->dtype != x->dtype) {
+        PyErr_SetString(PyExc_TypeError, "linear_backward: x, w and grad_y must share a dtype");
+        return NULL;
+    }
+    _Tensor *dx = NULL, *dw = NULL, *db = NULL;
+    dw = alloc_result((long long)k * n, x->dtype);
+    if (dw && need_dx) dx = alloc_result(m * k, x->dtype);
+    if (dw && (!need_dx || dx) && need_db) db = alloc_result(n, x->dtype);
+    if (!dw || (need_dx && !dx) || (need_db && !db)) {
+        Py_XDECREF(dx);
+        Py_XDECREF(dw);
+        Py_XDECREF(db);
+        return NULL;
+    }
+    int rc = ember_linear_bwd(x->d_ptr, w->d_ptr, g->d_ptr, dx ? dx->d_ptr : NULL, dw->d_ptr, db ? db->d_ptr : NULL, m, n, k,
+                              x->dtype, xh, yh, seq, hd, NULL);
+    if (rc) {
+        Py_XDECREF(dx);
+        Py_DECREF(dw);
+        Py_XDECREF(db);
+        return raise_status(rc);
+    }
+    PyObject *odx = dx ? (PyObject *)dx : Py_NewRef(Py_None), *odb = db ? (PyObject *)db : Py_NewRef(Py_None);
+    return Py_BuildValue("(NNN)", odx, dw, odb);
+}
+
 static PyObject *_sync(PyObject *module, PyObject *noargs)
 {
     sync_device();
@@ -337,6 +461,7 @@ static PyObject *_sync(PyObject *module, PyObject *noargs)
 static PyMethodDef _Tensor_methods[] = {
     {"_copy_to_buffer", (PyCFunction)_Tensor_copy_to_buffer, METH_VARARGS, "Copy to a writable float32 host buffer"},
     {"_ptr", (PyCFunction)_Tensor_ptr, METH_NOARGS, "Device address as an int"},
+    {"_view", (PyCFunction)_Tensor_view, METH_VARARGS, "A tensor over a range of this tensor's elements"},
     {NULL}};
 
 static PyMemberDef _Tensor_members[] = {{"size", T_LONGLONG, offsetof(_Tensor, size64), READONLY, "element count"},
@@ -350,6 +475,8 @@ static PyMethodDef module_methods[] = {OP_METHOD(_from_numpy),
                                        OP_METHOD(_attention_fwd),
                                        OP_METHOD(_attention_bwd),
                                        OP_METHOD(_attention_decode),
+                                       OP_METHOD(_linear_fwd),
+                                       OP_METHOD(_linear_bwd),
                                        {"_sync", (PyCFunction)_sync, METH_NOARGS, "Wait for the library stream"},
                                        {NULL, NULL, 0, NULL}};
 

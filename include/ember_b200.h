@@ -158,6 +158,37 @@ EMBER_API int ember_attention_decode_splits(int batch_heads, int lk, int d, int 
  * arguments: "sm100_tcgen05" or "simt_f32". For tests and the benchmark. */
 EMBER_API const char *ember_attention_kernel_name(int op, int lq, int lk, int d, int dtype);
 
+/* ---- The Linear layers either side of attention -----------------------------
+ *
+ * Replaces the reference's Linear layer (ember/nn/layers.py:9-56), which composes
+ *     forward   y      = b + x @ w            (tensor.py:163-197 -> tensor_api.c:330-354, operators.def:65)
+ *     backward  grad_w = T(x) @ grad_y ; grad_b = sum(grad_y, axis=0) ; grad_x = grad_y @ T(w)
+ * from its matmul, transpose, broadcast-add and sum operators, one allocation per step.
+ *
+ * x is a logical (m, k) matrix, w is (k, n) row-major as the reference stores it (in_features,
+ * out_features), bias has n elements (or NULL), y is (m, n). dtype selects storage as for attention
+ * (float32 arithmetic on CUDA cores for EMBER_F32; bf16 tensor-core products with float32
+ * accumulation for EMBER_BF16 when the shapes allow, else float32 arithmetic on bf16 storage).
+ *
+ * Head-major operands, so that no transpose runs between a projection and attention:
+ *   x_heads > 0: x (and grad_x) lie as (batch, x_heads, seq, head_dim), the layout attention
+ *                writes; k == x_heads * head_dim, m == batch * seq.
+ *   y_heads > 0: y (and grad_y) lie as (parts, batch, y_heads, seq, head_dim) with
+ *                n == parts * y_heads * head_dim: a fused q/k/v projection (parts == 3) writes the
+ *                three (batch, heads, seq, head_dim) tensors attention reads, back to back.
+ *   0 means row-major. seq and head_dim are ignored when both head counts are 0.
+ *
+ * ember_linear_bwd: any of grad_x, grad_w, grad_b may be NULL and is then skipped. */
+EMBER_API int ember_linear_fwd(const void *x, const void *w, const void *bias, void *y, long long m, int n, int k,
+                               int dtype, int x_heads, int y_heads, int seq, int head_dim, void *stream);
+EMBER_API int ember_linear_bwd(const void *x, const void *w, const void *grad_y, void *grad_x, void *grad_w,
+                               void *grad_b, long long m, int n, int k, int dtype, int x_heads, int y_heads,
+                               int seq, int head_dim, void *stream);
+/* Kernel family the dispatcher picks for one of the three products (0 forward, 1 grad_w,
+ * 2 grad_x) with 16-byte aligned pointers: "sm100_tcgen05" or "simt_f32". */
+EMBER_API const char *ember_linear_kernel_name(int product, long long m, int n, int k, int dtype, int x_heads,
+                                               int y_heads, int seq, int head_dim);
+
 #ifdef __cplusplus
 }
 #endif
