@@ -66,8 +66,50 @@ __global__ void __launch_bounds__(256) simt_gemm_kernel(MatView a, MatView b, Ma
     }
 }
 
-// out[j] = sum over the rows of a(:, j), rows added in order by 32 partial sums per column (one per
-// lane of a warp; lane t takes rows t, t + 32, ...), then a warp reduction.
+// out[j] = sum over the rows of a(:, j). One block owns 32 consecutive columns and all the rows:
+// 4 threads read the 32 columns of a row as 8-element vectors (whole 64- or 128-byte segments), 64
+// rows at a time; every thread keeps 8 float32 partial sums over the rows it visits (rows t, t + 64,
+// ...), and shared memory adds the 64 partials of a column in a fixed order. Needs 8-element groups
+// that do not straddle a head (cols, or the head dimension, a multiple of 8) and a 16-byte aligned
+// base; other shapes take the element-wise kernel below.
+template <typename T>
+__global__ void __launch_bounds__(256) column_sum_vec_kernel(MatView a, T *out)
+{
+    __shared__ float part[64][33];
+    const int part_col = (threadIdx.x % 4) * 8, rt = threadIdx.x / 4;
+    const int col = blockIdx.x * 32 + part_col;
+    const T *ap = (const T *)a.ptr;
+    float s[8] = {};
+    if (col < a.cols) {
+        for (long long r = rt; r < a.rows; r += 64) {
+            const T *src = ap + view_offset(a, r, col);
+            if constexpr (sizeof(T) == 2) {
+                const uint4 v = *reinterpret_cast<const uint4 *>(src);
+                const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    s[2 * i] += __uint_as_float(w[i] << 16);
+                    s[2 * i + 1] += __uint_as_float(w[i] & 0xffff0000u);
+                }
+            } else {
+                const float4 v0 = *reinterpret_cast<const float4 *>(src), v1 = *reinterpret_cast<const float4 *>(src + 4);
+                s[0] += v0.x; s[1] += v0.y; s[2] += v0.z; s[3] += v0.w;
+                s[4] += v1.x; s[5] += v1.y; s[6] += v1.z; s[7] += v1.w;
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 8; i++) part[rt][part_col + i] = s[i];
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        float t = 0.f;
+        for (int r = 0; r < 64; r++) t += part[r][threadIdx.x];
+        const int c = blockIdx.x * 32 + threadIdx.x;
+        if (c < a.cols) st(out, (size_t)c, t);
+    }
+}
+
+// Element-wise variant for any shape: one warp per column, lane t takes rows t, t + 32, ...
 template <typename T>
 __global__ void __launch_bounds__(256) column_sum_kernel(MatView a, T *out)
 {
@@ -109,11 +151,20 @@ int simt_gemm(const GemmArgs &g, cudaStream_t s)
 
 int column_sums(const MatView &a, void *out, int dtype, cudaStream_t s)
 {
-    const int grid = (a.cols + 7) / 8;
-    if (dtype == EMBER_BF16)
-        column_sum_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(a, (__nv_bfloat16 *)out);
-    else
-        column_sum_kernel<float><<<grid, 256, 0, s>>>(a, (float *)out);
+    const bool vec = ((uintptr_t)a.ptr & 15) == 0 && (a.heads ? a.dim % 8 == 0 : a.cols % 8 == 0);
+    if (vec) {
+        const int grid = (a.cols + 31) / 32;
+        if (dtype == EMBER_BF16)
+            column_sum_vec_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(a, (__nv_bfloat16 *)out);
+        else
+            column_sum_vec_kernel<float><<<grid, 256, 0, s>>>(a, (float *)out);
+    } else {
+        const int grid = (a.cols + 7) / 8;
+        if (dtype == EMBER_BF16)
+            column_sum_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(a, (__nv_bfloat16 *)out);
+        else
+            column_sum_kernel<float><<<grid, 256, 0, s>>>(a, (float *)out);
+    }
     EMBER_CUDA_TRY(cudaGetLastError());
     return EMBER_OK;
 }

@@ -55,19 +55,47 @@ struct GemmParams {
     DeviceStatus *status;
 };
 
-// TMA coordinates of the box whose first element is (row0, col0) of a view.
-__device__ __forceinline__ void load_box(uint32_t dst, const CUtensorMap *map, uint32_t bar, const ViewGeom &g,
-                                         long long row0, int col0)
-{
-    if (g.heads == 0) {
-        tma_load_5d(dst, map, bar, col0, (int)row0, 0, 0, 0);
-    } else {
-        const int b = (int)(row0 / g.seq), l = (int)(row0 - (long long)b * g.seq);
-        const int ph = col0 / g.dim, d = col0 - ph * g.dim;
-        const int part = ph / g.heads, h = ph - part * g.heads;
-        tma_load_5d(dst, map, bar, d, l, h, b, part);
+// TMA coordinates of a 64-column box of a view, walked along the contraction index. The producer
+// computes coordinates on the critical path of every stage, so the divisions that split a row into
+// (batch, position) and a column into (part, head, element) are done once per tile and the walk
+// itself only adds and carries (all steps are 64; seq and dim are multiples of 64 for head-major
+// views the kernel accepts).
+struct BoxWalker {
+    int c0, c1, c2, c3, c4;  // column | element, row | position, head, batch, part
+    int heads, seq, dim;
+
+    __device__ __forceinline__ void init(const ViewGeom &g, int row0, int col0)
+    {
+        heads = g.heads;
+        seq = g.seq;
+        dim = g.dim;
+        if (heads == 0) {
+            c0 = col0; c1 = row0; c2 = c3 = c4 = 0;
+        } else {
+            c3 = row0 / seq; c1 = row0 - c3 * seq;
+            const int ph = col0 / dim;
+            c0 = col0 - ph * dim;
+            c4 = ph / heads; c2 = ph - c4 * heads;
+        }
     }
-}
+    __device__ __forceinline__ void step_rows()  // 64 rows further
+    {
+        c1 += 64;
+        if (heads != 0 && c1 >= seq) { c1 -= seq; c3++; }
+    }
+    __device__ __forceinline__ void step_cols()  // 64 columns further
+    {
+        c0 += 64;
+        if (heads != 0 && c0 >= dim) {
+            c0 = 0;
+            if (++c2 >= heads) { c2 = 0; c4++; }
+        }
+    }
+    __device__ __forceinline__ void load(uint32_t dst, const CUtensorMap *map, uint32_t bar) const
+    {
+        tma_load_5d(dst, map, bar, c0, c1, c2, c3, c4);
+    }
+};
 
 __device__ __forceinline__ void tile_coords(const GemmParams &p, int tile, int &tm, int &tn)
 {
@@ -141,24 +169,28 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
                 int tm, tn;
                 tile_coords(p, tile, tm, tn);
+                constexpr int NA = MODE == GEMM_TN ? BM / 64 : 1, NB = MODE == GEMM_NT ? 1 : BN / 64;
+                BoxWalker wa[NA], wb[NB];
+#pragma unroll
+                for (int sub = 0; sub < NA; sub++)  // TN: A view is (k x m), boxes of 64 k-rows x 64 m-columns
+                    wa[sub].init(p.a, MODE == GEMM_TN ? 0 : tm * BM, MODE == GEMM_TN ? tm * BM + sub * 64 : 0);
+#pragma unroll
+                for (int sub = 0; sub < NB; sub++)  // NN, TN: B view is (k x n), boxes of 64 k-rows x 64 n-columns
+                    wb[sub].init(p.b, MODE == GEMM_NT ? tn * BN : 0, MODE == GEMM_NT ? 0 : tn * BN + sub * 64);
                 for (int kb = 0; kb < kblocks; kb++, it++) {
                     const int s = it % STAGES;
                     if (!(ok = mbar_wait(BAR(B_EMPTY + s), ((it / STAGES) & 1) ^ 1, abort_flag, p.status, WG_EMPTY))) break;
                     const uint32_t a_dst = smem_base + s * STAGE_BYTES, b_dst = a_dst + A_BYTES;
                     mbar_arrive_expect_tx(BAR(B_FULL + s), STAGE_BYTES);
-                    if (MODE == GEMM_TN) {  // A view is (k x m): two boxes of 64 k-rows x 64 m-columns
-                        for (int sub = 0; sub < BM / 64; sub++)
-                            load_box(a_dst + sub * SUB_BYTES, &tm_a, BAR(B_FULL + s), p.a, (long long)kb * BK,
-                                     tm * BM + sub * 64);
-                    } else {                // A view is (m x k): one box of 128 rows x 64 k
-                        load_box(a_dst, &tm_a, BAR(B_FULL + s), p.a, (long long)tm * BM, kb * BK);
+#pragma unroll
+                    for (int sub = 0; sub < NA; sub++) {
+                        wa[sub].load(a_dst + sub * SUB_BYTES, &tm_a, BAR(B_FULL + s));
+                        if (MODE == GEMM_TN) wa[sub].step_rows(); else wa[sub].step_cols();
                     }
-                    if (MODE == GEMM_NT) {  // B view is (n x k): one box of 256 rows x 64 k
-                        load_box(b_dst, &tm_b, BAR(B_FULL + s), p.b, (long long)tn * BN, kb * BK);
-                    } else {                // B view is (k x n): four boxes of 64 k-rows x 64 n-columns
-                        for (int sub = 0; sub < BN / 64; sub++)
-                            load_box(b_dst + sub * SUB_BYTES, &tm_b, BAR(B_FULL + s), p.b, (long long)kb * BK,
-                                     tn * BN + sub * 64);
+#pragma unroll
+                    for (int sub = 0; sub < NB; sub++) {
+                        wb[sub].load(b_dst + sub * SUB_BYTES, &tm_b, BAR(B_FULL + s));
+                        if (MODE == GEMM_NT) wb[sub].step_cols(); else wb[sub].step_rows();
                     }
                 }
             }
@@ -300,6 +332,7 @@ int launch(const GemmArgs &g, DeviceState *st, cudaStream_t s)
 bool sm100_gemm_supported(const GemmArgs &g)
 {
     if (g.dtype != EMBER_BF16 || g.m <= 0 || g.n <= 0 || g.k <= 0) return false;
+    if (g.m > 0x7fffff00LL || g.a.rows > 0x7fffff00LL || g.b.rows > 0x7fffff00LL) return false;  // 32-bit box coordinates
     if ((g.m + BM - 1) / BM * (long long)((g.n + BN - 1) / BN) > 0x7fffffffLL) return false;
     if (g.n % 8 != 0 || ((uintptr_t)g.c.ptr & 15) != 0) return false;       // 16-byte output chunks
     if (g.c.heads > 0 && g.c.dim % 8 != 0) return false;
