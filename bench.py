@@ -522,6 +522,37 @@ def run_extras(L, _lib, torch, dev, sptr, stream, peaks):
                                     "unit": "GB/s", "frac": nbytes / ms_d / 1e6 / peaks["hbm_gbs"],
                                     "frac_of_nominal_8000": nbytes / ms_d / 1e6 / NOMINAL_HBM_GBS,
                                     "peak_source": peaks["source"] + " copy"}}
+    del kc, vc, ws
+
+    # ---- the projections either side of attention at the headline shape (E = H * D = 4096):
+    # fused q/k/v projection writing (3, B, H, L, D), output projection reading (B, H, L, D)
+    B, H, S, D = (WORKLOAD[x] for x in "BHLD")
+    E, m = H * D, B * S
+    x = torch.randn((m, E), generator=gen, device=dev).to(torch.bfloat16)
+    proj = {}
+    for name, n, xh, yh in (("qkv_projection", 3 * E, 0, H), ("output_projection", E, H, 0)):
+        w = (torch.randn((E, n), generator=gen, device=dev) * 0.02).to(torch.bfloat16)
+        bias = torch.randn((n,), generator=gen, device=dev).to(torch.bfloat16)
+        dy = torch.randn((m, n), generator=gen, device=dev).to(torch.bfloat16)
+        y, dx, dw, db = torch.empty_like(dy), torch.empty_like(x), torch.empty_like(w), torch.empty_like(bias)
+
+        def lin_f():
+            _lib.check(L.ember_linear_fwd(x.data_ptr(), w.data_ptr(), bias.data_ptr(), y.data_ptr(), m, n, E, 1, xh, yh,
+                                          S, D, sptr))
+
+        def lin_b():
+            _lib.check(L.ember_linear_bwd(x.data_ptr(), w.data_ptr(), dy.data_ptr(), dx.data_ptr(), dw.data_ptr(),
+                                          db.data_ptr(), m, n, E, 1, xh, yh, S, D, sptr))
+
+        ms_lf, ms_lb = timed(lin_f, 20), timed(lin_b, 10)
+        fl = 2.0 * m * n * E
+        proj[name] = {"m": m, "n": n, "k": E, "kernel": L.ember_linear_kernel_name(0, m, n, E, 1, xh, yh, S, D).decode(),
+                      "fwd_ms": ms_lf, "fwd_tflops": fl / ms_lf / 1e9,
+                      "fwd_frac_of_measured_peak": fl / ms_lf / 1e9 / peaks["bf16_tflops"],
+                      "bwd_ms": ms_lb, "bwd_tflops": 2 * fl / ms_lb / 1e9,
+                      "bwd_frac_of_measured_peak": 2 * fl / ms_lb / 1e9 / peaks["bf16_tflops"]}
+        del w, bias, dy, y, dx, dw, db
+    extra["projections"] = proj
     return extra
 
 
@@ -563,6 +594,19 @@ def run_profile_case(args):
         fn = fwd if args.profile == "fwd" else bwd
         work = 4.0 * B * H * S * S * D / 2.0 * (1.0 if args.profile == "fwd" else 2.5)
         unit, name = "TFLOP/s", f"causal_{args.profile}_bf16_B{B}_H{H}_L{S}_D{D}"
+    elif args.profile == "linear":
+        m, n, k, heads = 8192, 6144, 2048, 16  # a q/k/v projection: x (8192, 2048) -> (3, 2, 16, 4096, 128)
+        x = torch.randn((m, k), generator=gen, device=dev).to(torch.bfloat16)
+        w = (torch.randn((k, n), generator=gen, device=dev) * 0.02).to(torch.bfloat16)
+        bias = torch.randn((n,), generator=gen, device=dev).to(torch.bfloat16)
+        y = torch.empty((m, n), device=dev, dtype=torch.bfloat16)
+
+        def fn():
+            _lib.check(L.ember_linear_fwd(x.data_ptr(), w.data_ptr(), bias.data_ptr(), y.data_ptr(), m, n, k, 1, 0, heads,
+                                          4096, D, sptr))
+
+        work = 2.0 * m * n * k
+        unit, name = "TFLOP/s", f"qkv_projection_bf16_m{m}_n{n}_k{k}"
     else:
         B, H, Lk = 8, 32, 32768
         kc = (torch.randn((B, H, Lk, D), generator=gen, device=dev) * 0.5).to(torch.bfloat16)
@@ -601,7 +645,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extra", action="store_true", help="skip the backward and decode extras at N=1")
-    ap.add_argument("--profile", choices=["fwd", "bwd", "decode"], default=None,
+    ap.add_argument("--profile", choices=["fwd", "bwd", "decode", "linear"], default=None,
                     help="run only a small single-kernel case (for ncu captures) and exit")
     args = ap.parse_args()
     if args.profile:

@@ -10,10 +10,10 @@ without the built CUDA library raises ImportError with the build command.
 import importlib
 
 __all__ = ["Tensor", "attention", "attention_forward", "attention_backward", "attention_decode", "linear_forward",
-           "linear_backward", "nn"]
+           "linear_backward", "softmax", "log_softmax", "nn", "loss"]
 
 _TENSOR_NAMES = {"Tensor", "attention", "attention_forward", "attention_backward", "attention_decode", "linear_forward",
-                 "linear_backward"}
+                 "linear_backward", "softmax", "log_softmax"}
 
 
 def __getattr__(name):
@@ -25,6 +25,6 @@ def __getattr__(name):
                 f"ember_b200 native libraries are not built ({e}); run `python -m ember_b200.build` "
                 "(needs nvcc and gcc; there is no CPU fallback for the attention path)") from e
         return getattr(mod, name)
-    if name in ("nn", "tensor", "shard", "_lib", "_core", "build"):
+    if name in ("nn", "loss", "tensor", "shard", "_lib", "_core", "build"):
         return importlib.import_module("." + name, __name__)
     raise AttributeError(f"module {__name__!r} has no attribute {name!r}")

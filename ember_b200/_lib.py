@@ -47,6 +47,10 @@ SIGNATURES = {
     "ember_linear_fwd": (_i, [_vp] * 4 + [ctypes.c_longlong] + [_i] * 7 + [_vp]),
     "ember_linear_bwd": (_i, [_vp] * 6 + [ctypes.c_longlong] + [_i] * 7 + [_vp]),
     "ember_linear_kernel_name": (ctypes.c_char_p, [_i, ctypes.c_longlong] + [_i] * 7),
+    "ember_softmax_fwd": (_i, [_vp, _vp, ctypes.c_longlong, _i, _i, _i, _vp]),
+    "ember_cross_entropy_workspace_bytes": (_sz, [ctypes.c_longlong]),
+    "ember_cross_entropy_fwd": (_i, [_vp] * 4 + [ctypes.c_longlong, _i, _i, _vp, _sz, _vp]),
+    "ember_cross_entropy_bwd": (_i, [_vp] * 3 + [ctypes.c_longlong, _i, _i, _vp]),
 }
 
 _LIB = None

@@ -1,0 +1,355 @@
+// Fused last-axis softmax, log-softmax and softmax cross-entropy (HBM-bound).
+//
+// The reference composes softmax from five operators (row max, broadcast subtract, exp, row sum,
+// broadcast divide: ember/tensor/tensor.py:430-437), each a full pass over the tensor with its own
+// allocation, and the cross-entropy loss from eight (ember/loss/losses.py:42-56). Here a row is read
+// from HBM once, kept in shared memory as float32 while its maximum and sum are formed, and the
+// result is written once: 2 (softmax) or 3 (cross-entropy: logits and targets in, probabilities
+// out) element transfers per element instead of about 12 and 20.
+//
+// A row is owned by a group of W threads of a 256-thread block: W = 32 for rows of up to 2048
+// elements (8 rows per block, warp shuffles only), W = 256 for longer rows (one row per block).
+// Rows longer than the shared-memory cache (49152 elements) are re-read from global memory instead.
+// float32 arithmetic throughout (expf/logf, not the fast intrinsics: the kernels are HBM-bound); f32 or bf16 storage; 8-element vector accesses when the row length
+// and the base addresses allow, element-wise accesses otherwise.
+#include "common.cuh"
+#include "kernels.cuh"
+
+namespace ember {
+
+namespace {
+
+constexpr int BLOCK = 256;
+constexpr int WARP_ROW_MAX_COLS = 2048;   // rows up to this length are owned by one warp
+constexpr int CACHE_COLS = 49152;         // floats of shared memory for one long row (192 KB)
+
+__device__ __forceinline__ float ldf(const float *p) { return *p; }
+__device__ __forceinline__ float ldf(const __nv_bfloat16 *p) { return __bfloat162float(*p); }
+__device__ __forceinline__ void stf(float *p, float v) { *p = v; }
+__device__ __forceinline__ void stf(__nv_bfloat16 *p, float v) { *p = __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ void load8(const float *p, float (&v)[8])
+{
+    const float4 a = *reinterpret_cast<const float4 *>(p), b = *reinterpret_cast<const float4 *>(p + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void load8(const __nv_bfloat16 *p, float (&v)[8])
+{
+    const uint4 u = *reinterpret_cast<const uint4 *>(p);
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        v[2 * i] = __uint_as_float(w[i] << 16);
+        v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+}
+__device__ __forceinline__ void store8(float *p, const float (&v)[8])
+{
+    *reinterpret_cast<float4 *>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4 *>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+__device__ __forceinline__ void store8(__nv_bfloat16 *p, const float (&v)[8])
+{
+    uint4 u;
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+        w[i] = *reinterpret_cast<const uint32_t *>(&h);
+    }
+    u.x = w[0]; u.y = w[1]; u.z = w[2]; u.w = w[3];
+    *reinterpret_cast<uint4 *>(p) = u;
+}
+
+// Reduction over the W threads that own a row. red: 8 floats of shared memory per block (W == 256).
+template <int W, bool IS_MAX>
+__device__ __forceinline__ float group_reduce(float v, float *red)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float t = __shfl_xor_sync(0xffffffffu, v, o);
+        v = IS_MAX ? fmaxf(v, t) : v + t;
+    }
+    if (W == 32) return v;
+    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    __syncthreads();  // red may still be read from the previous reduction
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float r = red[0];
+#pragma unroll
+    for (int i = 1; i < BLOCK / 32; i++) r = IS_MAX ? fmaxf(r, red[i]) : r + red[i];
+    return r;
+}
+
+enum { MODE_SOFTMAX = 0, MODE_LOG_SOFTMAX = 1, MODE_CROSS_ENTROPY = 2 };
+
+// x, y (and target): rows x cols. cache_cols: floats of shared memory per row (0 = none: re-read x).
+template <typename T, int W, int MODE, bool VEC>
+__global__ void __launch_bounds__(BLOCK) row_softmax_kernel(const T *__restrict__ x, const T *__restrict__ target,
+                                                            T *__restrict__ y, float *__restrict__ row_loss,
+                                                            long long rows, int cols, int cache_cols)
+{
+    extern __shared__ float smem[];
+    float *red = smem;  // 8 floats
+    constexpr int GROUPS = BLOCK / W;
+    const int group = threadIdx.x / W, t = threadIdx.x % W;
+    float *buf = smem + 8 + (size_t)group * cache_cols;
+    const bool cached = cache_cols >= cols;
+    constexpr int STEP = VEC ? 8 : 1;
+    // Vector path: element i of a thread's 8-element vector lies at buf[i * nvec + vector index], so
+    // that the threads of a warp touch consecutive words (each thread only ever reads back its own).
+    const int nvec = cols >> 3;
+
+    for (long long row0 = (long long)blockIdx.x * GROUPS; row0 < rows; row0 += (long long)gridDim.x * GROUPS) {
+        const long long row = row0 + group;
+        const bool active = row < rows;  // W == 256: always true; W == 32: the whole warp agrees
+        const T *xr = x + (size_t)(active ? row : 0) * cols;
+        // ---- pass 1: maximum (and fill the cache)
+        float m = -INFINITY;
+        if (active) {
+            for (int j = t * STEP; j < cols; j += W * STEP) {
+                if constexpr (VEC) {
+                    float v[8];
+                    load8(xr + j, v);
+#pragma unroll
+                    for (int i = 0; i < 8; i++) m = fmaxf(m, v[i]);
+                    if (cached) {
+#pragma unroll
+                        for (int i = 0; i < 8; i++) buf[i * nvec + (j >> 3)] = v[i];
+                    }
+                } else {
+                    const float v = ldf(xr + j);
+                    m = fmaxf(m, v);
+                    if (cached) buf[j] = v;
+                }
+            }
+        }
+        m = group_reduce<W, true>(m, red);
+        // ---- pass 2: sum of exp(x - max)
+        float s = 0.f;
+        if (active) {
+            for (int j = t * STEP; j < cols; j += W * STEP) {
+                if constexpr (VEC) {
+                    float v[8];
+                    if (cached) {
+#pragma unroll
+                        for (int i = 0; i < 8; i++) v[i] = buf[i * nvec + (j >> 3)];
+                    } else {
+                        load8(xr + j, v);
+                    }
+#pragma unroll
+                    for (int i = 0; i < 8; i++) s += expf(v[i] - m);
+                } else {
+                    s += expf((cached ? buf[j] : ldf(xr + j)) - m);
+                }
+            }
+        }
+        s = group_reduce<W, false>(s, red);
+        // ---- pass 3: results
+        const float inv = 1.f / s, lg = logf(s);
+        float loss = 0.f;
+        if (active) {
+            T *yr = y + (size_t)row * cols;
+            const T *tr = MODE == MODE_CROSS_ENTROPY ? target + (size_t)row * cols : nullptr;
+            for (int j = t * STEP; j < cols; j += W * STEP) {
+                if constexpr (VEC) {
+                    float v[8], o[8], tv[8];
+                    if (cached) {
+#pragma unroll
+                        for (int i = 0; i < 8; i++) v[i] = buf[i * nvec + (j >> 3)];
+                    } else {
+                        load8(xr + j, v);
+                    }
+                    if (MODE == MODE_CROSS_ENTROPY) load8(tr + j, tv);
+#pragma unroll
+                    for (int i = 0; i < 8; i++) {
+                        if (MODE == MODE_SOFTMAX) {
+                            o[i] = expf(v[i] - m) * inv;
+                        } else {
+                            const float lp = (v[i] - m) - lg;
+                            o[i] = MODE == MODE_LOG_SOFTMAX ? lp : expf(lp);
+                            if (MODE == MODE_CROSS_ENTROPY) loss = fmaf(tv[i], lp, loss);
+                        }
+                    }
+                    store8(yr + j, o);
+                } else {
+                    const float v = cached ? buf[j] : ldf(xr + j);
+                    float o;
+                    if (MODE == MODE_SOFTMAX) {
+                        o = expf(v - m) * inv;
+                    } else {
+                        const float lp = (v - m) - lg;
+                        o = MODE == MODE_LOG_SOFTMAX ? lp : expf(lp);
+                        if (MODE == MODE_CROSS_ENTROPY) loss = fmaf(ldf(tr + j), lp, loss);
+                    }
+                    stf(yr + j, o);
+                }
+            }
+        }
+        if (MODE == MODE_CROSS_ENTROPY) {
+            loss = group_reduce<W, false>(loss, red);
+            if (active && t == 0) row_loss[row] = loss;
+        }
+        if (W == 256) __syncthreads();  // the cache is rewritten by the next row
+    }
+}
+
+// loss = -(sum of the row losses) / rows, added in a fixed order.
+__global__ void __launch_bounds__(BLOCK) loss_finalize_kernel(const float *row_loss, long long rows, float *loss)
+{
+    __shared__ float red[BLOCK];
+    float s = 0.f;
+    for (long long r = threadIdx.x; r < rows; r += BLOCK) s += row_loss[r];
+    red[threadIdx.x] = s;
+    __syncthreads();
+    for (int o = BLOCK / 2; o > 0; o >>= 1) {
+        if (threadIdx.x < o) red[threadIdx.x] += red[threadIdx.x + o];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) *loss = -red[0] / (float)rows;
+}
+
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(BLOCK) ce_backward_kernel(const T *__restrict__ probs, const T *__restrict__ target,
+                                                            T *__restrict__ grad, size_t total, float inv_n)
+{
+    constexpr int STEP = VEC ? 8 : 1;
+    for (size_t i = ((size_t)blockIdx.x * BLOCK + threadIdx.x) * STEP; i < total; i += (size_t)gridDim.x * BLOCK * STEP) {
+        if constexpr (VEC) {
+            float p[8], t[8], g[8];
+            load8(probs + i, p);
+            load8(target + i, t);
+#pragma unroll
+            for (int k = 0; k < 8; k++) g[k] = (p[k] - t[k]) * inv_n;
+            store8(grad + i, g);
+        } else {
+            stf(grad + i, (ldf(probs + i) - ldf(target + i)) * inv_n);
+        }
+    }
+}
+
+bool aligned16(const void *p) { return ((uintptr_t)p & 15) == 0; }
+
+template <typename T, int MODE>
+int launch_rows(const T *x, const T *target, T *y, float *row_loss, long long rows, int cols, int sm_count,
+                cudaStream_t s)
+{
+    const bool vec = cols % 8 == 0 && aligned16(x) && aligned16(y) && (MODE != MODE_CROSS_ENTROPY || aligned16(target));
+    const bool warp_rows = cols <= WARP_ROW_MAX_COLS;
+    const int groups = warp_rows ? BLOCK / 32 : 1;
+    const int cache_cols = warp_rows ? cols : (cols <= CACHE_COLS ? cols : 0);
+    const size_t smem = (8 + (size_t)groups * cache_cols) * sizeof(float);
+    const long long blocks_needed = (rows + groups - 1) / groups;
+    const long long cap = (long long)(sm_count > 0 ? sm_count : 148) * 16;
+    const int grid = (int)(blocks_needed < cap ? blocks_needed : cap);
+#define EMBER_LAUNCH_ROWS(W, VEC)                                                                               \
+    do {                                                                                                        \
+        auto kern = row_softmax_kernel<T, W, MODE, VEC>;                                                        \
+        EMBER_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));     \
+        kern<<<grid, BLOCK, smem, s>>>(x, target, y, row_loss, rows, cols, cache_cols);                         \
+    } while (0)
+    if (warp_rows) {
+        if (vec) EMBER_LAUNCH_ROWS(32, true); else EMBER_LAUNCH_ROWS(32, false);
+    } else {
+        if (vec) EMBER_LAUNCH_ROWS(256, true); else EMBER_LAUNCH_ROWS(256, false);
+    }
+#undef EMBER_LAUNCH_ROWS
+    EMBER_CUDA_TRY(cudaGetLastError());
+    return EMBER_OK;
+}
+
+int check_rows(const char *fn, long long rows, int cols, int dtype)
+{
+    EMBER_REQUIRE(dtype == EMBER_F32 || dtype == EMBER_BF16, "%s: unknown dtype %d", fn, dtype);
+    EMBER_REQUIRE(rows > 0 && cols > 0, "%s: extents must be positive, got rows=%lld cols=%d", fn, rows, cols);
+    return EMBER_OK;
+}
+
+}  // namespace
+
+}  // namespace ember
+
+using namespace ember;
+
+extern "C" {
+
+int ember_softmax_fwd(const void *x, void *y, long long rows, int cols, int dtype, int log_softmax, void *stream)
+{
+    int rc = check_rows("ember_softmax_fwd", rows, cols, dtype);
+    if (rc) return rc;
+    EMBER_REQUIRE(x && y, "ember_softmax_fwd: NULL tensor pointer");
+    DeviceState *st = device_state();
+    if (!st) return EMBER_ERR_CUDA;
+    cudaStream_t s = pick_stream(stream, st);
+    if (dtype == EMBER_BF16) {
+        auto xp = (const __nv_bfloat16 *)x;
+        auto yp = (__nv_bfloat16 *)y;
+        return log_softmax ? launch_rows<__nv_bfloat16, MODE_LOG_SOFTMAX>(xp, nullptr, yp, nullptr, rows, cols, st->sm_count, s)
+                           : launch_rows<__nv_bfloat16, MODE_SOFTMAX>(xp, nullptr, yp, nullptr, rows, cols, st->sm_count, s);
+    }
+    auto xp = (const float *)x;
+    auto yp = (float *)y;
+    return log_softmax ? launch_rows<float, MODE_LOG_SOFTMAX>(xp, nullptr, yp, nullptr, rows, cols, st->sm_count, s)
+                       : launch_rows<float, MODE_SOFTMAX>(xp, nullptr, yp, nullptr, rows, cols, st->sm_count, s);
+}
+
+size_t ember_cross_entropy_workspace_bytes(long long rows)
+{
+    return rows > 0 ? align_up((size_t)rows * sizeof(float), 256) : 0;
+}
+
+int ember_cross_entropy_fwd(const void *pred, const void *target, void *probs, float *loss, long long rows, int cols,
+                            int dtype, void *workspace, size_t workspace_bytes, void *stream)
+{
+    int rc = check_rows("ember_cross_entropy_fwd", rows, cols, dtype);
+    if (rc) return rc;
+    EMBER_REQUIRE(pred && target && probs && loss, "ember_cross_entropy_fwd: NULL tensor pointer");
+    const size_t need = ember_cross_entropy_workspace_bytes(rows);
+    if (!workspace || workspace_bytes < need) {
+        set_error("ember_cross_entropy_fwd: workspace of %zu bytes needed, %zu given", need, workspace_bytes);
+        return EMBER_ERR_WORKSPACE;
+    }
+    DeviceState *st = device_state();
+    if (!st) return EMBER_ERR_CUDA;
+    cudaStream_t s = pick_stream(stream, st);
+    float *row_loss = (float *)workspace;
+    if (dtype == EMBER_BF16)
+        rc = launch_rows<__nv_bfloat16, MODE_CROSS_ENTROPY>((const __nv_bfloat16 *)pred, (const __nv_bfloat16 *)target,
+                                                           (__nv_bfloat16 *)probs, row_loss, rows, cols, st->sm_count, s);
+    else
+        rc = launch_rows<float, MODE_CROSS_ENTROPY>((const float *)pred, (const float *)target, (float *)probs, row_loss,
+                                                   rows, cols, st->sm_count, s);
+    if (rc) return rc;
+    loss_finalize_kernel<<<1, BLOCK, 0, s>>>(row_loss, rows, loss);
+    EMBER_CUDA_TRY(cudaGetLastError());
+    return EMBER_OK;
+}
+
+int ember_cross_entropy_bwd(const void *probs, const void *target, void *grad, long long rows, int cols, int dtype,
+                            void *stream)
+{
+    int rc = check_rows("ember_cross_entropy_bwd", rows, cols, dtype);
+    if (rc) return rc;
+    EMBER_REQUIRE(probs && target && grad, "ember_cross_entropy_bwd: NULL tensor pointer");
+    DeviceState *st = device_state();
+    if (!st) return EMBER_ERR_CUDA;
+    cudaStream_t s = pick_stream(stream, st);
+    const size_t total = (size_t)rows * cols;
+    const bool vec = total % 8 == 0 && aligned16(probs) && aligned16(target) && aligned16(grad);
+    const size_t per_block = (size_t)BLOCK * (vec ? 8 : 1);
+    const size_t want = (total + per_block - 1) / per_block;
+    const size_t cap = (size_t)(st->sm_count > 0 ? st->sm_count : 148) * 32;
+    const int grid = (int)(want < cap ? want : cap);
+    const float inv_n = 1.f / (float)rows;
+    if (dtype == EMBER_BF16) {
+        if (vec) ce_backward_kernel<__nv_bfloat16, true><<<grid, BLOCK, 0, s>>>((const __nv_bfloat16 *)probs, (const __nv_bfloat16 *)target, (__nv_bfloat16 *)grad, total, inv_n);
+        else ce_backward_kernel<__nv_bfloat16, false><<<grid, BLOCK, 0, s>>>((const __nv_bfloat16 *)probs, (const __nv_bfloat16 *)target, (__nv_bfloat16 *)grad, total, inv_n);
+    } else {
+        if (vec) ce_backward_kernel<float, true><<<grid, BLOCK, 0, s>>>((const float *)probs, (const float *)target, (float *)grad, total, inv_n);
+        else ce_backward_kernel<float, false><<<grid, BLOCK, 0, s>>>((const float *)probs, (const float *)target, (float *)grad, total, inv_n);
+    }
+    EMBER_CUDA_TRY(cudaGetLastError());
+    return EMBER_OK;
+}
+
+}  // extern "C"

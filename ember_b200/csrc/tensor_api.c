@@ -452,6 +452,91 @@ static PyObject *_linear_bwd(PyObject *module, PyObject *args)
     return Py_BuildValue("(NNN)", odx, dw, odb);
 }
 
+/* _softmax(x, rows, cols, log) -> y: softmax (log = 0) or log-softmax (log = 1) over the last axis. */
+static PyObject *_softmax(PyObject *module, PyObject *args)
+{
+    _Tensor *x;
+    long long rows;
+    int cols, lg;
+    if (!PyArg_ParseTuple(args, "O!Lii", &_TensorType, &x, &rows, &cols, &lg)) return NULL;
+    if (rows <= 0 || cols <= 0 || x->size64 != rows * cols) {
+        PyErr_Format(PyExc_ValueError, "softmax: size mismatch: tensor has %lld elements, rows*cols = %lld", x->size64,
+                     rows * cols);
+        return NULL;
+    }
+    _Tensor *y = alloc_result(x->size64, x->dtype);
+    if (!y) return NULL;
+    int rc = ember_softmax_fwd(x->d_ptr, y->d_ptr, rows, cols, x->dtype, lg, NULL);
+    if (rc) {
+        Py_DECREF(y);
+        return raise_status(rc);
+    }
+    return (PyObject *)y;
+}
+
+/* _cross_entropy_fwd(pred, target, rows, cols) -> (loss, probs); loss is a 1-element float32 tensor.
+ * CrossEntropyLoss.forward of the reference (ember/loss/losses.py:42-51). */
+static PyObject *_cross_entropy_fwd(PyObject *module, PyObject *args)
+{
+    _Tensor *pred, *target;
+    long long rows;
+    int cols;
+    if (!PyArg_ParseTuple(args, "O!O!Li", &_TensorType, &pred, &_TensorType, &target, &rows, &cols)) return NULL;
+    if (rows <= 0 || cols <= 0 || pred->size64 != rows * cols || target->size64 != pred->size64) {
+        PyErr_Format(PyExc_ValueError, "cross_entropy: size mismatch: pred %lld, target %lld, rows*cols = %lld",
+                     pred->size64, target->size64, rows * cols);
+        return NULL;
+    }
+    if (pred->dtype != target->dtype) {
+        PyErr_SetString(PyExc_TypeError, "cross_entropy: pred and target must share a dtype");
+        return NULL;
+    }
+    _Tensor *probs = alloc_result(pred->size64, pred->dtype), *loss = NULL;
+    void *ws = NULL;
+    const size_t wsn = ember_cross_entropy_workspace_bytes(rows);
+    if (probs) loss = alloc_result(1, EMBER_F32);
+    if (loss) {
+        ws = alloc_memory(wsn);
+        if (!ws) PyErr_Format(PyExc_MemoryError, "Failed to allocate device memory: %s", ember_last_error());
+    }
+    if (!ws) {
+        Py_XDECREF(probs);
+        Py_XDECREF(loss);
+        return NULL;
+    }
+    int rc = ember_cross_entropy_fwd(pred->d_ptr, target->d_ptr, probs->d_ptr, (float *)loss->d_ptr, rows, cols, pred->dtype,
+                                     ws, wsn, NULL);
+    free_memory(ws); /* stream-ordered: released after the kernels that use it */
+    if (rc) {
+        Py_DECREF(probs);
+        Py_DECREF(loss);
+        return raise_status(rc);
+    }
+    return Py_BuildValue("(NN)", loss, probs);
+}
+
+/* _cross_entropy_bwd(probs, target, rows, cols) -> grad = (probs - target) / rows */
+static PyObject *_cross_entropy_bwd(PyObject *module, PyObject *args)
+{
+    _Tensor *probs, *target;
+    long long rows;
+    int cols;
+    if (!PyArg_ParseTuple(args, "O!O!Li", &_TensorType, &probs, &_TensorType, &target, &rows, &cols)) return NULL;
+    if (rows <= 0 || cols <= 0 || probs->size64 != rows * cols || target->size64 != probs->size64 ||
+        probs->dtype != target->dtype) {
+        PyErr_SetString(PyExc_ValueError, "cross_entropy_backward: probs and target must both be (rows, cols) of one dtype");
+        return NULL;
+    }
+    _Tensor *g = alloc_result(probs->size64, probs->dtype);
+    if (!g) return NULL;
+    int rc = ember_cross_entropy_bwd(probs->d_ptr, target->d_ptr, g->d_ptr, rows, cols, probs->dtype, NULL);
+    if (rc) {
+        Py_DECREF(g);
+        return raise_status(rc);
+    }
+    return (PyObject *)g;
+}
+
 static PyObject *_sync(PyObject *module, PyObject *noargs)
 {
     sync_device();
@@ -477,6 +562,9 @@ static PyMethodDef module_methods[] = {OP_METHOD(_from_numpy),
                                        OP_METHOD(_attention_decode),
                                        OP_METHOD(_linear_fwd),
                                        OP_METHOD(_linear_bwd),
+                                       OP_METHOD(_softmax),
+                                       OP_METHOD(_cross_entropy_fwd),
+                                       OP_METHOD(_cross_entropy_bwd),
                                        {"_sync", (PyCFunction)_sync, METH_NOARGS, "Wait for the library stream"},
                                        {NULL, NULL, 0, NULL}};
 

@@ -213,3 +213,27 @@ def linear_backward(x: Tensor, w: Tensor, grad_y: Tensor, *, x_heads: int = 0, y
                                    int(bool(need_grad_x)), int(bool(need_grad_b)))
     return (Tensor._from_core(dx, x.shape, x.dtype) if dx is not None else None, Tensor._from_core(dw, w.shape, w.dtype),
             Tensor._from_core(db, (n,), w.dtype) if db is not None else None)
+
+
+def _rows_cols(a: Tensor, fn: str):
+    if not isinstance(a, Tensor):
+        raise TypeError(f"{fn} expects a Tensor, got '{type(a).__name__}'")
+    if len(a.shape) < 1:
+        raise ValueError(f"{fn} needs at least one axis")
+    return a.size // a.shape[-1], a.shape[-1]
+
+
+def softmax(a: Tensor, axis: int = -1) -> Tensor:
+    """Numerically-stable softmax along the last axis (the reference's ``softmax``,
+    ember/tensor/tensor.py:430-437, as one fused pass)."""
+    if axis not in (-1, len(a.shape) - 1):
+        raise ValueError("softmax: only the last axis is supported by the fused kernel")
+    rows, cols = _rows_cols(a, "softmax()")
+    return Tensor._from_core(_core._softmax(a._core, rows, cols, 0), a.shape, a.dtype)
+
+
+def log_softmax(a: Tensor, axis: int = -1) -> Tensor:
+    if axis not in (-1, len(a.shape) - 1):
+        raise ValueError("log_softmax: only the last axis is supported by the fused kernel")
+    rows, cols = _rows_cols(a, "log_softmax()")
+    return Tensor._from_core(_core._softmax(a._core, rows, cols, 1), a.shape, a.dtype)

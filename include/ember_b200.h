@@ -189,6 +189,27 @@ EMBER_API int ember_linear_bwd(const void *x, const void *w, const void *grad_y,
 EMBER_API const char *ember_linear_kernel_name(int product, long long m, int n, int k, int dtype, int x_heads,
                                                int y_heads, int seq, int head_dim);
 
+/* ---- Fused softmax and softmax cross-entropy --------------------------------
+ *
+ * ember_softmax_fwd replaces the reference's softmax over the last axis
+ * (ember/tensor/tensor.py:430-437: amax, broadcast subtract, exp, sum, broadcast divide, i.e. five
+ * passes and five allocations) with one read and one write per element; log_softmax != 0 gives
+ * x - max - log(sum(exp(x - max))) instead. x and y are (rows, cols) row-major of `dtype`.
+ *
+ * ember_cross_entropy_fwd / _bwd replace CrossEntropyLoss.forward / .backward
+ * (ember/loss/losses.py:42-56): pred are logits and target probabilities (one-hot in the
+ * reference's use), both (rows, cols); probs receives softmax(pred) (the reference caches it for the
+ * backward), *loss (one float32 in device memory) receives -sum(target * log_softmax(pred)) / rows.
+ * workspace: ember_cross_entropy_workspace_bytes(rows) bytes of device memory (one partial per row,
+ * added in a fixed order). backward: grad = (probs - target) / rows. */
+EMBER_API int ember_softmax_fwd(const void *x, void *y, long long rows, int cols, int dtype, int log_softmax,
+                                void *stream);
+EMBER_API size_t ember_cross_entropy_workspace_bytes(long long rows);
+EMBER_API int ember_cross_entropy_fwd(const void *pred, const void *target, void *probs, float *loss, long long rows,
+                                      int cols, int dtype, void *workspace, size_t workspace_bytes, void *stream);
+EMBER_API int ember_cross_entropy_bwd(const void *probs, const void *target, void *grad, long long rows, int cols,
+                                      int dtype, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

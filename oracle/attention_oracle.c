@@ -309,3 +309,64 @@ void oracle_linear_bwd(const float *x, const float *w, const float *dy, float *d
     free(xt);
     free(wt);
 }
+
+/* ------------------------------------------------------------------------
+ * Softmax over the last axis and the softmax cross-entropy loss, as the
+ * reference composes them from its operators.
+ *
+ *   softmax (ember/tensor/tensor.py:430-437):
+ *       shifted = a - amax(a, -1, keepdims) ; e = exp(shifted) ; e / sum(e, -1, keepdims)
+ *   CrossEntropyLoss.forward (ember/loss/losses.py:42-51):
+ *       shifted   = pred - amax(pred, -1, keepdims)
+ *       log_probs = shifted - log(sum(exp(shifted), -1, keepdims))
+ *       probs     = exp(log_probs)
+ *       loss      = -sum(target * log_probs) / n          n = rows; sum() over ALL elements
+ *   CrossEntropyLoss.backward (losses.py:53-56):  (probs - target) / n
+ *
+ * amax: fmaxf left to right (src/tensor/operators_cpu.c:107-120); row sums fp32
+ * left to right (:92-105); the loss sum is the flat fp32 sum (:78-83), negated
+ * and divided in Python floats (double); "/ n" in backward is a float divide by
+ * (float)n (src/tensor/operators.def:58).
+ * ------------------------------------------------------------------------ */
+void oracle_softmax(const float *x, float *y, int rows, int cols)
+{
+    for (int r = 0; r < rows; r++) {
+        const float *a = x + (size_t)r * cols;
+        float *o = y + (size_t)r * cols;
+        float m = a[0];
+        for (int j = 1; j < cols; j++) m = fmaxf(m, a[j]);
+        float s = 0.0f;
+        for (int j = 0; j < cols; j++) {
+            o[j] = expf(a[j] - m);
+            s += o[j];
+        }
+        for (int j = 0; j < cols; j++) o[j] = o[j] / s;
+    }
+}
+
+double oracle_cross_entropy_fwd(const float *pred, const float *target, float *probs, int rows, int cols)
+{
+    float total = 0.0f;
+    for (int r = 0; r < rows; r++) {
+        const float *a = pred + (size_t)r * cols, *t = target + (size_t)r * cols;
+        float *p = probs + (size_t)r * cols;
+        float m = a[0];
+        for (int j = 1; j < cols; j++) m = fmaxf(m, a[j]);
+        float s = 0.0f;
+        for (int j = 0; j < cols; j++) s += expf(a[j] - m);
+        const float lg = logf(s);
+        for (int j = 0; j < cols; j++) {
+            const float lp = (a[j] - m) - lg;
+            p[j] = expf(lp);
+            total += t[j] * lp;
+        }
+    }
+    return -(double)total / (double)rows;
+}
+
+void oracle_cross_entropy_bwd(const float *probs, const float *target, float *grad, int rows, int cols)
+{
+    const float n = (float)rows;
+    const size_t total = (size_t)rows * cols;
+    for (size_t i = 0; i < total; i++) grad[i] = (probs[i] - target[i]) / n;
+}

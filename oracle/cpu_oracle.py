@@ -40,6 +40,12 @@ def lib() -> ctypes.CDLL:
         L.oracle_linear_fwd.restype = None
         L.oracle_linear_bwd.argtypes = [_f32p] * 6 + [ctypes.c_int] * 3
         L.oracle_linear_bwd.restype = None
+        L.oracle_softmax.argtypes = [_f32p, _f32p, ctypes.c_int, ctypes.c_int]
+        L.oracle_softmax.restype = None
+        L.oracle_cross_entropy_fwd.argtypes = [_f32p] * 3 + [ctypes.c_int] * 2
+        L.oracle_cross_entropy_fwd.restype = ctypes.c_double
+        L.oracle_cross_entropy_bwd.argtypes = [_f32p] * 3 + [ctypes.c_int] * 2
+        L.oracle_cross_entropy_bwd.restype = None
         L.oracle_set_threads.argtypes = [ctypes.c_int]
         _LIB = L
     return _LIB
@@ -107,3 +113,30 @@ def linear_bwd(x, w, dy):
     dx, dw, db = np.empty((m, k), np.float32), np.empty((k, n), np.float32), np.empty((n,), np.float32)
     lib().oracle_linear_bwd(_p(x), _p(w), _p(dy), _p(dx), _p(dw), _p(db), m, n, k)
     return dx, dw, db
+
+
+def softmax(x):
+    """Softmax over the last axis, as the reference composes it (ember/tensor/tensor.py:430-437)."""
+    x = _prep(x)
+    cols = x.shape[-1]
+    y = np.empty_like(x)
+    lib().oracle_softmax(_p(x), _p(y), x.size // cols, cols)
+    return y
+
+
+def cross_entropy_fwd(pred, target):
+    """Returns (loss, probs) of the reference's CrossEntropyLoss.forward (ember/loss/losses.py:42-51)."""
+    pred, target = _prep(pred), _prep(target)
+    rows, cols = pred.shape
+    probs = np.empty_like(pred)
+    loss = lib().oracle_cross_entropy_fwd(_p(pred), _p(target), _p(probs), rows, cols)
+    return float(loss), probs
+
+
+def cross_entropy_bwd(probs, target):
+    """(probs - target) / n of CrossEntropyLoss.backward (ember/loss/losses.py:53-56)."""
+    probs, target = _prep(probs), _prep(target)
+    rows, cols = probs.shape
+    grad = np.empty_like(probs)
+    lib().oracle_cross_entropy_bwd(_p(probs), _p(target), _p(grad), rows, cols)
+    return grad

@@ -41,8 +41,14 @@ def lib():
         L.exponent_tensor.argtypes = [_f, _f, ctypes.c_int]
         L.max_axis.argtypes = [_f, _f] + [ctypes.c_int] * 3
         L.sum_axis.argtypes = [_f, _f] + [ctypes.c_int] * 3
+        L.log_tensor.argtypes = [_f, _f, ctypes.c_int]
+        L.sub_tensor.argtypes = [_f, _f, _f, ctypes.c_int]
+        L.truediv_scalar.argtypes = [_f, ctypes.c_float, _f, ctypes.c_int]
+        L.sum.argtypes = [_f, ctypes.c_int]
+        L.sum.restype = ctypes.c_float
         for n in ("matmul_batched", "mul_scalar", "mul_tensor", "add_broadcasted", "sub_broadcasted",
-                  "truediv_broadcasted", "exponent_tensor", "max_axis", "sum_axis"):
+                  "truediv_broadcasted", "exponent_tensor", "max_axis", "sum_axis", "log_tensor", "sub_tensor",
+                  "truediv_scalar"):
             getattr(L, n).restype = None
         _LIB = L
     return _LIB
@@ -171,3 +177,42 @@ def linear_bwd(x, w, dy):
     lib().sum_axis(_p(dy), _p(db), 1, n, m)
     dx = _mm(dy, np.ascontiguousarray(w.T))
     return dx, dw, db
+
+
+def softmax(x):
+    """ember.softmax(x, axis=-1) on the reference's compiled C operators (2-D input)."""
+    x = np.ascontiguousarray(x, np.float32)
+    p, _, _ = _softmax_rows(x.copy())
+    return p
+
+
+def cross_entropy_fwd(pred, target):
+    """CrossEntropyLoss.forward (ember/loss/losses.py:42-51) op by op; returns (loss, probs)."""
+    pred, target = (np.ascontiguousarray(t, np.float32) for t in (pred, target))
+    rows, cols = pred.shape
+    L = lib()
+    mx = np.empty((rows, 1), np.float32)
+    L.max_axis(_p(pred), _p(mx), rows, 1, cols)
+    shifted = _bcast("sub", pred, mx, (1, 0))
+    e = np.empty_like(shifted)
+    L.exponent_tensor(_p(shifted), _p(e), e.size)
+    sm = np.empty((rows, 1), np.float32)
+    L.sum_axis(_p(e), _p(sm), rows, 1, cols)
+    lg = np.empty_like(sm)
+    L.log_tensor(_p(sm), _p(lg), rows)
+    logp = _bcast("sub", shifted, lg, (1, 0))
+    probs = np.empty_like(logp)
+    L.exponent_tensor(_p(logp), _p(probs), probs.size)
+    prod = np.empty_like(logp)
+    L.mul_tensor(_p(target), _p(logp), _p(prod), prod.size)
+    total = L.sum(_p(prod), prod.size)
+    return -float(total) / rows, probs
+
+
+def cross_entropy_bwd(probs, target):
+    probs, target = (np.ascontiguousarray(t, np.float32) for t in (probs, target))
+    d = np.empty_like(probs)
+    lib().sub_tensor(_p(probs), _p(target), _p(d), d.size)
+    g = np.empty_like(d)
+    lib().truediv_scalar(_p(d), ctypes.c_float(float(probs.shape[0])), _p(g), d.size)
+    return g

@@ -42,6 +42,22 @@ def linear_golden_inputs(meta):
     return x, w, b, normal(seed + 3, (m, n))
 
 
+@pytest.fixture(scope="session")
+def softmax_golden():
+    return np.load(os.path.join(ROOT, "tests", "golden", "softmax_golden.npz"))
+
+
+def softmax_golden_inputs(meta):
+    """Logits and one-hot targets of one softmax_golden.npz case."""
+    from inputs import normal
+
+    rows, cols, seed = (int(x) for x in meta)
+    x = normal(seed, (rows, cols)) * np.float32(3.0)
+    target = np.zeros((rows, cols), np.float32)
+    target[np.arange(rows), (7 * np.arange(rows)) % cols] = 1.0
+    return x, target
+
+
 def golden_inputs(meta, with_dout=False):
     from inputs import normal
 

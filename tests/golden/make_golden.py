@@ -53,6 +53,15 @@ LINEAR_CASES = {
 }
 
 
+SOFTMAX_CASES = {
+    # name: (rows, cols, seed) -- em.softmax (ember/tensor/tensor.py:430-437) and the reference's
+    # CrossEntropyLoss (ember/loss/losses.py:30-56) with one-hot targets at column (7 * row) % cols
+    "sm_small": (4, 7, 21),
+    "sm_ragged": (33, 130, 22),
+    "sm_wide": (6, 5000, 23),
+}
+
+
 def import_reference():
     tmp = tempfile.mkdtemp(prefix="ember_ref_")
     shutil.copytree(os.path.join(REF, "ember"), os.path.join(tmp, "ember"))
@@ -122,6 +131,21 @@ def main():
             y.to_np(), gx.to_np(), gw.to_np(), gb.to_np())
         print(name, "ok", lin[name + "/y"].shape)
     np.savez_compressed(os.path.join(HERE, "linear_golden.npz"), **lin)
+
+    sm = {}
+    for name, (rows, cols, seed) in SOFTMAX_CASES.items():
+        x = normal(seed, (rows, cols)) * np.float32(3.0)
+        target = np.zeros((rows, cols), np.float32)
+        target[np.arange(rows), (7 * np.arange(rows)) % cols] = 1.0
+        loss_fn = em.loss.CrossEntropyLoss()
+        loss = loss_fn.forward(T(x), T(target))
+        sm[name + "/meta"] = np.array([rows, cols, seed], np.int64)
+        sm[name + "/softmax"] = em.softmax(T(x), axis=-1).to_np()
+        sm[name + "/loss"] = np.float64(loss)
+        sm[name + "/probs"] = loss_fn.probs.to_np()
+        sm[name + "/grad"] = loss_fn.backward().to_np()
+        print(name, "ok", float(loss))
+    np.savez_compressed(os.path.join(HERE, "softmax_golden.npz"), **sm)
 
 
 if __name__ == "__main__":

@@ -3,7 +3,7 @@ own compiled operators (when that build is present) and against float64 NumPy.""
 import numpy as np
 import pytest
 
-from conftest import golden_inputs, linear_golden_inputs, seeded
+from conftest import golden_inputs, linear_golden_inputs, seeded, softmax_golden_inputs
 from oracle import cpu_oracle, ref_ops
 
 CASES = ["c1_fwd_f32", "c1_causal", "ragged_causal", "ragged_noncausal", "decode", "d128"]
@@ -102,3 +102,25 @@ def test_linear_oracle_matches_compiled_reference_ops(mkn):
     assert np.array_equal(cpu_oracle.linear_fwd(x, w, b), ref_ops.linear_fwd(x, w, b))
     for a, c in zip(cpu_oracle.linear_bwd(x, w, dy), ref_ops.linear_bwd(x, w, dy)):
         assert np.array_equal(a, c)
+
+
+@pytest.mark.parametrize("name", ["sm_small", "sm_ragged", "sm_wide"])
+def test_softmax_and_cross_entropy_oracle_match_golden_bit_for_bit(softmax_golden, name):
+    """The golden file holds em.softmax and the reference's CrossEntropyLoss (loss, cached probs, gradient)."""
+    x, target = softmax_golden_inputs(softmax_golden[name + "/meta"])
+    assert np.array_equal(cpu_oracle.softmax(x), softmax_golden[name + "/softmax"])
+    loss, probs = cpu_oracle.cross_entropy_fwd(x, target)
+    assert loss == float(softmax_golden[name + "/loss"])
+    assert np.array_equal(probs, softmax_golden[name + "/probs"])
+    assert np.array_equal(cpu_oracle.cross_entropy_bwd(probs, target), softmax_golden[name + "/grad"])
+
+
+@pytest.mark.skipif(not ref_ops.available(), reason="oracle/_ref not built (needs the reference checkout)")
+def test_softmax_and_cross_entropy_oracle_match_compiled_reference_ops():
+    x = seeded((40, 257), 9, 3.0)
+    target = np.zeros_like(x)
+    target[np.arange(40), np.arange(40) * 5 % 257] = 1.0
+    assert np.array_equal(cpu_oracle.softmax(x), ref_ops.softmax(x))
+    (l1, p1), (l2, p2) = cpu_oracle.cross_entropy_fwd(x, target), ref_ops.cross_entropy_fwd(x, target)
+    assert l1 == l2 and np.array_equal(p1, p2)
+    assert np.array_equal(cpu_oracle.cross_entropy_bwd(p1, target), ref_ops.cross_entropy_bwd(p2, target))
