@@ -553,6 +553,46 @@ def run_extras(L, _lib, torch, dev, sptr, stream, peaks):
                       "bwd_frac_of_measured_peak": 2 * fl / ms_lb / 1e9 / peaks["bf16_tflops"]}
         del w, bias, dy, y, dx, dw, db
     extra["projections"] = proj
+    del x
+
+    # ---- fused softmax (rows of attention-score length) and softmax cross-entropy (a vocabulary-
+    # sized classifier head): HBM-bound, algorithmic bytes = one read and one write per element
+    # (cross-entropy: logits and targets read, probabilities written)
+    rows, cols = 65536, 4096
+    xs = (torch.randn((rows, cols), generator=gen, device=dev) * 3).to(torch.bfloat16)
+    ys = torch.empty_like(xs)
+
+    def sm():
+        _lib.check(L.ember_softmax_fwd(xs.data_ptr(), ys.data_ptr(), rows, cols, 1, 0, sptr))
+
+    ms_s = timed(sm, 20)
+    nb = 2.0 * rows * cols * 2
+    extra["softmax"] = {"workload": f"softmax_bf16_rows{rows}_cols{cols}", "ms": ms_s, "gbs": nb / ms_s / 1e6,
+                        "roofline": {"bound": "hbm", "achieved": nb / ms_s / 1e6, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                                     "frac": nb / ms_s / 1e6 / peaks["hbm_gbs"], "peak_source": peaks["source"] + " copy"}}
+    del xs, ys
+    rows, cols = 8192, 32768
+    pred = (torch.randn((rows, cols), generator=gen, device=dev) * 3).to(torch.bfloat16)
+    tgt = torch.zeros((rows, cols), device=dev, dtype=torch.bfloat16)
+    tgt[torch.arange(rows, device=dev), torch.randint(0, cols, (rows,), generator=gen, device=dev)] = 1
+    probs, grad = torch.empty_like(pred), torch.empty_like(pred)
+    loss = torch.zeros(1, device=dev, dtype=torch.float32)
+    wn = L.ember_cross_entropy_workspace_bytes(rows)
+    wsc = torch.empty(wn, device=dev, dtype=torch.uint8)
+
+    def ce_f():
+        _lib.check(L.ember_cross_entropy_fwd(pred.data_ptr(), tgt.data_ptr(), probs.data_ptr(), loss.data_ptr(), rows, cols,
+                                             1, wsc.data_ptr(), wn, sptr))
+
+    def ce_b():
+        _lib.check(L.ember_cross_entropy_bwd(probs.data_ptr(), tgt.data_ptr(), grad.data_ptr(), rows, cols, 1, sptr))
+
+    ms_cf, ms_cb = timed(ce_f, 10), timed(ce_b, 10)
+    nb = 3.0 * rows * cols * 2
+    extra["cross_entropy"] = {"workload": f"cross_entropy_bf16_rows{rows}_cols{cols}", "fwd_ms": ms_cf,
+                              "fwd_gbs": nb / ms_cf / 1e6, "fwd_frac_of_measured_copy": nb / ms_cf / 1e6 / peaks["hbm_gbs"],
+                              "bwd_ms": ms_cb, "bwd_gbs": nb / ms_cb / 1e6,
+                              "bwd_frac_of_measured_copy": nb / ms_cb / 1e6 / peaks["hbm_gbs"], "loss": float(loss[0])}
     return extra
 
 
@@ -594,6 +634,16 @@ def run_profile_case(args):
         fn = fwd if args.profile == "fwd" else bwd
         work = 4.0 * B * H * S * S * D / 2.0 * (1.0 if args.profile == "fwd" else 2.5)
         unit, name = "TFLOP/s", f"causal_{args.profile}_bf16_B{B}_H{H}_L{S}_D{D}"
+    elif args.profile == "softmax":
+        rows, cols = 32768, 4096  # 268 MB in, 268 MB out
+        xs = (torch.randn((rows, cols), generator=gen, device=dev) * 3).to(torch.bfloat16)
+        ys = torch.empty_like(xs)
+
+        def fn():
+            _lib.check(L.ember_softmax_fwd(xs.data_ptr(), ys.data_ptr(), rows, cols, 1, 0, sptr))
+
+        work = 2.0 * rows * cols * 2
+        unit, name = "GB/s", f"softmax_bf16_rows{rows}_cols{cols}"
     elif args.profile == "linear":
         m, n, k, heads = 8192, 6144, 2048, 16  # a q/k/v projection: x (8192, 2048) -> (3, 2, 16, 4096, 128)
         x = torch.randn((m, k), generator=gen, device=dev).to(torch.bfloat16)
@@ -645,7 +695,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extra", action="store_true", help="skip the backward and decode extras at N=1")
-    ap.add_argument("--profile", choices=["fwd", "bwd", "decode", "linear"], default=None,
+    ap.add_argument("--profile", choices=["fwd", "bwd", "decode", "linear", "softmax"], default=None,
                     help="run only a small single-kernel case (for ncu captures) and exit")
     args = ap.parse_args()
     if args.profile:

@@ -7,11 +7,14 @@
 // result is written once: 2 (softmax) or 3 (cross-entropy: logits and targets in, probabilities
 // out) element transfers per element instead of about 12 and 20.
 //
-// A row is owned by a group of W threads of a 256-thread block: W = 32 for rows of up to 2048
-// elements (8 rows per block, warp shuffles only), W = 256 for longer rows (one row per block).
-// Rows longer than the shared-memory cache (49152 elements) are re-read from global memory instead.
-// float32 arithmetic throughout (expf/logf, not the fast intrinsics: the kernels are HBM-bound); f32 or bf16 storage; 8-element vector accesses when the row length
-// and the base addresses allow, element-wise accesses otherwise.
+// A row is owned by a group of W threads: W = 32 for rows of up to 2048 elements (8 rows per
+// 256-thread block, warp shuffles only), W = 256 up to 8192 elements and W = 1024 beyond (one row
+// per block; long rows need the threads to keep enough loads in flight). Rows longer than the
+// shared-memory cache (49152 elements) are re-read from global memory instead.
+// float32 arithmetic; exponentials are ex2.approx-based (__expf: with the accurate expf the kernels
+// were bound by instruction issue at a third of the HBM rate) and the softmax path evaluates one
+// per element (the cache then holds exp(x - max)); f32 or bf16 storage; 8-element vector accesses
+// when the row length and the base addresses allow, element-wise accesses otherwise.
 #include "common.cuh"
 #include "kernels.cuh"
 
@@ -19,7 +22,7 @@ namespace ember {
 
 namespace {
 
-constexpr int BLOCK = 256;
+constexpr int BLOCK = 256;                // block size of the element-wise kernels
 constexpr int WARP_ROW_MAX_COLS = 2048;   // rows up to this length are owned by one warp
 constexpr int CACHE_COLS = 49152;         // floats of shared memory for one long row (192 KB)
 
@@ -61,7 +64,7 @@ __device__ __forceinline__ void store8(__nv_bfloat16 *p, const float (&v)[8])
     *reinterpret_cast<uint4 *>(p) = u;
 }
 
-// Reduction over the W threads that own a row. red: 8 floats of shared memory per block (W == 256).
+// Reduction over the W threads that own a row. red: 32 floats of shared memory per block (W > 32).
 template <int W, bool IS_MAX>
 __device__ __forceinline__ float group_reduce(float v, float *red)
 {
@@ -77,7 +80,7 @@ __device__ __forceinline__ float group_reduce(float v, float *red)
     __syncthreads();
     float r = red[0];
 #pragma unroll
-    for (int i = 1; i < BLOCK / 32; i++) r = IS_MAX ? fmaxf(r, red[i]) : r + red[i];
+    for (int i = 1; i < W / 32; i++) r = IS_MAX ? fmaxf(r, red[i]) : r + red[i];
     return r;
 }
 
@@ -85,15 +88,15 @@ enum { MODE_SOFTMAX = 0, MODE_LOG_SOFTMAX = 1, MODE_CROSS_ENTROPY = 2 };
 
 // x, y (and target): rows x cols. cache_cols: floats of shared memory per row (0 = none: re-read x).
 template <typename T, int W, int MODE, bool VEC>
-__global__ void __launch_bounds__(BLOCK) row_softmax_kernel(const T *__restrict__ x, const T *__restrict__ target,
+__global__ void __launch_bounds__(W < 256 ? 256 : W) row_softmax_kernel(const T *__restrict__ x, const T *__restrict__ target,
                                                             T *__restrict__ y, float *__restrict__ row_loss,
                                                             long long rows, int cols, int cache_cols)
 {
     extern __shared__ float smem[];
-    float *red = smem;  // 8 floats
-    constexpr int GROUPS = BLOCK / W;
+    float *red = smem;  // 32 floats
+    constexpr int BS = W < 256 ? 256 : W, GROUPS = BS / W;
     const int group = threadIdx.x / W, t = threadIdx.x % W;
-    float *buf = smem + 8 + (size_t)group * cache_cols;
+    float *buf = smem + 32 + (size_t)group * cache_cols;
     const bool cached = cache_cols >= cols;
     constexpr int STEP = VEC ? 8 : 1;
     // Vector path: element i of a thread's 8-element vector lies at buf[i * nvec + vector index], so
@@ -138,9 +141,15 @@ __global__ void __launch_bounds__(BLOCK) row_softmax_kernel(const T *__restrict_
                         load8(xr + j, v);
                     }
 #pragma unroll
-                    for (int i = 0; i < 8; i++) s += expf(v[i] - m);
+                    for (int i = 0; i < 8; i++) {
+                        const float e = __expf(v[i] - m);
+                        s += e;
+                        if (MODE == MODE_SOFTMAX && cached) buf[i * nvec + (j >> 3)] = e;  // pass 3 only scales it
+                    }
                 } else {
-                    s += expf((cached ? buf[j] : ldf(xr + j)) - m);
+                    const float e = __expf((cached ? buf[j] : ldf(xr + j)) - m);
+                    s += e;
+                    if (MODE == MODE_SOFTMAX && cached) buf[j] = e;
                 }
             }
         }
@@ -164,10 +173,10 @@ __global__ void __launch_bounds__(BLOCK) row_softmax_kernel(const T *__restrict_
 #pragma unroll
                     for (int i = 0; i < 8; i++) {
                         if (MODE == MODE_SOFTMAX) {
-                            o[i] = expf(v[i] - m) * inv;
+                            o[i] = (cached ? v[i] : __expf(v[i] - m)) * inv;
                         } else {
                             const float lp = (v[i] - m) - lg;
-                            o[i] = MODE == MODE_LOG_SOFTMAX ? lp : expf(lp);
+                            o[i] = MODE == MODE_LOG_SOFTMAX ? lp : __expf(lp);
                             if (MODE == MODE_CROSS_ENTROPY) loss = fmaf(tv[i], lp, loss);
                         }
                     }
@@ -176,10 +185,10 @@ __global__ void __launch_bounds__(BLOCK) row_softmax_kernel(const T *__restrict_
                     const float v = cached ? buf[j] : ldf(xr + j);
                     float o;
                     if (MODE == MODE_SOFTMAX) {
-                        o = expf(v - m) * inv;
+                        o = (cached ? v : __expf(v - m)) * inv;
                     } else {
                         const float lp = (v - m) - lg;
-                        o = MODE == MODE_LOG_SOFTMAX ? lp : expf(lp);
+                        o = MODE == MODE_LOG_SOFTMAX ? lp : __expf(lp);
                         if (MODE == MODE_CROSS_ENTROPY) loss = fmaf(ldf(tr + j), lp, loss);
                     }
                     stf(yr + j, o);
@@ -190,7 +199,7 @@ __global__ void __launch_bounds__(BLOCK) row_softmax_kernel(const T *__restrict_
             loss = group_reduce<W, false>(loss, red);
             if (active && t == 0) row_loss[row] = loss;
         }
-        if (W == 256) __syncthreads();  // the cache is rewritten by the next row
+        if (W > 32) __syncthreads();  // the cache is rewritten by the next row
     }
 }
 
@@ -236,9 +245,10 @@ int launch_rows(const T *x, const T *target, T *y, float *row_loss, long long ro
 {
     const bool vec = cols % 8 == 0 && aligned16(x) && aligned16(y) && (MODE != MODE_CROSS_ENTROPY || aligned16(target));
     const bool warp_rows = cols <= WARP_ROW_MAX_COLS;
-    const int groups = warp_rows ? BLOCK / 32 : 1;
+    const int width = warp_rows ? 32 : (cols <= 8192 ? 256 : 1024);
+    const int block = width < 256 ? 256 : width, groups = block / width;
     const int cache_cols = warp_rows ? cols : (cols <= CACHE_COLS ? cols : 0);
-    const size_t smem = (8 + (size_t)groups * cache_cols) * sizeof(float);
+    const size_t smem = (32 + (size_t)groups * cache_cols) * sizeof(float);
     const long long blocks_needed = (rows + groups - 1) / groups;
     const long long cap = (long long)(sm_count > 0 ? sm_count : 148) * 16;
     const int grid = (int)(blocks_needed < cap ? blocks_needed : cap);
@@ -246,12 +256,14 @@ int launch_rows(const T *x, const T *target, T *y, float *row_loss, long long ro
     do {                                                                                                        \
         auto kern = row_softmax_kernel<T, W, MODE, VEC>;                                                        \
         EMBER_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));     \
-        kern<<<grid, BLOCK, smem, s>>>(x, target, y, row_loss, rows, cols, cache_cols);                         \
+        kern<<<grid, block, smem, s>>>(x, target, y, row_loss, rows, cols, cache_cols);                         \
     } while (0)
-    if (warp_rows) {
+    if (width == 32) {
         if (vec) EMBER_LAUNCH_ROWS(32, true); else EMBER_LAUNCH_ROWS(32, false);
-    } else {
+    } else if (width == 256) {
         if (vec) EMBER_LAUNCH_ROWS(256, true); else EMBER_LAUNCH_ROWS(256, false);
+    } else {
+        if (vec) EMBER_LAUNCH_ROWS(1024, true); else EMBER_LAUNCH_ROWS(1024, false);
     }
 #undef EMBER_LAUNCH_ROWS
     EMBER_CUDA_TRY(cudaGetLastError());

@@ -34,7 +34,8 @@ def _round(a, bf16):
     return torch.from_numpy(a).to(torch.bfloat16).float().numpy() if bf16 else a
 
 
-SHAPES = [(1, 1), (5, 7), (33, 130), (64, 128), (300, 1000), (17, 2048), (9, 2056), (6, 5000), (3, 50000), (2, 70001)]
+SHAPES = [(1, 1), (5, 7), (33, 130), (64, 128), (300, 1000), (17, 2048), (9, 2056), (6, 5000), (4, 16384), (3, 40001),
+          (3, 50000), (2, 70001)]
 
 
 @pytest.mark.parametrize("bf16", [False, True])
@@ -65,7 +66,7 @@ def test_softmax_and_log_softmax(env, shape, bf16):
 
 
 @pytest.mark.parametrize("bf16", [False, True])
-@pytest.mark.parametrize("shape", [(4, 7), (33, 130), (256, 1000), (64, 4096), (5, 50000)])
+@pytest.mark.parametrize("shape", [(4, 7), (33, 130), (256, 1000), (64, 4096), (7, 32768), (5, 50000)])
 def test_cross_entropy(env, shape, bf16):
     L, dev, sp = env
     rows, cols = shape
