@@ -47,6 +47,10 @@ SIGNATURES = {
     "ember_linear_fwd": (_i, [_vp] * 4 + [ctypes.c_longlong] + [_i] * 7 + [_vp]),
     "ember_linear_bwd": (_i, [_vp] * 6 + [ctypes.c_longlong] + [_i] * 7 + [_vp]),
     "ember_linear_kernel_name": (ctypes.c_char_p, [_i, ctypes.c_longlong] + [_i] * 7),
+    "ember_kv_cache_append": (_i, [_vp] * 4 + [_i] * 6 + [_vp, _vp, _i, _i, _i, _vp]),
+    "ember_attention_decode_cache": (_i, [_vp] * 5 + [_i] * 6 + [ctypes.c_float, _i, _vp, _vp, _i, _i, _i, _vp, _sz, _vp]),
+    "ember_attention_decode_cache_workspace_bytes": (_sz, [_i] * 6),
+    "ember_attention_decode_cache_splits": (_i, [_i] * 3),
     "ember_softmax_fwd": (_i, [_vp, _vp, ctypes.c_longlong, _i, _i, _i, _vp]),
     "ember_cross_entropy_workspace_bytes": (_sz, [ctypes.c_longlong]),
     "ember_cross_entropy_fwd": (_i, [_vp] * 4 + [ctypes.c_longlong, _i, _i, _vp, _sz, _vp]),

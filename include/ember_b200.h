@@ -210,6 +210,41 @@ EMBER_API int ember_cross_entropy_fwd(const void *pred, const void *target, void
 EMBER_API int ember_cross_entropy_bwd(const void *probs, const void *target, void *grad, long long rows, int cols,
                                       int dtype, void *stream);
 
+/* ---- Key/value cache for decode ---------------------------------------------
+ *
+ * The reference has no cache concept: a decode step would re-run the composed attention over
+ * freshly built (B, H, Lk, D) tensors, whose element count is a C int (src/core/tensor_types.h:8).
+ * These entry points keep K and V in a preallocated cache, append new rows in place and decode
+ * over the filled part, with grouped-query heads and an optional page table.
+ *
+ * Contiguous cache: K and V are (batch, kv_heads, capacity, d). Paged cache (block_table != NULL):
+ * K and V are (num_pages, kv_heads, page_size, d), page_size a power of two, and key j of sequence
+ * b lives in page block_table[b * max_blocks + j / page_size], row j % page_size; `capacity` is
+ * ignored. seq_lens (device int32[batch], or NULL) gives each sequence's filled length.
+ *
+ * ember_kv_cache_append: k_new, v_new are (batch, kv_heads, n_new, d); they are written at rows
+ * [p, p + n_new) with p = seq_lens[b], or `pos` when seq_lens is NULL. Rows that do not fit are
+ * skipped and reported through ember_check_device_status (EMBER_ERR_INVALID). The caller advances
+ * its lengths.
+ *
+ * ember_attention_decode_cache: q and out are (batch, q_heads, d), q_heads a multiple (1, 2, 4 or 8)
+ * of kv_heads; query head h reads K/V head h / (q_heads / kv_heads), and the K/V rows of a group
+ * are loaded once for all its query heads. Sequence b attends to its first seq_lens[b] keys (each
+ * >= 1), or to `lk` keys when seq_lens is NULL; with seq_lens, `lk` is an upper bound of the lengths
+ * (it sizes the split of the key axis). lse (batch, q_heads) may be NULL. Workspace as for
+ * ember_attention_decode, sized by ember_attention_decode_cache_workspace_bytes. */
+EMBER_API int ember_kv_cache_append(void *k_cache, void *v_cache, const void *k_new, const void *v_new, int batch,
+                                    int kv_heads, int capacity, int d, int n_new, int pos, const int *seq_lens,
+                                    const int *block_table, int page_size, int max_blocks, int dtype, void *stream);
+EMBER_API int ember_attention_decode_cache(const void *q, const void *k_cache, const void *v_cache, void *out, float *lse,
+                                           int batch, int q_heads, int kv_heads, int lk, int capacity, int d, float scale,
+                                           int dtype, const int *seq_lens, const int *block_table, int page_size,
+                                           int max_blocks, int num_splits, void *workspace, size_t workspace_bytes,
+                                           void *stream);
+EMBER_API size_t ember_attention_decode_cache_workspace_bytes(int batch, int q_heads, int kv_heads, int lk, int d,
+                                                              int num_splits);
+EMBER_API int ember_attention_decode_cache_splits(int batch, int kv_heads, int lk);
+
 #ifdef __cplusplus
 }
 #endif
