@@ -522,7 +522,27 @@ def run_extras(L, _lib, torch, dev, sptr, stream, peaks):
                                     "unit": "GB/s", "frac": nbytes / ms_d / 1e6 / peaks["hbm_gbs"],
                                     "frac_of_nominal_8000": nbytes / ms_d / 1e6 / NOMINAL_HBM_GBS,
                                     "peak_source": peaks["source"] + " copy"}}
-    del kc, vc, ws
+    # ---- the same decode step with grouped-query heads over a cache with spare capacity: 32 query
+    # heads share 8 K/V heads, so the step streams a quarter of the cache bytes (the K/V of the first
+    # 8 heads of the tensors above, read as a (B, 8, 4*Lk, D) cache filled to Lk rows)
+    Hkv, cap = 8, 4 * Lk
+    qg = qd.view(B, H, D)
+    og = torch.empty_like(qg)
+    wsn_g = L.ember_attention_decode_cache_workspace_bytes(B, H, Hkv, Lk, D, 0)
+    ws_g = torch.empty(max(wsn_g, 256), device=dev, dtype=torch.uint8)
+
+    def dec_gqa():
+        _lib.check(L.ember_attention_decode_cache(qg.data_ptr(), kc.data_ptr(), vc.data_ptr(), og.data_ptr(), ld.data_ptr(), B, H,
+                                                  Hkv, Lk, cap, D, scale, 1, None, None, 0, 0, 0, ws_g.data_ptr(), wsn_g, sptr))
+
+    ms_g = timed(dec_gqa, 10)
+    nbytes_g = 2.0 * B * Hkv * Lk * D * 2
+    extra["decode_gqa"] = {"workload": f"decode_gqa_bf16_B{B}_Hq{H}_Hkv{Hkv}_Lk{Lk}_D{D}", "ms": ms_g, "gbs": nbytes_g / ms_g / 1e6,
+                           "speedup_vs_per_head_cache": ms_d / ms_g,
+                           "roofline": {"bound": "hbm", "achieved": nbytes_g / ms_g / 1e6, "peak": peaks["hbm_gbs"],
+                                        "unit": "GB/s", "frac": nbytes_g / ms_g / 1e6 / peaks["hbm_gbs"],
+                                        "peak_source": peaks["source"] + " copy"}}
+    del kc, vc, ws, ws_g
 
     # ---- the projections either side of attention at the headline shape (E = H * D = 4096):
     # fused q/k/v projection writing (3, B, H, L, D), output projection reading (B, H, L, D)

@@ -10,7 +10,7 @@ without the built CUDA library raises ImportError with the build command.
 import importlib
 
 __all__ = ["Tensor", "attention", "attention_forward", "attention_backward", "attention_decode", "linear_forward",
-           "linear_backward", "softmax", "log_softmax", "nn", "loss"]
+           "linear_backward", "softmax", "log_softmax", "KVCache", "nn", "loss"]
 
 _TENSOR_NAMES = {"Tensor", "attention", "attention_forward", "attention_backward", "attention_decode", "linear_forward",
                  "linear_backward", "softmax", "log_softmax"}
@@ -25,6 +25,8 @@ def __getattr__(name):
                 f"ember_b200 native libraries are not built ({e}); run `python -m ember_b200.build` "
                 "(needs nvcc and gcc; there is no CPU fallback for the attention path)") from e
         return getattr(mod, name)
-    if name in ("nn", "loss", "tensor", "shard", "_lib", "_core", "build"):
+    if name == "KVCache":
+        return importlib.import_module(".cache", __name__).KVCache
+    if name in ("nn", "loss", "cache", "tensor", "shard", "_lib", "_core", "build"):
         return importlib.import_module("." + name, __name__)
     raise AttributeError(f"module {__name__!r} has no attribute {name!r}")

@@ -7,14 +7,15 @@
 // result is written once: 2 (softmax) or 3 (cross-entropy: logits and targets in, probabilities
 // out) element transfers per element instead of about 12 and 20.
 //
-// A row is owned by a group of W threads: W = 32 for rows of up to 2048 elements (8 rows per
-// 256-thread block, warp shuffles only), W = 256 up to 8192 elements and W = 1024 beyond (one row
-// per block; long rows need the threads to keep enough loads in flight). Rows longer than the
-// shared-memory cache (49152 elements) are re-read from global memory instead.
-// float32 arithmetic; exponentials are ex2.approx-based (__expf: with the accurate expf the kernels
-// were bound by instruction issue at a third of the HBM rate) and the softmax path evaluates one
-// per element (the cache then holds exp(x - max)); f32 or bf16 storage; 8-element vector accesses
-// when the row length and the base addresses allow, element-wise accesses otherwise.
+// A row is owned by a group of W threads: W = 32 while a row is at most 8 KB (8 rows per
+// 256-thread block, warp shuffles only, no block-wide barrier), W = 256 up to 32 KB and W = 1024
+// beyond (one row per block; long rows need the threads to keep enough loads in flight). The cache
+// holds the row in its storage type (a bf16 row needs half the shared memory of its float32 image,
+// which decides how many blocks fit on an SM); rows longer than 192 KB are re-read from global memory.
+// float32 arithmetic; exponentials are ex2.approx-based (__expf: with the accurate expf, twice per
+// element, the kernels were bound by instruction issue at a third of the HBM rate). f32 or bf16
+// storage; 16-byte vector accesses when the row length and the base addresses allow, element-wise
+// accesses otherwise.
 #include "common.cuh"
 #include "kernels.cuh"
 
@@ -23,46 +24,53 @@ namespace ember {
 namespace {
 
 constexpr int BLOCK = 256;                // block size of the element-wise kernels
-constexpr int WARP_ROW_MAX_COLS = 2048;   // rows up to this length are owned by one warp
-constexpr int CACHE_COLS = 49152;         // floats of shared memory for one long row (192 KB)
+constexpr int WARP_ROW_MAX_BYTES = 8192;  // rows up to this size are owned by one warp
+constexpr int BLOCK_ROW_MAX_BYTES = 32768;  // ... by 256 threads; longer rows by 1024
+constexpr int CACHE_BYTES = 196608;       // shared memory for one long row
 
 __device__ __forceinline__ float ldf(const float *p) { return *p; }
 __device__ __forceinline__ float ldf(const __nv_bfloat16 *p) { return __bfloat162float(*p); }
 __device__ __forceinline__ void stf(float *p, float v) { *p = v; }
 __device__ __forceinline__ void stf(__nv_bfloat16 *p, float v) { *p = __float2bfloat16_rn(v); }
 
-__device__ __forceinline__ void load8(const float *p, float (&v)[8])
-{
-    const float4 a = *reinterpret_cast<const float4 *>(p), b = *reinterpret_cast<const float4 *>(p + 4);
-    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-}
-__device__ __forceinline__ void load8(const __nv_bfloat16 *p, float (&v)[8])
-{
-    const uint4 u = *reinterpret_cast<const uint4 *>(p);
-    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-        v[2 * i] = __uint_as_float(w[i] << 16);
-        v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+// 16 bytes of T <-> NV floats
+template <typename T>
+struct Vec16;
+template <>
+struct Vec16<float> {
+    static constexpr int NV = 4;
+    static __device__ __forceinline__ void unpack(const uint4 &u, float (&v)[4])
+    {
+        v[0] = __uint_as_float(u.x); v[1] = __uint_as_float(u.y); v[2] = __uint_as_float(u.z); v[3] = __uint_as_float(u.w);
     }
-}
-__device__ __forceinline__ void store8(float *p, const float (&v)[8])
-{
-    *reinterpret_cast<float4 *>(p) = make_float4(v[0], v[1], v[2], v[3]);
-    *reinterpret_cast<float4 *>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
-}
-__device__ __forceinline__ void store8(__nv_bfloat16 *p, const float (&v)[8])
-{
-    uint4 u;
-    uint32_t w[4];
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-        const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
-        w[i] = *reinterpret_cast<const uint32_t *>(&h);
+    static __device__ __forceinline__ uint4 pack(const float (&v)[4])
+    {
+        return make_uint4(__float_as_uint(v[0]), __float_as_uint(v[1]), __float_as_uint(v[2]), __float_as_uint(v[3]));
     }
-    u.x = w[0]; u.y = w[1]; u.z = w[2]; u.w = w[3];
-    *reinterpret_cast<uint4 *>(p) = u;
-}
+};
+template <>
+struct Vec16<__nv_bfloat16> {
+    static constexpr int NV = 8;
+    static __device__ __forceinline__ void unpack(const uint4 &u, float (&v)[8])
+    {
+        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            v[2 * i] = __uint_as_float(w[i] << 16);
+            v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        }
+    }
+    static __device__ __forceinline__ uint4 pack(const float (&v)[8])
+    {
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+            w[i] = *reinterpret_cast<const uint32_t *>(&h);
+        }
+        return make_uint4(w[0], w[1], w[2], w[3]);
+    }
+};
 
 // Reduction over the W threads that own a row. red: 32 floats of shared memory per block (W > 32).
 template <int W, bool IS_MAX>
@@ -86,44 +94,43 @@ __device__ __forceinline__ float group_reduce(float v, float *red)
 
 enum { MODE_SOFTMAX = 0, MODE_LOG_SOFTMAX = 1, MODE_CROSS_ENTROPY = 2 };
 
-// x, y (and target): rows x cols. cache_cols: floats of shared memory per row (0 = none: re-read x).
+// x, y (and target): rows x cols. cache_elems: elements of T cached per row (0 = none: re-read x).
 template <typename T, int W, int MODE, bool VEC>
 __global__ void __launch_bounds__(W < 256 ? 256 : W) row_softmax_kernel(const T *__restrict__ x, const T *__restrict__ target,
-                                                            T *__restrict__ y, float *__restrict__ row_loss,
-                                                            long long rows, int cols, int cache_cols)
+                                                                         T *__restrict__ y, float *__restrict__ row_loss,
+                                                                         long long rows, int cols, int cache_elems)
 {
-    extern __shared__ float smem[];
-    float *red = smem;  // 32 floats
-    constexpr int BS = W < 256 ? 256 : W, GROUPS = BS / W;
+    extern __shared__ __align__(16) unsigned char smem_bytes[];
+    float *red = reinterpret_cast<float *>(smem_bytes);  // 32 floats
+    constexpr int BS = W < 256 ? 256 : W, GROUPS = BS / W, NV = Vec16<T>::NV;
     const int group = threadIdx.x / W, t = threadIdx.x % W;
-    float *buf = smem + 32 + (size_t)group * cache_cols;
-    const bool cached = cache_cols >= cols;
-    constexpr int STEP = VEC ? 8 : 1;
-    // Vector path: element i of a thread's 8-element vector lies at buf[i * nvec + vector index], so
-    // that the threads of a warp touch consecutive words (each thread only ever reads back its own).
-    const int nvec = cols >> 3;
+    T *buf = reinterpret_cast<T *>(smem_bytes + 128) + (size_t)group * cache_elems;
+    uint4 *bufv = reinterpret_cast<uint4 *>(buf);
+    const bool cached = cache_elems >= cols;
+    const int nvec = cols / NV;  // VEC: cols is a multiple of NV
 
     for (long long row0 = (long long)blockIdx.x * GROUPS; row0 < rows; row0 += (long long)gridDim.x * GROUPS) {
         const long long row = row0 + group;
-        const bool active = row < rows;  // W == 256: always true; W == 32: the whole warp agrees
+        const bool active = row < rows;  // W > 32: always true; W == 32: the whole warp agrees
         const T *xr = x + (size_t)(active ? row : 0) * cols;
+        const uint4 *xv = reinterpret_cast<const uint4 *>(xr);
         // ---- pass 1: maximum (and fill the cache)
         float m = -INFINITY;
         if (active) {
-            for (int j = t * STEP; j < cols; j += W * STEP) {
-                if constexpr (VEC) {
-                    float v[8];
-                    load8(xr + j, v);
+            if constexpr (VEC) {
+                for (int j = t; j < nvec; j += W) {
+                    const uint4 u = xv[j];
+                    if (cached) bufv[j] = u;
+                    float v[NV];
+                    Vec16<T>::unpack(u, v);
 #pragma unroll
-                    for (int i = 0; i < 8; i++) m = fmaxf(m, v[i]);
-                    if (cached) {
-#pragma unroll
-                        for (int i = 0; i < 8; i++) buf[i * nvec + (j >> 3)] = v[i];
-                    }
-                } else {
-                    const float v = ldf(xr + j);
-                    m = fmaxf(m, v);
-                    if (cached) buf[j] = v;
+                    for (int i = 0; i < NV; i++) m = fmaxf(m, v[i]);
+                }
+            } else {
+                for (int j = t; j < cols; j += W) {
+                    const T raw = xr[j];
+                    if (cached) buf[j] = raw;
+                    m = fmaxf(m, ldf(&raw));
                 }
             }
         }
@@ -131,26 +138,15 @@ __global__ void __launch_bounds__(W < 256 ? 256 : W) row_softmax_kernel(const T 
         // ---- pass 2: sum of exp(x - max)
         float s = 0.f;
         if (active) {
-            for (int j = t * STEP; j < cols; j += W * STEP) {
-                if constexpr (VEC) {
-                    float v[8];
-                    if (cached) {
+            if constexpr (VEC) {
+                for (int j = t; j < nvec; j += W) {
+                    float v[NV];
+                    Vec16<T>::unpack(cached ? bufv[j] : xv[j], v);
 #pragma unroll
-                        for (int i = 0; i < 8; i++) v[i] = buf[i * nvec + (j >> 3)];
-                    } else {
-                        load8(xr + j, v);
-                    }
-#pragma unroll
-                    for (int i = 0; i < 8; i++) {
-                        const float e = __expf(v[i] - m);
-                        s += e;
-                        if (MODE == MODE_SOFTMAX && cached) buf[i * nvec + (j >> 3)] = e;  // pass 3 only scales it
-                    }
-                } else {
-                    const float e = __expf((cached ? buf[j] : ldf(xr + j)) - m);
-                    s += e;
-                    if (MODE == MODE_SOFTMAX && cached) buf[j] = e;
+                    for (int i = 0; i < NV; i++) s += __expf(v[i] - m);
                 }
+            } else {
+                for (int j = t; j < cols; j += W) s += __expf(ldf(cached ? buf + j : xr + j) - m);
             }
         }
         s = group_reduce<W, false>(s, red);
@@ -160,32 +156,31 @@ __global__ void __launch_bounds__(W < 256 ? 256 : W) row_softmax_kernel(const T 
         if (active) {
             T *yr = y + (size_t)row * cols;
             const T *tr = MODE == MODE_CROSS_ENTROPY ? target + (size_t)row * cols : nullptr;
-            for (int j = t * STEP; j < cols; j += W * STEP) {
-                if constexpr (VEC) {
-                    float v[8], o[8], tv[8];
-                    if (cached) {
+            if constexpr (VEC) {
+                uint4 *yv = reinterpret_cast<uint4 *>(yr);
+                const uint4 *tv4 = reinterpret_cast<const uint4 *>(tr);
+                for (int j = t; j < nvec; j += W) {
+                    float v[NV], o[NV], tv[NV];
+                    Vec16<T>::unpack(cached ? bufv[j] : xv[j], v);
+                    if (MODE == MODE_CROSS_ENTROPY) Vec16<T>::unpack(tv4[j], tv);
 #pragma unroll
-                        for (int i = 0; i < 8; i++) v[i] = buf[i * nvec + (j >> 3)];
-                    } else {
-                        load8(xr + j, v);
-                    }
-                    if (MODE == MODE_CROSS_ENTROPY) load8(tr + j, tv);
-#pragma unroll
-                    for (int i = 0; i < 8; i++) {
+                    for (int i = 0; i < NV; i++) {
                         if (MODE == MODE_SOFTMAX) {
-                            o[i] = (cached ? v[i] : __expf(v[i] - m)) * inv;
+                            o[i] = __expf(v[i] - m) * inv;
                         } else {
                             const float lp = (v[i] - m) - lg;
                             o[i] = MODE == MODE_LOG_SOFTMAX ? lp : __expf(lp);
                             if (MODE == MODE_CROSS_ENTROPY) loss = fmaf(tv[i], lp, loss);
                         }
                     }
-                    store8(yr + j, o);
-                } else {
-                    const float v = cached ? buf[j] : ldf(xr + j);
+                    yv[j] = Vec16<T>::pack(o);
+                }
+            } else {
+                for (int j = t; j < cols; j += W) {
+                    const float v = ldf(cached ? buf + j : xr + j);
                     float o;
                     if (MODE == MODE_SOFTMAX) {
-                        o = (cached ? v : __expf(v - m)) * inv;
+                        o = __expf(v - m) * inv;
                     } else {
                         const float lp = (v - m) - lg;
                         o = MODE == MODE_LOG_SOFTMAX ? lp : __expf(lp);
@@ -222,18 +217,22 @@ template <typename T, bool VEC>
 __global__ void __launch_bounds__(BLOCK) ce_backward_kernel(const T *__restrict__ probs, const T *__restrict__ target,
                                                             T *__restrict__ grad, size_t total, float inv_n)
 {
-    constexpr int STEP = VEC ? 8 : 1;
-    for (size_t i = ((size_t)blockIdx.x * BLOCK + threadIdx.x) * STEP; i < total; i += (size_t)gridDim.x * BLOCK * STEP) {
-        if constexpr (VEC) {
-            float p[8], t[8], g[8];
-            load8(probs + i, p);
-            load8(target + i, t);
+    constexpr int NV = Vec16<T>::NV;
+    if constexpr (VEC) {
+        const uint4 *pv = reinterpret_cast<const uint4 *>(probs), *tv = reinterpret_cast<const uint4 *>(target);
+        uint4 *gv = reinterpret_cast<uint4 *>(grad);
+        const size_t nvec = total / NV;
+        for (size_t i = (size_t)blockIdx.x * BLOCK + threadIdx.x; i < nvec; i += (size_t)gridDim.x * BLOCK) {
+            float p[NV], t[NV], g[NV];
+            Vec16<T>::unpack(pv[i], p);
+            Vec16<T>::unpack(tv[i], t);
 #pragma unroll
-            for (int k = 0; k < 8; k++) g[k] = (p[k] - t[k]) * inv_n;
-            store8(grad + i, g);
-        } else {
-            stf(grad + i, (ldf(probs + i) - ldf(target + i)) * inv_n);
+            for (int k = 0; k < NV; k++) g[k] = (p[k] - t[k]) * inv_n;
+            gv[i] = Vec16<T>::pack(g);
         }
+    } else {
+        for (size_t i = (size_t)blockIdx.x * BLOCK + threadIdx.x; i < total; i += (size_t)gridDim.x * BLOCK)
+            stf(grad + i, (ldf(probs + i) - ldf(target + i)) * inv_n);
     }
 }
 
@@ -243,12 +242,14 @@ template <typename T, int MODE>
 int launch_rows(const T *x, const T *target, T *y, float *row_loss, long long rows, int cols, int sm_count,
                 cudaStream_t s)
 {
-    const bool vec = cols % 8 == 0 && aligned16(x) && aligned16(y) && (MODE != MODE_CROSS_ENTROPY || aligned16(target));
-    const bool warp_rows = cols <= WARP_ROW_MAX_COLS;
-    const int width = warp_rows ? 32 : (cols <= 8192 ? 256 : 1024);
+    constexpr int NV = Vec16<T>::NV;
+    const bool vec = cols % NV == 0 && aligned16(x) && aligned16(y) && (MODE != MODE_CROSS_ENTROPY || aligned16(target));
+    const size_t row_bytes = (size_t)cols * sizeof(T);
+    const int width = row_bytes <= WARP_ROW_MAX_BYTES ? 32 : (row_bytes <= BLOCK_ROW_MAX_BYTES ? 256 : 1024);
     const int block = width < 256 ? 256 : width, groups = block / width;
-    const int cache_cols = warp_rows ? cols : (cols <= CACHE_COLS ? cols : 0);
-    const size_t smem = (32 + (size_t)groups * cache_cols) * sizeof(float);
+    // per-row cache, rounded up to 16 bytes so that every group's cache stays vector-aligned
+    const int cache_elems = row_bytes <= CACHE_BYTES ? (int)(align_up(row_bytes, 16) / sizeof(T)) : 0;
+    const size_t smem = 128 + (size_t)groups * cache_elems * sizeof(T);
     const long long blocks_needed = (rows + groups - 1) / groups;
     const long long cap = (long long)(sm_count > 0 ? sm_count : 148) * 16;
     const int grid = (int)(blocks_needed < cap ? blocks_needed : cap);
@@ -256,7 +257,7 @@ int launch_rows(const T *x, const T *target, T *y, float *row_loss, long long ro
     do {                                                                                                        \
         auto kern = row_softmax_kernel<T, W, MODE, VEC>;                                                        \
         EMBER_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));     \
-        kern<<<grid, block, smem, s>>>(x, target, y, row_loss, rows, cols, cache_cols);                         \
+        kern<<<grid, block, smem, s>>>(x, target, y, row_loss, rows, cols, cache_elems);                         \
     } while (0)
     if (width == 32) {
         if (vec) EMBER_LAUNCH_ROWS(32, true); else EMBER_LAUNCH_ROWS(32, false);
@@ -347,8 +348,9 @@ int ember_cross_entropy_bwd(const void *probs, const void *target, void *grad, l
     if (!st) return EMBER_ERR_CUDA;
     cudaStream_t s = pick_stream(stream, st);
     const size_t total = (size_t)rows * cols;
-    const bool vec = total % 8 == 0 && aligned16(probs) && aligned16(target) && aligned16(grad);
-    const size_t per_block = (size_t)BLOCK * (vec ? 8 : 1);
+    const size_t nv = dtype == EMBER_BF16 ? 8 : 4;
+    const bool vec = total % nv == 0 && aligned16(probs) && aligned16(target) && aligned16(grad);
+    const size_t per_block = (size_t)BLOCK * (vec ? nv : 1);
     const size_t want = (total + per_block - 1) / per_block;
     const size_t cap = (size_t)(st->sm_count > 0 ? st->sm_count : 148) * 32;
     const int grid = (int)(want < cap ? want : cap);

@@ -537,6 +537,77 @@ static PyObject *_cross_entropy_bwd(PyObject *module, PyObject *args)
     return (PyObject *)g;
 }
 
+/* _kv_append(k_cache, v_cache, k_new, v_new, B, Hkv, capacity, D, n_new, pos) -> None
+ * Writes (B, Hkv, n_new, D) rows into the (B, Hkv, capacity, D) caches at rows [pos, pos + n_new). */
+static PyObject *_kv_append(PyObject *module, PyObject *args)
+{
+    _Tensor *kc, *vc, *kn, *vn;
+    int B, H, cap, d, n_new, pos;
+    if (!PyArg_ParseTuple(args, "O!O!O!O!iiiiii", &_TensorType, &kc, &_TensorType, &vc, &_TensorType, &kn, &_TensorType, &vn,
+                          &B, &H, &cap, &d, &n_new, &pos))
+        return NULL;
+    const long long cache_n = (long long)B * H * cap * d, new_n = (long long)B * H * n_new * d;
+    if (B <= 0 || H <= 0 || cap <= 0 || d <= 0 || n_new <= 0 || kc->size64 != cache_n || vc->size64 != cache_n ||
+        kn->size64 != new_n || vn->size64 != new_n) {
+        PyErr_Format(PyExc_ValueError, "kv_append: size mismatch: caches %lld/%lld (expected %lld), new rows %lld/%lld (expected %lld)",
+                     kc->size64, vc->size64, cache_n, kn->size64, vn->size64, new_n);
+        return NULL;
+    }
+    if (kc->dtype != vc->dtype || kn->dtype != kc->dtype || vn->dtype != kc->dtype) {
+        PyErr_SetString(PyExc_TypeError, "kv_append: caches and new rows must share a dtype");
+        return NULL;
+    }
+    int rc = ember_kv_cache_append(kc->d_ptr, vc->d_ptr, kn->d_ptr, vn->d_ptr, B, H, cap, d, n_new, pos, NULL, NULL, 0, 0,
+                                   kc->dtype, NULL);
+    if (rc) return raise_status(rc);
+    Py_RETURN_NONE;
+}
+
+/* _decode_cache(q, k_cache, v_cache, B, Hq, Hkv, lk, capacity, D, scale, num_splits) -> (out, lse)
+ * One query row per (batch, query head) against the first lk rows of the caches. */
+static PyObject *_decode_cache(PyObject *module, PyObject *args)
+{
+    _Tensor *q, *kc, *vc;
+    int B, Hq, Hkv, lk, cap, d, splits;
+    float scale;
+    if (!PyArg_ParseTuple(args, "O!O!O!iiiiiifi", &_TensorType, &q, &_TensorType, &kc, &_TensorType, &vc, &B, &Hq, &Hkv, &lk,
+                          &cap, &d, &scale, &splits))
+        return NULL;
+    const long long cache_n = (long long)B * Hkv * cap * d;
+    if (B <= 0 || Hq <= 0 || Hkv <= 0 || cap <= 0 || d <= 0 || q->size64 != (long long)B * Hq * d || kc->size64 != cache_n ||
+        vc->size64 != cache_n) {
+        PyErr_Format(PyExc_ValueError, "decode_cache: size mismatch: q %lld (expected %lld), caches %lld/%lld (expected %lld)",
+                     q->size64, (long long)B * Hq * d, kc->size64, vc->size64, cache_n);
+        return NULL;
+    }
+    if (kc->dtype != q->dtype || vc->dtype != q->dtype) {
+        PyErr_SetString(PyExc_TypeError, "decode_cache: q and the caches must share a dtype");
+        return NULL;
+    }
+    _Tensor *out = alloc_result(q->size64, q->dtype), *lse = NULL;
+    void *ws = NULL;
+    const size_t wsn = ember_attention_decode_cache_workspace_bytes(B, Hq, Hkv, lk, d, splits);
+    if (out) lse = alloc_result((long long)B * Hq, EMBER_F32);
+    if (lse) {
+        ws = alloc_memory(wsn ? wsn : 256);
+        if (!ws) PyErr_Format(PyExc_MemoryError, "Failed to allocate device memory: %s", ember_last_error());
+    }
+    if (!ws) {
+        Py_XDECREF(out);
+        Py_XDECREF(lse);
+        return NULL;
+    }
+    int rc = ember_attention_decode_cache(q->d_ptr, kc->d_ptr, vc->d_ptr, out->d_ptr, (float *)lse->d_ptr, B, Hq, Hkv, lk, cap, d,
+                                          scale, q->dtype, NULL, NULL, 0, 0, splits, ws, wsn, NULL);
+    free_memory(ws); /* stream-ordered: released after the kernels that use it */
+    if (rc) {
+        Py_DECREF(out);
+        Py_DECREF(lse);
+        return raise_status(rc);
+    }
+    return Py_BuildValue("(NN)", out, lse);
+}
+
 static PyObject *_sync(PyObject *module, PyObject *noargs)
 {
     sync_device();
@@ -565,6 +636,8 @@ static PyMethodDef module_methods[] = {OP_METHOD(_from_numpy),
                                        OP_METHOD(_softmax),
                                        OP_METHOD(_cross_entropy_fwd),
                                        OP_METHOD(_cross_entropy_bwd),
+                                       OP_METHOD(_kv_append),
+                                       OP_METHOD(_decode_cache),
                                        {"_sync", (PyCFunction)_sync, METH_NOARGS, "Wait for the library stream"},
                                        {NULL, NULL, 0, NULL}};
 

@@ -79,3 +79,28 @@ def test_classifier_head_training_step(em):
     rgx, rgw, rgb = cpu_oracle.linear_bwd(y.to_np().reshape(B * L, E), head.w.to_np(), ref_g)
     assert np.abs(g_y.to_np() - rgx).max() <= 1e-3 * max(np.abs(rgx).max(), 1e-6)
     assert np.abs(head.grad_w.to_np() - rgw).max() <= 1e-3 * np.abs(rgw).max()
+
+
+def test_kv_cache_class_grows_and_decodes(em):
+    """Token-by-token decode over a growing cache equals causal attention over the whole sequence."""
+    B, Hq, Hkv, L, D = 2, 8, 2, 40, 64
+    rng = np.random.default_rng(2)
+    q = rng.standard_normal((B, Hq, L, D), dtype=np.float32) * 0.5
+    k = rng.standard_normal((B, Hkv, L, D), dtype=np.float32) * 0.5
+    v = rng.standard_normal((B, Hkv, L, D), dtype=np.float32) * 0.5
+    cache = em.KVCache(B, Hkv, 64, D, dtype="float32")
+    cache.append(em.Tensor(k[:, :, :25]), em.Tensor(v[:, :, :25]))  # prefill
+    outs = []
+    for t in range(25, L):
+        cache.append(em.Tensor(k[:, :, t:t + 1]), em.Tensor(v[:, :, t:t + 1]))
+        o, lse = cache.decode(em.Tensor(np.ascontiguousarray(q[:, :, t])))
+        assert o.shape == (B, Hq, D) and lse.shape == (B, Hq)
+        outs.append(o.to_np())
+    kr, vr = np.repeat(k, Hq // Hkv, axis=1), np.repeat(v, Hq // Hkv, axis=1)
+    ref, _ = cpu_oracle.attention_fwd(q, kr, vr, None, True)
+    got = np.stack(outs, axis=2)
+    assert np.abs(got - ref[:, :, 25:]).max() <= 1e-3
+    with pytest.raises(ValueError):
+        cache.append(em.Tensor(k[:, :, :30]), em.Tensor(v[:, :, :30]))
+    with pytest.raises(ValueError):
+        cache.decode(em.Tensor(np.zeros((B, 3, D), np.float32)))
