@@ -80,6 +80,12 @@ struct FwdParams {
     float scale_log2;  // scale * log2(e)
     DeviceStatus *status;
     WorkOrder order;
+    // Split-key use (decode over a key/value cache with a few query rows per unit): a work unit is
+    // (sequence unit, split); the split covers keys [split * chunk, split * chunk + chunk) of the
+    // unit's first seq_lens[unit / lens_div] (or lk) keys and writes a normalised partial output
+    // plus its log-sum-exp, which a second kernel merges. splits == 1 is the plain forward.
+    int splits, chunk, lens_div;
+    const int *seq_lens;
 };
 
 // EMU: of every 4 pairs of exponentials, how many are evaluated as a polynomial on the FMA pipe
@@ -106,7 +112,19 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
     work_item(p.order, blockIdx.x, bh, rank);
     const int qblock = p.order.blocks - 1 - rank;  // heaviest (latest) causal rows first
     const int q_base = qblock * 256;
-    const int off = p.lk - p.lq;
+    // which tensor slab the unit reads, where its keys start and how many it sees
+    const int unit = p.splits > 1 ? bh / p.splits : bh;
+    const int k_row0 = p.splits > 1 ? (bh - unit * p.splits) * p.chunk : 0;
+    int lk = p.seq_lens ? min(p.lk, p.seq_lens[unit / p.lens_div]) : p.lk;
+    lk = p.splits > 1 ? min(p.chunk, lk - k_row0) : lk;
+    if (lk <= 0) {
+        // An empty split (a sequence shorter than the others): its partial is "no weight". Every
+        // thread leaves here, before any barrier or tensor-memory allocation exists.
+        if (p.lse && threadIdx.x < 256 && q_base + (int)threadIdx.x < p.lq)
+            p.lse[(size_t)bh * p.lq + q_base + threadIdx.x] = -INFINITY;
+        return;
+    }
+    const int off = lk - p.lq;
 
     // number of key tiles each query tile visits
     int n_t[2];
@@ -116,7 +134,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
         if (qs >= p.lq) {
             n_t[t] = 0;
         } else {
-            const int visible = p.causal ? min(p.lk, qs + 128 + off) : p.lk;
+            const int visible = p.causal ? min(lk, qs + 128 + off) : lk;
             n_t[t] = (visible + 127) / 128;
         }
     }
@@ -165,7 +183,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
             for (int t = 0; t < ntiles_q; t++)
                 for (int s = 0; s < C::NSUB; s++)
                     tma_load_3d(smem_base + C::OFF_Q + t * C::TILE_BYTES + s * C::SUB_BYTES, &tm_q,
-                                BAR(B_Q), s * 64, q_base + t * 128, bh);
+                                BAR(B_Q), s * 64, q_base + t * 128, p.splits > 1 ? unit : bh);
             int k_issued = 0, v_issued = 0;
             for (int j = 0; j < n; j++) {
                 const int ks = j % C::KSTAGES, vs = j % C::VSTAGES;
@@ -173,13 +191,13 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
                 mbar_arrive_expect_tx(BAR(B_KFULL + ks), C::TILE_BYTES);
                 for (int s = 0; s < C::NSUB; s++)
                     tma_load_3d(smem_base + C::OFF_K + ks * C::TILE_BYTES + s * C::SUB_BYTES, &tm_k,
-                                BAR(B_KFULL + ks), s * 64, j * 128, bh);
+                                BAR(B_KFULL + ks), s * 64, k_row0 + j * 128, unit);
                 k_issued = j + 1;
                 if (!mbar_wait(BAR(B_VEMPTY + vs), ((j / C::VSTAGES) & 1) ^ 1, abort_flag, p.status, W_TMA_VEMPTY)) break;
                 mbar_arrive_expect_tx(BAR(B_VFULL + vs), C::TILE_BYTES);
                 for (int s = 0; s < C::NSUB; s++)
                     tma_load_3d(smem_base + C::OFF_V + vs * C::TILE_BYTES + s * C::SUB_BYTES, &tm_v,
-                                BAR(B_VFULL + vs), s * 64, j * 128, bh);
+                                BAR(B_VFULL + vs), s * 64, k_row0 + j * 128, unit);
                 v_issued = j + 1;
             }
             // Do not leave the CTA while one of its own copies is still landing in shared memory:
@@ -273,8 +291,8 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
         const uint32_t to = tmem + lane_sel + C::TMEM_O + t * HD;
         const int nk = n_t[t];
         const float c = p.scale_log2;
-        const int limit_row = p.causal ? min(p.lk - 1, row + off) : p.lk - 1;
-        const int limit_tile = p.causal ? min(p.lk - 1, q_base + t * 128 + off) : p.lk - 1;
+        const int limit_row = p.causal ? min(lk - 1, row + off) : lk - 1;
+        const int limit_tile = p.causal ? min(lk - 1, q_base + t * 128 + off) : lk - 1;
 
         float m_ref = -INFINITY, l = 0.f;
         bool ok = true;
@@ -462,6 +480,10 @@ int launch(const AttnArgs &a, DeviceState *st, cudaStream_t s)
     p.causal = a.causal;
     p.scale_log2 = a.scale * LOG2E_F;
     p.status = st->status;
+    p.splits = 1;
+    p.chunk = a.lk;
+    p.lens_div = 1;
+    p.seq_lens = nullptr;
     auto kern = sm100_fwd_kernel<HD, EMU>;
     EMBER_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
     p.order = make_work_order(a.bh, (a.lq + 255) / 256, st->sm_count, ((size_t)a.lq + a.lk) * HD * 2 * 2,  // Q, O, K, V
@@ -469,6 +491,70 @@ int launch(const AttnArgs &a, DeviceState *st, cudaStream_t s)
     dim3 grid((unsigned)(p.order.units * p.order.blocks));
     kern<<<grid, FWD_THREADS, C::SMEM_BYTES, s>>>(tq, tk, tv, p);
     EMBER_CUDA_TRY(cudaGetLastError());
+    return EMBER_OK;
+}
+
+// Merges the normalised partial outputs of the splits of one (unit, query row):
+// out = sum_s w_s O_s / sum_s w_s with w_s = exp(lse_s - max lse). One block per (unit, row).
+__global__ void split_merge_kernel(const __nv_bfloat16 *__restrict__ o_part, const float *__restrict__ lse_part,
+                                   __nv_bfloat16 *__restrict__ out, float *__restrict__ lse, int rows_per_unit, int splits,
+                                   int d)
+{
+    const size_t unit = blockIdx.x / rows_per_unit;
+    const int row = blockIdx.x - (int)unit * rows_per_unit;
+    float mx = -INFINITY;
+    for (int s = 0; s < splits; s++) mx = fmaxf(mx, lse_part[(unit * splits + s) * rows_per_unit + row]);
+    float wsum = 0.f;
+    for (int s = 0; s < splits; s++) {
+        const float ls = lse_part[(unit * splits + s) * rows_per_unit + row];
+        if (ls != -INFINITY) wsum += expf(ls - mx);
+    }
+    for (int c = threadIdx.x; c < d; c += blockDim.x) {
+        float acc = 0.f;
+        for (int s = 0; s < splits; s++) {
+            const float ls = lse_part[(unit * splits + s) * rows_per_unit + row];
+            if (ls != -INFINITY)
+                acc += expf(ls - mx) * __bfloat162float(o_part[((unit * splits + s) * rows_per_unit + row) * (size_t)d + c]);
+        }
+        out[((size_t)unit * rows_per_unit + row) * d + c] = __float2bfloat16_rn(acc / wsum);
+    }
+    if (lse && threadIdx.x == 0) lse[unit * rows_per_unit + row] = mx + logf(wsum);
+}
+
+template <int HD>
+int launch_cache_decode(const CacheDecodeArgs &a, DeviceState *st, cudaStream_t s)
+{
+    using C = FwdCfg<HD>;
+    const int units = a.batch * a.kv_heads, rows = a.q_heads / a.kv_heads;
+    CUtensorMap tq, tk, tv;
+    int rc;
+    if ((rc = make_tensor_map_bf16_3d(&tq, a.q, HD, rows, units, 64, 128)) != EMBER_OK) return rc;
+    if ((rc = make_tensor_map_bf16_3d(&tk, a.k_cache, HD, a.lk, units, 64, 128, a.capacity)) != EMBER_OK) return rc;
+    if ((rc = make_tensor_map_bf16_3d(&tv, a.v_cache, HD, a.lk, units, 64, 128, a.capacity)) != EMBER_OK) return rc;
+    FwdParams p;
+    const bool split = a.splits > 1;
+    __nv_bfloat16 *o_part = (__nv_bfloat16 *)a.workspace;
+    float *lse_part = (float *)((char *)a.workspace + align_up((size_t)units * a.splits * rows * HD * 2, 256));
+    p.out = split ? o_part : (__nv_bfloat16 *)a.out;
+    p.lse = split ? lse_part : a.lse;
+    p.lq = rows;
+    p.lk = a.lk;
+    p.causal = 0;
+    p.scale_log2 = a.scale * LOG2E_F;
+    p.status = st->status;
+    p.splits = a.splits;
+    p.chunk = a.chunk;
+    p.lens_div = a.kv_heads;
+    p.seq_lens = a.seq_lens;
+    p.order = make_work_order(units * a.splits, 1, st->sm_count, 1, false);
+    auto kern = sm100_fwd_kernel<HD, 1>;
+    EMBER_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+    kern<<<(unsigned)(units * a.splits), FWD_THREADS, C::SMEM_BYTES, s>>>(tq, tk, tv, p);
+    EMBER_CUDA_TRY(cudaGetLastError());
+    if (split) {
+        split_merge_kernel<<<units * rows, 128, 0, s>>>(o_part, lse_part, (__nv_bfloat16 *)a.out, a.lse, rows, a.splits, HD);
+        EMBER_CUDA_TRY(cudaGetLastError());
+    }
     return EMBER_OK;
 }
 
@@ -508,6 +594,28 @@ int sm100_attention_fwd(const AttnArgs &a, DeviceState *st, cudaStream_t s)
     if (emu == 0) return launch<64, 0>(a, st, s);
     if (emu == 2) return launch<64, 2>(a, st, s);
     return launch<64, 1>(a, st, s);
+}
+
+// Decode over a contiguous key/value cache on the tensor cores: the query heads that share a K/V
+// head are the rows of one 128-row tile (zero-padded), the key axis is cut into splits.
+bool sm100_cache_decode_supported(const CacheDecodeArgs &a)
+{
+    if (a.dtype != EMBER_BF16 || (a.d != 64 && a.d != 128)) return false;
+    if (a.q_heads % a.kv_heads != 0 || a.q_heads / a.kv_heads > 128) return false;
+    if (!(a.scale != 0.f) || !isfinite(a.scale)) return false;
+    const uintptr_t bits = (uintptr_t)a.q | (uintptr_t)a.k_cache | (uintptr_t)a.v_cache | (uintptr_t)a.out;
+    return (bits & 15) == 0;
+}
+
+size_t sm100_cache_decode_workspace_bytes(int units, int rows, int d, int splits)
+{
+    if (splits <= 1) return 0;
+    return align_up((size_t)units * splits * rows * d * 2, 256) + align_up((size_t)units * splits * rows * sizeof(float), 256);
+}
+
+int sm100_cache_decode(const CacheDecodeArgs &a, DeviceState *st, cudaStream_t s)
+{
+    return a.d == 128 ? launch_cache_decode<128>(a, st, s) : launch_cache_decode<64>(a, st, s);
 }
 
 }  // namespace ember

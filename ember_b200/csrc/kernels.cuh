@@ -30,6 +30,23 @@ int sm100_attention_fwd(const AttnArgs &a, DeviceState *st, cudaStream_t s);
 bool sm100_bwd_supported(const AttnArgs &a);
 int sm100_attention_bwd(const AttnArgs &a, float *delta, DeviceState *st, cudaStream_t s);
 
+// Decode over a contiguous key/value cache with grouped-query heads on the tensor cores
+// (attn_fwd_sm100.cu: the forward kernel with the group's query heads as the rows of one tile and the
+// key axis cut into splits). chunk: keys per split, a multiple of 128; workspace: partial outputs.
+struct CacheDecodeArgs {
+    const void *q = nullptr, *k_cache = nullptr, *v_cache = nullptr;
+    void *out = nullptr;
+    float *lse = nullptr;
+    int batch = 0, q_heads = 0, kv_heads = 0, lk = 0, capacity = 0, d = 0, dtype = EMBER_BF16;
+    float scale = 1.f;
+    const int *seq_lens = nullptr;
+    int splits = 1, chunk = 0;
+    void *workspace = nullptr;
+};
+bool sm100_cache_decode_supported(const CacheDecodeArgs &a);
+size_t sm100_cache_decode_workspace_bytes(int units, int rows, int d, int splits);
+int sm100_cache_decode(const CacheDecodeArgs &a, DeviceState *st, cudaStream_t s);
+
 // Split-KV decode (attn_decode.cu): lq == 1, bf16 or f32 storage, d <= 256 and d % 8 == 0.
 int decode_pick_splits(int bh, int lk, int d, int dtype, int sm_count);
 size_t decode_workspace_bytes(int bh, int d, int splits);

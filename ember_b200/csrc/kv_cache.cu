@@ -10,7 +10,16 @@
 //   queries / outputs  (batch, q_heads, d), q_heads = group * kv_heads; query head h reads K/V head
 //                      h / group
 //
-// The decode kernel is the split-KV kernel of attn_decode.cu with one change that matters for
+// Two decode paths. With bf16 storage, head dimension 64 or 128, a contiguous cache and several
+// query heads per K/V head, the step runs on the tensor cores: the forward kernel of
+// attn_fwd_sm100.cu takes the group's query heads as the rows of one (zero-padded) 128-row tile, one
+// CTA per (batch, kv_head, split) streams its keys by TMA, and a small kernel merges the splits'
+// normalised partial outputs by their log-sum-exps. On CUDA cores the same step is bound by
+// arithmetic as soon as four query heads share a key row (1.85 TB/s of cache traffic measured for
+// groups of 4, no faster than reading the cache once per query head).
+// Everything else (one query head per K/V head, float32, a page table, other head dimensions)
+// runs the CUDA-core kernel below,
+// the split-KV kernel of attn_decode.cu with one change that matters for
 // bandwidth: a CTA owns one (batch, kv_head, split) and ALL `group` query heads that share it, so a
 // K or V row is loaded from HBM once and used by every query head of the group (the cache is the
 // only large stream of a decode step; with group = 4 the step moves a quarter of the bytes a
@@ -385,6 +394,21 @@ int pick_splits(int batch, int kv_heads, int lk, int sm_count)
     return decode_pick_splits(batch * kv_heads, lk, 0, 0, sm_count);
 }
 
+// Tensor-core path: one CTA per (batch, kv_head, split) streams its keys through a 128-key pipeline,
+// so a few CTAs per SM in total are enough; splits of at least 512 keys, in multiples of 128.
+void tensor_core_split(int units, int lk, int sm_count, int requested, int &splits, int &chunk)
+{
+    if (sm_count <= 0) sm_count = 148;
+    long long want = requested > 0 ? requested : (3LL * sm_count + units - 1) / units;
+    const long long most = requested > 0 ? (lk + 127) / 128 : (lk + 511) / 512;
+    if (want > most) want = most;
+    if (want > 64) want = 64;
+    if (want < 1) want = 1;
+    chunk = (int)((lk + want - 1) / want);
+    chunk = (chunk + 127) / 128 * 128;
+    splits = (lk + chunk - 1) / chunk;
+}
+
 int check_cache(const char *fn, int batch, int q_heads, int kv_heads, int lk, int capacity, int d, int dtype,
                 const int *block_table, int page_size, int max_blocks)
 {
@@ -461,7 +485,13 @@ size_t ember_attention_decode_cache_workspace_bytes(int batch, int q_heads, int 
     if (batch <= 0 || q_heads <= 0 || kv_heads <= 0 || lk <= 0 || d <= 0) return 0;
     int splits = num_splits > 0 ? num_splits : ember_attention_decode_cache_splits(batch, kv_heads, lk);
     if (splits > lk) splits = lk;
-    return gqa_workspace_bytes(batch * q_heads, d, splits);
+    size_t need = gqa_workspace_bytes(batch * q_heads, d, splits);
+    // the tensor-core path (bf16, contiguous cache) makes its own split choice; cover both
+    DeviceState *st = device_state();
+    int tsplits, tchunk;
+    tensor_core_split(batch * kv_heads, lk, st ? st->sm_count : 148, num_splits, tsplits, tchunk);
+    const size_t tneed = sm100_cache_decode_workspace_bytes(batch * kv_heads, q_heads / kv_heads, d, tsplits);
+    return tneed > need ? tneed : need;
 }
 
 int ember_attention_decode_cache(const void *q, const void *k_cache, const void *v_cache, void *out, float *lse, int batch,
@@ -479,6 +509,29 @@ int ember_attention_decode_cache(const void *q, const void *k_cache, const void 
                   "ember_attention_decode_cache: q and the caches must be 16-byte aligned");
     DeviceState *st = device_state();
     if (!st) return EMBER_ERR_CUDA;
+    cudaStream_t s = pick_stream(stream, st);
+    if (!block_table && q_heads / kv_heads > 1) {
+        // Grouped-query heads over a contiguous bf16 cache: tensor cores (the CUDA-core kernel below
+        // is arithmetic-bound once several query heads share a key row).
+        CacheDecodeArgs t;
+        t.q = q; t.k_cache = k_cache; t.v_cache = v_cache; t.out = out; t.lse = lse;
+        t.batch = batch; t.q_heads = q_heads; t.kv_heads = kv_heads; t.lk = lk; t.capacity = capacity; t.d = d;
+        t.dtype = dtype; t.scale = scale; t.seq_lens = seq_lens;
+        if (sm100_cache_decode_supported(t)) {
+            tensor_core_split(batch * kv_heads, lk, st->sm_count, num_splits, t.splits, t.chunk);
+            const size_t tneed = sm100_cache_decode_workspace_bytes(batch * kv_heads, q_heads / kv_heads, d, t.splits);
+            if (tneed > 0) {
+                if (!workspace || workspace_bytes < tneed) {
+                    set_error("ember_attention_decode_cache: workspace of %zu bytes needed for %d splits, %zu given", tneed,
+                              t.splits, workspace_bytes);
+                    return EMBER_ERR_WORKSPACE;
+                }
+                EMBER_REQUIRE(((uintptr_t)workspace & 255) == 0, "ember_attention_decode_cache: workspace must be 256-byte aligned");
+            }
+            t.workspace = workspace;
+            return sm100_cache_decode(t, st, s);
+        }
+    }
     int splits = num_splits > 0 ? num_splits : pick_splits(batch, kv_heads, lk, st->sm_count);
     if (splits > lk) splits = lk;
     const size_t need = gqa_workspace_bytes(batch * q_heads, d, splits);
@@ -503,7 +556,6 @@ int ember_attention_decode_cache(const void *q, const void *k_cache, const void 
     a.batch = batch; a.q_heads = q_heads; a.kv_heads = kv_heads; a.lk = lk; a.capacity = capacity; a.d = d;
     a.dtype = dtype; a.scale = scale; a.seq_lens = seq_lens; a.block_table = block_table; a.page_size = page_size;
     a.max_blocks = max_blocks;
-    cudaStream_t s = pick_stream(stream, st);
     if (dtype == EMBER_BF16) return dispatch_lanes<__nv_bfloat16>(a, used, chunk, ws_o, ws_ml, s);
     return dispatch_lanes<float>(a, used, chunk, ws_o, ws_ml, s);
 }

@@ -414,6 +414,6 @@ __device__ __forceinline__ void exp2_poly2(f32x2 x2, float &p0, float &p1)
 
 // Host side: building TMA tensor maps through the driver entry point (no link against libcuda).
 int make_tensor_map_bf16_3d(CUtensorMap *map, const void *base, uint64_t inner, uint64_t rows,
-                            uint64_t batch, uint32_t box_inner, uint32_t box_rows);
+                            uint64_t batch, uint32_t box_inner, uint32_t box_rows, uint64_t batch_stride_rows = 0);
 
 }  // namespace ember

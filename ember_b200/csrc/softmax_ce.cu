@@ -118,6 +118,7 @@ __global__ void __launch_bounds__(W < 256 ? 256 : W) row_softmax_kernel(const T 
         float m = -INFINITY;
         if (active) {
             if constexpr (VEC) {
+#pragma unroll 4
                 for (int j = t; j < nvec; j += W) {
                     const uint4 u = xv[j];
                     if (cached) bufv[j] = u;
@@ -139,6 +140,7 @@ __global__ void __launch_bounds__(W < 256 ? 256 : W) row_softmax_kernel(const T 
         float s = 0.f;
         if (active) {
             if constexpr (VEC) {
+#pragma unroll 4
                 for (int j = t; j < nvec; j += W) {
                     float v[NV];
                     Vec16<T>::unpack(cached ? bufv[j] : xv[j], v);
@@ -159,6 +161,7 @@ __global__ void __launch_bounds__(W < 256 ? 256 : W) row_softmax_kernel(const T 
             if constexpr (VEC) {
                 uint4 *yv = reinterpret_cast<uint4 *>(yr);
                 const uint4 *tv4 = reinterpret_cast<const uint4 *>(tr);
+#pragma unroll 4
                 for (int j = t; j < nvec; j += W) {
                     float v[NV], o[NV], tv[NV];
                     Vec16<T>::unpack(cached ? bufv[j] : xv[j], v);

@@ -25,17 +25,19 @@ static EncodeTiledFn encode_fn()
 
 // A (batch, rows, inner) row-major bf16 tensor viewed as a 3-D TMA tensor; boxes of
 // box_rows x box_inner elements with the 128-byte swizzle (box_inner * 2 bytes must be 128).
-// Out-of-range parts of a box read as zero.
+// Out-of-range parts of a box read as zero. batch_stride_rows > rows describes a tensor whose batch
+// entries hold more rows than are valid (a cache with spare capacity): rows past `rows` read as zero.
 int make_tensor_map_bf16_3d(CUtensorMap *map, const void *base, uint64_t inner, uint64_t rows,
-                            uint64_t batch, uint32_t box_inner, uint32_t box_rows)
+                            uint64_t batch, uint32_t box_inner, uint32_t box_rows, uint64_t batch_stride_rows)
 {
+    if (batch_stride_rows == 0) batch_stride_rows = rows;  // dense: one batch entry right after the other
     EncodeTiledFn fn = encode_fn();
     if (!fn) {
         set_error("cuTensorMapEncodeTiled is not available from this driver");
         return EMBER_ERR_CUDA;
     }
     cuuint64_t dims[3] = {inner, rows, batch};
-    cuuint64_t strides[2] = {inner * 2, rows * inner * 2};
+    cuuint64_t strides[2] = {inner * 2, batch_stride_rows * inner * 2};
     cuuint32_t box[3] = {box_inner, box_rows, 1};
     cuuint32_t estr[3] = {1, 1, 1};
     CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(base), dims, strides, box,

@@ -232,7 +232,10 @@ EMBER_API int ember_cross_entropy_bwd(const void *probs, const void *target, voi
  * are loaded once for all its query heads. Sequence b attends to its first seq_lens[b] keys (each
  * >= 1), or to `lk` keys when seq_lens is NULL; with seq_lens, `lk` is an upper bound of the lengths
  * (it sizes the split of the key axis). lse (batch, q_heads) may be NULL. Workspace as for
- * ember_attention_decode, sized by ember_attention_decode_cache_workspace_bytes. */
+ * ember_attention_decode, sized by ember_attention_decode_cache_workspace_bytes.
+ * Kernels: bf16, d in {64, 128}, a contiguous cache and more than one query head per K/V head run
+ * on the tensor cores (the group's query heads are the rows of one tile); everything else (one
+ * query head per K/V head, float32, a page table, other head dimensions) on the CUDA-core kernel. */
 EMBER_API int ember_kv_cache_append(void *k_cache, void *v_cache, const void *k_new, const void *v_new, int batch,
                                     int kv_heads, int capacity, int d, int n_new, int pos, const int *seq_lens,
                                     const int *block_table, int page_size, int max_blocks, int dtype, void *stream);
