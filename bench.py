@@ -398,7 +398,7 @@ def run_gpu_arm(args):
 
 
 def run_c5_sweep(L, _lib, torch, dist, dev, sptr, stream, rank, world):
-    """BASELINE configs[4]: causal forward+backward, bf16, 128 (batch*head) units with D=128 split over
+    """The strong-scaling configuration: causal forward+backward, bf16, 128 (batch*head) units with D=128 split over
     the ranks (strong scaling: the total work is fixed), L in {2048, 8192, 16384}. Every rank owns
     the contiguous slab shard_range(128, rank, world); no collective on the data path. Returns, per
     L, the whole-job TFLOP/s from the slowest rank's device time."""
@@ -654,6 +654,23 @@ def run_profile_case(args):
         fn = fwd if args.profile == "fwd" else bwd
         work = 4.0 * B * H * S * S * D / 2.0 * (1.0 if args.profile == "fwd" else 2.5)
         unit, name = "TFLOP/s", f"causal_{args.profile}_bf16_B{B}_H{H}_L{S}_D{D}"
+    elif args.profile == "decode_gqa":
+        B, Hq, Hkv, Lk = 16, 32, 8, 32768  # 2.1 GB of cache, read once per step
+        kc = (torch.randn((B, Hkv, Lk, D), generator=gen, device=dev) * 0.5).to(torch.bfloat16)
+        vc = (torch.randn((B, Hkv, Lk, D), generator=gen, device=dev) * 0.5).to(torch.bfloat16)
+        qd = (torch.randn((B, Hq, D), generator=gen, device=dev) * 0.5).to(torch.bfloat16)
+        od = torch.empty_like(qd)
+        ld = torch.empty((B, Hq), device=dev, dtype=torch.float32)
+        wsn = L.ember_attention_decode_cache_workspace_bytes(B, Hq, Hkv, Lk, D, 0)
+        ws = torch.empty(max(wsn, 256), device=dev, dtype=torch.uint8)
+
+        def fn():
+            _lib.check(L.ember_attention_decode_cache(qd.data_ptr(), kc.data_ptr(), vc.data_ptr(), od.data_ptr(),
+                                                      ld.data_ptr(), B, Hq, Hkv, Lk, Lk, D, scale, 1, None, None, 0, 0, 0,
+                                                      ws.data_ptr(), wsn, sptr))
+
+        work = 2.0 * B * Hkv * Lk * D * 2
+        unit, name = "GB/s", f"decode_gqa_bf16_B{B}_Hq{Hq}_Hkv{Hkv}_Lk{Lk}_D{D}"
     elif args.profile == "softmax":
         rows, cols = 32768, 4096  # 268 MB in, 268 MB out
         xs = (torch.randn((rows, cols), generator=gen, device=dev) * 3).to(torch.bfloat16)
@@ -715,7 +732,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extra", action="store_true", help="skip the backward and decode extras at N=1")
-    ap.add_argument("--profile", choices=["fwd", "bwd", "decode", "linear", "softmax"], default=None,
+    ap.add_argument("--profile", choices=["fwd", "bwd", "decode", "decode_gqa", "linear", "softmax"], default=None,
                     help="run only a small single-kernel case (for ncu captures) and exit")
     args = ap.parse_args()
     if args.profile:

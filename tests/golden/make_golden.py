@@ -1,6 +1,6 @@
 """Generates tests/golden/attention_golden.npz by running the REFERENCE itself.
 
-Run in a container that has the reference checkout (default /root/reference):
+Run where the reference checkout is available (its path in the EMBER_REFERENCE environment variable):
 
     make -C oracle ref && python tests/golden/make_golden.py
 
@@ -35,7 +35,7 @@ ROOT = os.path.dirname(os.path.dirname(HERE))
 
 CASES = {
     # name: (B, H, Lq, Lk, D, causal, seed, with_backward)
-    "c1_fwd_f32": (2, 4, 128, 128, 64, False, 1, False),  # BASELINE configs[0]
+    "c1_fwd_f32": (2, 4, 128, 128, 64, False, 1, False),  # the reference-runnable float32 configuration
     "c1_causal": (1, 2, 128, 128, 64, True, 2, True),
     "ragged_causal": (1, 2, 48, 80, 32, True, 3, True),
     "ragged_noncausal": (1, 3, 37, 129, 64, False, 4, True),

@@ -1,4 +1,4 @@
-"""GPU tests at the full BASELINE sizes. The CPU oracle is far too slow there (minutes per
+"""GPU tests at the full sizes of the benchmark configurations. The CPU oracle is far too slow there (minutes per
 (batch, head) slice), so parity is established in two ways: whole tensors against this library's
 float32-arithmetic CUDA-core kernels (themselves pinned to the oracle and the golden vectors by the
 small-shape tests), and one full (batch, head) slice against the CPU oracle."""
