@@ -270,6 +270,8 @@ def run_gpu_arm(args):
         raise SystemExit("bench.py needs a CUDA device; there is no CPU fallback for the attention path")
     torch.cuda.set_device(local_rank)
     if world > 1:
+        if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":  # keeps stdout to the one JSON line
+            os.environ["NCCL_DEBUG"] = "WARN"
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     L = _lib.lib()
     _lib.check(L.ember_set_device(local_rank))
