@@ -127,6 +127,80 @@ size_t ember_attention_workspace_bytes(int op, int batch_heads, int lq, int lk, 
     }
 }
 
+// Forward over tensors that live in HOST memory (the reference's own calling pattern: NumPy in,
+// NumPy out). The (batch*head) units are independent, so they are processed in chunks through two
+// sets of device staging buffers: while chunk c computes, chunk c+1 is copied in and chunk c-1 is
+// copied out, on three streams chained by events. With pinned host memory the copies run at the
+// PCIe rate in both directions at once and the kernel time disappears behind them.
+int ember_attention_fwd_host(const void *q_host, const void *k_host, const void *v_host, void *out_host, float *lse_host,
+                             int batch_heads, int lq, int lk, int d, float scale, int causal, int dtype)
+{
+    int rc = check_common("ember_attention_fwd_host", batch_heads, lq, lk, d, dtype, scale);
+    if (rc) return rc;
+    EMBER_REQUIRE(q_host && k_host && v_host && out_host, "ember_attention_fwd_host: NULL tensor pointer");
+    EMBER_REQUIRE(!causal || lq <= lk, "ember_attention_fwd_host: causal attention needs lq <= lk, got lq=%d lk=%d", lq, lk);
+    DeviceState *st = device_state();
+    if (!st) return EMBER_ERR_CUDA;
+    if (!st->copy_in) {
+        EMBER_CUDA_TRY(cudaStreamCreateWithFlags(&st->copy_in, cudaStreamNonBlocking));
+        EMBER_CUDA_TRY(cudaStreamCreateWithFlags(&st->copy_out, cudaStreamNonBlocking));
+        for (int i = 0; i < 2; i++) {
+            EMBER_CUDA_TRY(cudaEventCreateWithFlags(&st->in_done[i], cudaEventDisableTiming));
+            EMBER_CUDA_TRY(cudaEventCreateWithFlags(&st->compute_done[i], cudaEventDisableTiming));
+            EMBER_CUDA_TRY(cudaEventCreateWithFlags(&st->out_done[i], cudaEventDisableTiming));
+        }
+    }
+    const size_t es = dtype_size(dtype);
+    const size_t q_unit = (size_t)lq * d * es, k_unit = (size_t)lk * d * es, l_unit = (size_t)lq * sizeof(float);
+    // chunks of about 32 MB of inputs, at least 2 so that copies and compute overlap, at most 16
+    int chunks = (int)(((q_unit + 2 * k_unit) * batch_heads + (32u << 20) - 1) / (32u << 20));
+    if (chunks < 2) chunks = 2;
+    if (chunks > 16) chunks = 16;
+    if (chunks > batch_heads) chunks = batch_heads;
+    const int per = (batch_heads + chunks - 1) / chunks;
+    chunks = (batch_heads + per - 1) / per;
+    // two sets of staging buffers: q, k, v, out, lse for `per` units each
+    const size_t set_bytes = align_up(per * q_unit, 256) * 2 + align_up(per * k_unit, 256) * 2 + align_up(per * l_unit, 256);
+    char *stage = (char *)alloc_memory(2 * set_bytes);
+    if (!stage) return EMBER_ERR_NOMEM;
+    // the staging memory was allocated in the order of the compute stream: the copy stream waits for it
+    EMBER_CUDA_TRY(cudaEventRecord(st->compute_done[0], st->stream));
+    EMBER_CUDA_TRY(cudaEventRecord(st->compute_done[1], st->stream));
+    EMBER_CUDA_TRY(cudaEventRecord(st->out_done[0], st->copy_out));
+    EMBER_CUDA_TRY(cudaEventRecord(st->out_done[1], st->copy_out));
+    for (int c = 0; c < chunks; c++) {
+        const int b = c & 1, u0 = c * per, n = (u0 + per <= batch_heads) ? per : batch_heads - u0;
+        char *dq = stage + b * set_bytes, *dk = dq + align_up(per * q_unit, 256), *dv = dk + align_up(per * k_unit, 256);
+        char *dout = dv + align_up(per * k_unit, 256), *dl = dout + align_up(per * q_unit, 256);
+        // inputs of this set may be overwritten once the kernel that last read them is done
+        EMBER_CUDA_TRY(cudaStreamWaitEvent(st->copy_in, st->compute_done[b], 0));
+        EMBER_CUDA_TRY(cudaMemcpyAsync(dq, (const char *)q_host + u0 * q_unit, n * q_unit, cudaMemcpyHostToDevice, st->copy_in));
+        EMBER_CUDA_TRY(cudaMemcpyAsync(dk, (const char *)k_host + u0 * k_unit, n * k_unit, cudaMemcpyHostToDevice, st->copy_in));
+        EMBER_CUDA_TRY(cudaMemcpyAsync(dv, (const char *)v_host + u0 * k_unit, n * k_unit, cudaMemcpyHostToDevice, st->copy_in));
+        EMBER_CUDA_TRY(cudaEventRecord(st->in_done[b], st->copy_in));
+        // the kernel needs its inputs, and its output buffer must have been copied out
+        EMBER_CUDA_TRY(cudaStreamWaitEvent(st->stream, st->in_done[b], 0));
+        EMBER_CUDA_TRY(cudaStreamWaitEvent(st->stream, st->out_done[b], 0));
+        if ((rc = ember_attention_fwd(dq, dk, dv, dout, (float *)dl, n, lq, lk, d, scale, causal, dtype, st->stream)) != EMBER_OK) {
+            cudaStreamSynchronize(st->copy_in);
+            cudaStreamSynchronize(st->copy_out);
+            free_memory(stage);
+            return rc;
+        }
+        EMBER_CUDA_TRY(cudaEventRecord(st->compute_done[b], st->stream));
+        EMBER_CUDA_TRY(cudaStreamWaitEvent(st->copy_out, st->compute_done[b], 0));
+        EMBER_CUDA_TRY(cudaMemcpyAsync((char *)out_host + u0 * q_unit, dout, n * q_unit, cudaMemcpyDeviceToHost, st->copy_out));
+        if (lse_host)
+            EMBER_CUDA_TRY(cudaMemcpyAsync((char *)lse_host + u0 * l_unit, dl, n * l_unit, cudaMemcpyDeviceToHost, st->copy_out));
+        EMBER_CUDA_TRY(cudaEventRecord(st->out_done[b], st->copy_out));
+    }
+    EMBER_CUDA_TRY(cudaStreamSynchronize(st->copy_out));
+    EMBER_CUDA_TRY(cudaStreamSynchronize(st->copy_in));
+    // every user of the staging memory has finished; release it in the compute stream's order
+    free_memory(stage);
+    return EMBER_OK;
+}
+
 const char *ember_attention_kernel_name(int op, int lq, int lk, int d, int dtype)
 {
     (void)lk;

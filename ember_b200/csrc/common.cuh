@@ -24,6 +24,9 @@ struct DeviceState {
     cudaStream_t stream = nullptr;
     DeviceStatus *status = nullptr;  // device memory
     int sm_count = 0;
+    // for the host-tensor entry point: copy streams and the events that chain them (made on first use)
+    cudaStream_t copy_in = nullptr, copy_out = nullptr;
+    cudaEvent_t in_done[2] = {}, compute_done[2] = {}, out_done[2] = {};
 };
 
 // State of the current device, created on first use. Returns nullptr and sets the error

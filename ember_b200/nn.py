@@ -153,3 +153,26 @@ class MultiHeadAttention:
         attention_backward(q, k, v, self._o, self._lse, grad_o, None, self.causal, into=self._split(grad_qkv))
         grad_x, self.grad_w_qkv, self.grad_b_qkv = linear_backward(self.x, self.w_qkv, grad_qkv, y_heads=H)
         return grad_x
+
+    # ---- generation: the same block over a key/value cache -----------------------------------
+    def prefill(self, x: Tensor, cache) -> Tensor:
+        """forward(x) under the causal mask that also stores the keys and values of x's positions in
+        ``cache`` (a ``KVCache`` with kv_heads == num_heads), ready for ``decode_step``."""
+        if not self.causal:
+            raise ValueError("prefill/decode_step need a causal MultiHeadAttention")
+        y = self.forward(x, False)
+        _, k, v = self._split(self._qkv)
+        cache.append(k, v)
+        return y
+
+    def decode_step(self, x_t: Tensor, cache) -> Tensor:
+        """One new position: x_t is (B, 1, E). Its key and value are appended to ``cache`` and its
+        query attends over everything stored so far; returns (B, 1, E)."""
+        if len(x_t.shape) != 3 or x_t.shape[1] != 1 or x_t.shape[2] != self.embed_dim:
+            raise ValueError(f"decode_step expects (B, 1, {self.embed_dim}), got {x_t.shape}")
+        B, H, D = x_t.shape[0], self.num_heads, self.embed_dim // self.num_heads
+        qkv = linear_forward(x_t, self.w_qkv, self.b_qkv, y_heads=H)  # (3, B, H, 1, D)
+        q, k, v = self._split(qkv)
+        cache.append(k, v)
+        o, _ = cache.decode(q.view(0, (B, H, D)))
+        return linear_forward(o.view(0, (B, H, 1, D)), self.w_o, self.b_o, x_heads=H)

@@ -144,6 +144,17 @@ EMBER_API int ember_attention_decode(const void *q, const void *k, const void *v
 EMBER_API int ember_attention_decode_static(const void *q, const void *k, const void *v, void *out,
                                             float *lse, int batch_heads, int lk, int d, float scale,
                                             int dtype, int num_splits, void *stream);
+/* Forward over tensors in HOST memory, the reference's own calling pattern (NumPy array in,
+ * Tensor, operators, to_np() out: ember/tensor/tensor.py:78-117,224-226). q, k, v, out (and lse,
+ * which may be NULL) are host pointers with the layouts of ember_attention_fwd; pinned (page-locked)
+ * memory lets the copies overlap. The (batch*head) units are streamed through device staging
+ * buffers in chunks, copy-in, compute and copy-out on three streams, so the call costs about the
+ * larger of the two PCIe directions instead of their sum plus the kernel. Returns when out_host is
+ * complete. */
+EMBER_API int ember_attention_fwd_host(const void *q_host, const void *k_host, const void *v_host, void *out_host,
+                                       float *lse_host, int batch_heads, int lq, int lk, int d, float scale, int causal,
+                                       int dtype);
+
 /* Size in bytes of the built-in scratch array of ember_attention_decode_static. */
 EMBER_API size_t ember_attention_decode_static_capacity(void);
 

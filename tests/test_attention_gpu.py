@@ -2,6 +2,8 @@
 reference's golden vectors. Tolerances (max-abs): float32 I/O <= 1e-3 on O (the float32 kernels
 are held to 1e-4 here); bf16 I/O <= 2e-2 on O with oracle inputs rounded to bf16 first; gradients
 in bf16 mode <= 2e-2 relative to the largest reference magnitude of that tensor."""
+import math
+
 import numpy as np
 import pytest
 
@@ -226,3 +228,35 @@ def test_bounded_wait_reports_timeout_and_context_survives():
     ro, _ = cpu_oracle.attention_fwd(q, k, v, None, True)
     o, _ = run_fwd(q, k, v, None, True, "bfloat16")
     assert np.abs(o - ro).max() <= BF16_TOL
+
+
+def test_forward_over_host_tensors_equals_device_path():
+    """ember_attention_fwd_host (chunked copy-in / compute / copy-out) gives the device path's bits."""
+    import ctypes
+
+    torch = pytest.importorskip("torch")
+    L = _lib.lib()
+    _lib.check(L.ember_set_device(0))
+    dev = torch.device("cuda", 0)
+    for (BH, Lq, Lk, D, causal, dt, tdt) in ((37, 300, 300, 128, 1, _lib.EMBER_BF16, torch.bfloat16),
+                                               (5, 64, 200, 64, 0, _lib.EMBER_F32, torch.float32),
+                                               (1, 130, 130, 128, 1, _lib.EMBER_BF16, torch.bfloat16)):
+        g = torch.Generator().manual_seed(BH)
+        q = (torch.randn((BH, Lq, D), generator=g) * 0.5).to(tdt).pin_memory()
+        k = (torch.randn((BH, Lk, D), generator=g) * 0.5).to(tdt).pin_memory()
+        v = (torch.randn((BH, Lk, D), generator=g) * 0.5).to(tdt).pin_memory()
+        out = torch.empty_like(q).pin_memory()
+        lse = torch.empty((BH, Lq), dtype=torch.float32).pin_memory()
+        sc = 1.0 / math.sqrt(D)
+        _lib.check(L.ember_attention_fwd_host(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(), BH, Lq,
+                                              Lk, D, sc, causal, dt))
+        dq, dk, dv = q.to(dev), k.to(dev), v.to(dev)
+        do, dl = torch.empty_like(dq), torch.empty((BH, Lq), device=dev, dtype=torch.float32)
+        torch.cuda.synchronize()
+        _lib.check(L.ember_attention_fwd(dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), do.data_ptr(), dl.data_ptr(), BH, Lq, Lk,
+                                         D, sc, causal, dt, None))
+        L.sync_device()
+        assert torch.equal(out, do.cpu()) and torch.equal(lse, dl.cpu())
+    with pytest.raises(ValueError):
+        _lib.check(L.ember_attention_fwd_host(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), None, 0, 1, 1, 8, 1.0, 0,
+                                              _lib.EMBER_F32))

@@ -104,3 +104,21 @@ def test_kv_cache_class_grows_and_decodes(em):
         cache.append(em.Tensor(k[:, :, :30]), em.Tensor(v[:, :, :30]))
     with pytest.raises(ValueError):
         cache.decode(em.Tensor(np.zeros((B, 3, D), np.float32)))
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", 2e-3), ("bfloat16", 5e-2)])
+def test_generation_with_cache_matches_full_forward(em, dtype, tol):
+    """prefill + decode_step token by token gives the rows the causal block gives on the whole sequence."""
+    B, L, E, H, P = 2, 24, 128, 2, 16
+    rng = np.random.default_rng(4)
+    x = rng.standard_normal((B, L, E), dtype=np.float32)
+    layer = em.nn.MultiHeadAttention(E, H, causal=True, dtype=dtype, seed=3)
+    full = layer(em.Tensor(x, dtype), False).to_np()
+    cache = em.KVCache(B, H, 32, E // H, dtype=dtype)
+    y0 = layer.prefill(em.Tensor(np.ascontiguousarray(x[:, :P]), dtype), cache).to_np()
+    assert np.abs(y0 - full[:, :P]).max() <= tol * max(1.0, np.abs(full).max())
+    for t in range(P, L):
+        yt = layer.decode_step(em.Tensor(np.ascontiguousarray(x[:, t:t + 1]), dtype), cache).to_np()
+        assert yt.shape == (B, 1, E)
+        assert np.abs(yt[:, 0] - full[:, t]).max() <= tol * max(1.0, np.abs(full).max())
+    assert cache.length == L
