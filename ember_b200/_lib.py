@@ -44,6 +44,7 @@ SIGNATURES = {
     "ember_attention_workspace_bytes": (_sz, [_i] * 7),
     "ember_attention_decode_splits": (_i, [_i] * 4),
     "ember_attention_kernel_name": (ctypes.c_char_p, [_i] * 5),
+    "ember_work_order_item": (_i, [_i, _i, _i, _sz, _i, _i, ctypes.POINTER(_i), ctypes.POINTER(_i)]),
     "ember_attention_fwd_host": (_i, [_vp] * 5 + [_i] * 4 + [ctypes.c_float, _i, _i]),
     "ember_linear_fwd": (_i, [_vp] * 4 + [ctypes.c_longlong] + [_i] * 7 + [_vp]),
     "ember_linear_bwd": (_i, [_vp] * 6 + [ctypes.c_longlong] + [_i] * 7 + [_vp]),

@@ -92,16 +92,20 @@ inline WorkOrder make_work_order(int units, int blocks, int sm_count, size_t tou
 }
 
 #ifdef __CUDACC__
-__device__ __forceinline__ void work_item(const WorkOrder &w, int idx, int &unit, int &rank)
+#define EMBER_HD __host__ __device__ __forceinline__
+#else
+#define EMBER_HD inline
+#endif
+EMBER_HD void work_item(const WorkOrder &w, int idx, int &unit, int &rank)
 {
     const int per_group = w.group * w.blocks;
-    const int g = min(idx / per_group, w.ngroups - 1);
+    int g = idx / per_group;
+    if (g > w.ngroups - 1) g = w.ngroups - 1;
     const int rem = idx - g * per_group;
     const int units_here = (g == w.ngroups - 1) ? w.units - g * w.group : w.group;
     rank = rem / units_here;
     unit = g * w.group + (rem - rank * units_here);
 }
-#endif
 
 inline size_t dtype_size(int dtype) { return dtype == EMBER_BF16 ? 2 : 4; }
 

@@ -147,6 +147,16 @@ void sync_device(void)
     if (e != cudaSuccess) cuda_fail(e, "sync_device");
 }
 
+int ember_work_order_item(int units, int blocks, int sm_count, size_t touched_bytes_per_unit, int causal, int index,
+                          int *unit, int *rank)
+{
+    EMBER_REQUIRE(units > 0 && blocks > 0 && unit && rank, "ember_work_order_item: bad arguments");
+    EMBER_REQUIRE(index >= 0 && (long long)index < (long long)units * blocks, "ember_work_order_item: index %d out of range", index);
+    const WorkOrder w = make_work_order(units, blocks, sm_count, touched_bytes_per_unit, causal != 0);
+    work_item(w, index, *unit, *rank);
+    return EMBER_OK;
+}
+
 int ember_set_device(int device)
 {
     EMBER_CUDA_TRY(cudaSetDevice(device));

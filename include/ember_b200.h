@@ -165,6 +165,14 @@ EMBER_API size_t ember_attention_workspace_bytes(int op, int batch_heads, int lq
 /* The split count ember_attention_decode uses for num_splits <= 0. */
 EMBER_API int ember_attention_decode_splits(int batch_heads, int lk, int d, int dtype);
 
+/* The order in which the CTAs of the tensor-core attention kernels take their work, for tests and
+ * tools (pure host arithmetic, no device needed): CTA `index` of a launch over `units` (batch*head)
+ * units of `blocks` row blocks each works on block rank *rank (0 = heaviest under a causal mask) of
+ * unit *unit. Units are taken in groups sized from sm_count and, under a causal mask, from the bytes
+ * one unit touches, so that concurrently running CTAs share their K/V through L2. */
+EMBER_API int ember_work_order_item(int units, int blocks, int sm_count, size_t touched_bytes_per_unit, int causal,
+                                    int index, int *unit, int *rank);
+
 /* Name of the kernel family the forward/backward dispatcher picks for these
  * arguments: "sm100_tcgen05" or "simt_f32". For tests and the benchmark. */
 EMBER_API const char *ember_attention_kernel_name(int op, int lq, int lk, int d, int dtype);

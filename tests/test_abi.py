@@ -117,3 +117,28 @@ def test_cpython_binding_surface_and_type_errors():
         _core._from_numpy(np.zeros(4, np.float64))
     with pytest.raises(ValueError):
         _core._from_numpy(np.zeros(4, np.float32), 7)
+
+
+def test_work_order_visits_every_block_once_and_groups_units():
+    """Host arithmetic of the CTA order: a bijection onto (unit, block rank); within a group the
+    heaviest ranks come first; concurrently launched CTAs (consecutive indices) share few units."""
+    import ctypes
+
+    L = _lib.lib()
+    u, r = ctypes.c_int(), ctypes.c_int()
+    for units, blocks, touched, causal in ((128, 16, 4 << 20, 1), (128, 16, 4 << 20, 0), (64, 32, 8 << 20, 1),
+                                           (7, 200, 100 << 20, 1), (149, 1, 64, 0), (13, 16, 2 << 20, 1), (1, 1, 1, 0)):
+        seen, order = set(), []
+        for idx in range(units * blocks):
+            assert L.ember_work_order_item(units, blocks, 148, touched, causal, idx, ctypes.byref(u), ctypes.byref(r)) == 0
+            assert 0 <= u.value < units and 0 <= r.value < blocks
+            seen.add((u.value, r.value))
+            order.append((u.value, r.value))
+        assert len(seen) == units * blocks
+        # a unit's blocks are taken heaviest first
+        for unit in {0, units - 1}:
+            ranks = [rk for (un, rk) in order if un == unit]
+            assert ranks == sorted(ranks)
+        if units * blocks >= 296:
+            assert len({un for (un, _) in order[:148]}) <= max(148 // blocks + 1, (64 << 20) // max(touched, 1)) + 1
+    assert L.ember_work_order_item(4, 4, 148, 1, 0, 16, ctypes.byref(u), ctypes.byref(r)) != 0
