@@ -24,6 +24,12 @@
 // reference maximum is only moved, and O rescaled, when the row maximum grew by more than 2^8,
 // which after the first tiles is rare. Causal tiles above the diagonal are never loaded or
 // multiplied; only tiles crossed by the diagonal (or by the end of the key axis) pay for a mask.
+// CTAs take their work in the order of WorkOrder (common.cuh): a few (batch*head) units at a time,
+// heaviest query blocks first, so that the K and V of the units in flight stay in L2.
+// The same kernel serves decode over a key/value cache with grouped-query heads (split-key mode):
+// the query heads that share a K/V head are the rows of one zero-padded tile, a CTA covers one split
+// of the key axis and writes a normalised partial output with its log-sum-exp, and
+// split_merge_kernel combines the splits.
 #include <math.h>
 #include <stdlib.h>
 
