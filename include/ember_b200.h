@@ -246,8 +246,8 @@ EMBER_API int ember_cross_entropy_bwd(const void *probs, const void *target, voi
  * skipped and reported through ember_check_device_status (EMBER_ERR_INVALID). The caller advances
  * its lengths.
  *
- * ember_attention_decode_cache: q and out are (batch, q_heads, d), q_heads a multiple (1, 2, 4 or 8)
- * of kv_heads; query head h reads K/V head h / (q_heads / kv_heads), and the K/V rows of a group
+ * ember_attention_decode_cache: q and out are (batch, q_heads, d), q_heads a multiple of kv_heads
+ * (1, 2, 4 or 8 times on the CUDA-core kernel, any multiple up to 128 on the tensor-core path); query head h reads K/V head h / (q_heads / kv_heads), and the K/V rows of a group
  * are loaded once for all its query heads. Sequence b attends to its first seq_lens[b] keys (each
  * >= 1), or to `lk` keys when seq_lens is NULL; with seq_lens, `lk` is an upper bound of the lengths
  * (it sizes the split of the key axis). lse (batch, q_heads) may be NULL. Workspace as for
