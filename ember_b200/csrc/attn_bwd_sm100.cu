@@ -69,9 +69,9 @@ struct BwdCfg {
     static constexpr int OFF_A = 2 * TILE_BYTES;
     static constexpr int OFF_B = OFF_A + NA * TILE_BYTES;
     static constexpr int OFF_BAR = OFF_B + NB * TILE_BYTES;
-    static constexpr int OFF_ROWVEC = OFF_BAR + 144;    // [2 buffers][2 vectors][128] floats
+    static constexpr int OFF_ROWVEC = OFF_BAR + 160;    // [2 buffers][2 vectors][128] floats
     static constexpr int USED_BYTES = OFF_ROWVEC + 2048;
-    // 7 tiles of 32 KB leave 880 bytes below the 227 KB limit at HD = 128: that is the room for
+    // 7 tiles of 32 KB leave 864 bytes below the 227 KB limit at HD = 128: that is the room for
     // rounding the dynamic shared memory base up to 1024 bytes (the kernel checks that it fits).
     static constexpr int SMEM_BYTES = HD == 128 ? 232448 : USED_BYTES + 1024;
     static constexpr int T_S = 0, T_DP = 128, T_ACC0 = 256, T_ACC1 = 256 + HD;
@@ -82,7 +82,9 @@ struct BwdCfg {
                          B_DP = B_S + 1,           // dP (or dP^T) is in TMEM
                          B_P = B_DP + 1,           // dK/dV: P^T written; dQ: S has been read (8 warp arrivals)
                          B_DS = B_P + 1,           // dS (or dS^T) written (8 warp arrivals)
-                         B_ACC = B_DS + 1, NUM_BARS = B_ACC + 1;
+                         B_ACC = B_DS + 1,
+                         B_DP1 = B_ACC + 1,        // dQ kernel: second dP / dS buffer (odd key tiles)
+                         B_DS1 = B_DP1 + 1, NUM_BARS = B_DS1 + 1;
 };
 
 enum { WB_RES = 101, WB_FULL, WB_EMPTY, WB_S, WB_DP, WB_P, WB_DS, WB_ACC, WB_SMEM };
@@ -121,6 +123,8 @@ __device__ __forceinline__ uint32_t bwd_setup(uint32_t smem_base, uint8_t *smem_
         mbar_init(bar0 + 8 * C::B_P, NCW);   // one arrival per compute warp
         mbar_init(bar0 + 8 * C::B_DS, NCW);
         mbar_init(bar0 + 8 * C::B_ACC, 2);  // one commit from each MMA warp
+        mbar_init(bar0 + 8 * C::B_DP1, 1);
+        mbar_init(bar0 + 8 * C::B_DS1, NCW);
         fence_mbar_init();
     }
     if (warp == W_ALLOC) {
@@ -601,14 +605,18 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
                 }
                 tc_commit_elect(BAR(C::B_S));
             };
+            // dP and dS live in two TMEM buffers, by the parity of the key tile (the dQ accumulator
+            // leaves 128 columns free in this kernel): dP(j+2) is computed while dQ(j+1) still reads
+            // dS(j+1) from the other buffer, so the gradient chain never waits for its own MMA.
             auto issue_dp = [&](int j) {  // dP = dO V^T
                 const uint32_t v_lo = desc_lo(v_addr(j), 16);
+                const uint32_t t_dp = tmem + ((j & 1) ? C::T_ACC1 : C::T_DP);
 #pragma unroll
                 for (int ks = 0; ks < HD / 16; ks++) {
                     const uint32_t o16 = ((ks / 4) * C::SUB_BYTES + (ks % 4) * 32) >> 4;
-                    mma_ss_lo(tmem + C::T_DP, do_lo + o16, v_lo + o16, IDESC_SS, ks > 0);
+                    mma_ss_lo(t_dp, do_lo + o16, v_lo + o16, IDESC_SS, ks > 0);
                 }
-                tc_commit_elect(BAR(C::B_DP));
+                tc_commit_elect(BAR((j & 1) ? C::B_DP1 : C::B_DP));
                 tc_commit_elect(BAR(C::B_EMPTYB + j % C::NB));  // V(j) is only read by dP(j)
             };
             bool ok = mbar_wait(BAR(C::B_RES), 0, abort_flag, p.status, WB_RES);
@@ -629,25 +637,32 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
                 }
                 tc_commit_elect(BAR(C::B_ACC));
             } else {
-                // gradient chain: dP(0); then per tile dQ(j) (reads dS, K) and dP(j+1) (overwrites dS)
+                // gradient chain: dP(0), dP(1); then per tile dQ(j) (reads dS(j) and K(j)) and dP(j+2)
+                // (overwrites dS(j): issued after dQ(j), and the tensor core keeps that order)
                 ok = ok && mbar_wait(BAR(C::B_FULLB + 0), 0, abort_flag, p.status, WB_FULL);
                 tc_fence_after();
                 issue_dp(0);
+                if (n > 1) {
+                    ok = ok && mbar_wait(BAR(C::B_FULLB + 1 % C::NB), (1 / C::NB) & 1, abort_flag, p.status, WB_FULL);
+                    tc_fence_after();
+                    issue_dp(1);
+                }
                 for (int j = 0; j < n && ok; j++) {
                     const uint32_t kmn_lo = desc_lo(k_addr(j), C::SUB_BYTES);
+                    const uint32_t t_ds = tmem + ((j & 1) ? C::T_ACC1 : C::T_DP);
                     ok = ok && mbar_wait(BAR(C::B_FULLA + j % C::NA), (j / C::NA) & 1, abort_flag, p.status, WB_FULL);
-                    ok = ok && mbar_wait(BAR(C::B_DS), j & 1, abort_flag, p.status, WB_DS);
+                    ok = ok && mbar_wait(BAR((j & 1) ? C::B_DS1 : C::B_DS), (j >> 1) & 1, abort_flag, p.status, WB_DS);
                     tc_fence_after();
 #pragma unroll
                     for (int ks = 0; ks < 8; ks++)  // dQ += dS K
-                        mma_ts_lo(tmem + C::T_ACC0, tmem + C::T_DP + ks * 8, kmn_lo + ks * (2048 >> 4), IDESC_TS,
+                        mma_ts_lo(tmem + C::T_ACC0, t_ds + ks * 8, kmn_lo + ks * (2048 >> 4), IDESC_TS,
                                   (j > 0 || ks > 0) ? 1u : 0u);
                     tc_commit_elect(BAR(C::B_EMPTYA + j % C::NA));  // this chain's last read of K(j)
-                    if (j + 1 < n) {
-                        ok = ok && mbar_wait(BAR(C::B_FULLB + (j + 1) % C::NB), ((j + 1) / C::NB) & 1, abort_flag,
+                    if (j + 2 < n) {
+                        ok = ok && mbar_wait(BAR(C::B_FULLB + (j + 2) % C::NB), ((j + 2) / C::NB) & 1, abort_flag,
                                              p.status, WB_FULL);
                         tc_fence_after();
-                        issue_dp(j + 1);  // overwrites dS(j): ordered after dQ(j); also releases V(j+1)
+                        issue_dp(j + 2);  // also releases V(j+2)
                     }
                 }
                 tc_commit_elect(BAR(C::B_ACC));
@@ -659,7 +674,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
         const int r = threadIdx.x % 128;
         const int row = q0 + r;
         const uint32_t lane_sel = (uint32_t)((warp % 4) * 32) << 16;
-        const uint32_t t_s = tmem + lane_sel + C::T_S, t_dp = tmem + lane_sel + C::T_DP;
+        const uint32_t t_s = tmem + lane_sel + C::T_S;
         const float c = p.scale_log2;
         const bool row_ok = row < p.lq;
         const float lse2 = row_ok ? p.lse[(size_t)bh * p.lq + row] * LOG2E_B : INFINITY;
@@ -691,7 +706,8 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
                 pv[2 * x + 1] = p1;
             }
             // ---- phase 2: dS = P * (dP - delta), bf16 into TMEM for dQ += dS K
-            ok = ok && mbar_wait(BAR(C::B_DP), j & 1, abort_flag, p.status, WB_DP);
+            const uint32_t t_dp = tmem + lane_sel + ((j & 1) ? C::T_ACC1 : C::T_DP);  // this tile's dP / dS buffer
+            ok = ok && mbar_wait(BAR((j & 1) ? C::B_DP1 : C::B_DP), (j >> 1) & 1, abort_flag, p.status, WB_DP);
             tc_fence_after();
             float dp[CPT];
             tmem_ld_cols<CPT>(t_dp + h * CPT, dp);
@@ -711,7 +727,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
                 tmem_st_x8(t_dp + h * (CPT / 2) + ch * 8, pk);
             }
             tmem_wait_st();
-            warp_arrive(BAR(C::B_DS), lane);
+            warp_arrive(BAR((j & 1) ? C::B_DS1 : C::B_DS), lane);
         }
         ok = ok && mbar_wait(BAR(C::B_ACC), 0, abort_flag, p.status, WB_ACC);
         tc_fence_after();
