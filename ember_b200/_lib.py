@@ -27,6 +27,9 @@ SIGNATURES = {
     "copy_to_device": (None, [_vp, _vp, _sz]),
     "copy_from_device": (None, [_vp, _vp, _sz]),
     "sync_device": (None, []),
+    "ember_alloc_async": (_vp, [_sz, _vp]),
+    "ember_free_async": (_i, [_vp, _vp]),
+    "ember_pool_stats": (_i, [ctypes.POINTER(_sz), ctypes.POINTER(_sz)]),
     "ember_set_device": (_i, [_i]),
     "ember_get_device": (_i, [ctypes.POINTER(_i)]),
     "ember_stream": (_vp, []),

@@ -163,41 +163,59 @@ int ember_attention_fwd_host(const void *q_host, const void *k_host, const void 
     const size_t set_bytes = align_up(per * q_unit, 256) * 2 + align_up(per * k_unit, 256) * 2 + align_up(per * l_unit, 256);
     char *stage = (char *)alloc_memory(2 * set_bytes);
     if (!stage) return EMBER_ERR_NOMEM;
+    // Any failure below goes through one exit that drains the three streams before the staging
+    // block is released, so that no queued copy or kernel still refers to it.
+    cudaError_t e = cudaSuccess;
+    const char *what = "";
+    rc = EMBER_OK;
+#define HOST_TRY(expr)                      \
+    do {                                    \
+        if ((e = (expr)) != cudaSuccess) {  \
+            what = #expr;                   \
+            goto done;                      \
+        }                                   \
+    } while (0)
     // the staging memory was allocated in the order of the compute stream: the copy stream waits for it
-    EMBER_CUDA_TRY(cudaEventRecord(st->compute_done[0], st->stream));
-    EMBER_CUDA_TRY(cudaEventRecord(st->compute_done[1], st->stream));
-    EMBER_CUDA_TRY(cudaEventRecord(st->out_done[0], st->copy_out));
-    EMBER_CUDA_TRY(cudaEventRecord(st->out_done[1], st->copy_out));
+    HOST_TRY(cudaEventRecord(st->compute_done[0], st->stream));
+    HOST_TRY(cudaEventRecord(st->compute_done[1], st->stream));
+    HOST_TRY(cudaEventRecord(st->out_done[0], st->copy_out));
+    HOST_TRY(cudaEventRecord(st->out_done[1], st->copy_out));
     for (int c = 0; c < chunks; c++) {
         const int b = c & 1, u0 = c * per, n = (u0 + per <= batch_heads) ? per : batch_heads - u0;
         char *dq = stage + b * set_bytes, *dk = dq + align_up(per * q_unit, 256), *dv = dk + align_up(per * k_unit, 256);
         char *dout = dv + align_up(per * k_unit, 256), *dl = dout + align_up(per * q_unit, 256);
         // inputs of this set may be overwritten once the kernel that last read them is done
-        EMBER_CUDA_TRY(cudaStreamWaitEvent(st->copy_in, st->compute_done[b], 0));
-        EMBER_CUDA_TRY(cudaMemcpyAsync(dq, (const char *)q_host + u0 * q_unit, n * q_unit, cudaMemcpyHostToDevice, st->copy_in));
-        EMBER_CUDA_TRY(cudaMemcpyAsync(dk, (const char *)k_host + u0 * k_unit, n * k_unit, cudaMemcpyHostToDevice, st->copy_in));
-        EMBER_CUDA_TRY(cudaMemcpyAsync(dv, (const char *)v_host + u0 * k_unit, n * k_unit, cudaMemcpyHostToDevice, st->copy_in));
-        EMBER_CUDA_TRY(cudaEventRecord(st->in_done[b], st->copy_in));
+        HOST_TRY(cudaStreamWaitEvent(st->copy_in, st->compute_done[b], 0));
+        HOST_TRY(cudaMemcpyAsync(dq, (const char *)q_host + u0 * q_unit, n * q_unit, cudaMemcpyHostToDevice, st->copy_in));
+        HOST_TRY(cudaMemcpyAsync(dk, (const char *)k_host + u0 * k_unit, n * k_unit, cudaMemcpyHostToDevice, st->copy_in));
+        HOST_TRY(cudaMemcpyAsync(dv, (const char *)v_host + u0 * k_unit, n * k_unit, cudaMemcpyHostToDevice, st->copy_in));
+        HOST_TRY(cudaEventRecord(st->in_done[b], st->copy_in));
         // the kernel needs its inputs, and its output buffer must have been copied out
-        EMBER_CUDA_TRY(cudaStreamWaitEvent(st->stream, st->in_done[b], 0));
-        EMBER_CUDA_TRY(cudaStreamWaitEvent(st->stream, st->out_done[b], 0));
-        if ((rc = ember_attention_fwd(dq, dk, dv, dout, (float *)dl, n, lq, lk, d, scale, causal, dtype, st->stream)) != EMBER_OK) {
-            cudaStreamSynchronize(st->copy_in);
-            cudaStreamSynchronize(st->copy_out);
-            free_memory(stage);
-            return rc;
-        }
-        EMBER_CUDA_TRY(cudaEventRecord(st->compute_done[b], st->stream));
-        EMBER_CUDA_TRY(cudaStreamWaitEvent(st->copy_out, st->compute_done[b], 0));
-        EMBER_CUDA_TRY(cudaMemcpyAsync((char *)out_host + u0 * q_unit, dout, n * q_unit, cudaMemcpyDeviceToHost, st->copy_out));
+        HOST_TRY(cudaStreamWaitEvent(st->stream, st->in_done[b], 0));
+        HOST_TRY(cudaStreamWaitEvent(st->stream, st->out_done[b], 0));
+        if ((rc = ember_attention_fwd(dq, dk, dv, dout, (float *)dl, n, lq, lk, d, scale, causal, dtype, st->stream)) != EMBER_OK)
+            goto done;
+        HOST_TRY(cudaEventRecord(st->compute_done[b], st->stream));
+        HOST_TRY(cudaStreamWaitEvent(st->copy_out, st->compute_done[b], 0));
+        HOST_TRY(cudaMemcpyAsync((char *)out_host + u0 * q_unit, dout, n * q_unit, cudaMemcpyDeviceToHost, st->copy_out));
         if (lse_host)
-            EMBER_CUDA_TRY(cudaMemcpyAsync((char *)lse_host + u0 * l_unit, dl, n * l_unit, cudaMemcpyDeviceToHost, st->copy_out));
-        EMBER_CUDA_TRY(cudaEventRecord(st->out_done[b], st->copy_out));
+            HOST_TRY(cudaMemcpyAsync((char *)lse_host + u0 * l_unit, dl, n * l_unit, cudaMemcpyDeviceToHost, st->copy_out));
+        HOST_TRY(cudaEventRecord(st->out_done[b], st->copy_out));
     }
-    EMBER_CUDA_TRY(cudaStreamSynchronize(st->copy_out));
-    EMBER_CUDA_TRY(cudaStreamSynchronize(st->copy_in));
-    // every user of the staging memory has finished; release it in the compute stream's order
-    free_memory(stage);
+done:
+#undef HOST_TRY
+    {
+        // every user of the staging memory must have finished before it goes back to the pool (in
+        // the compute stream's order); the first failure, if any, is the one reported
+        const cudaError_t s1 = cudaStreamSynchronize(st->copy_out), s2 = cudaStreamSynchronize(st->copy_in),
+                          s3 = cudaStreamSynchronize(st->stream);
+        free_memory(stage);
+        if (e != cudaSuccess) return cuda_fail(e, what);
+        if (rc != EMBER_OK) return rc;
+        if (s1 != cudaSuccess) return cuda_fail(s1, "cudaStreamSynchronize(copy_out)");
+        if (s2 != cudaSuccess) return cuda_fail(s2, "cudaStreamSynchronize(copy_in)");
+        if (s3 != cudaSuccess) return cuda_fail(s3, "cudaStreamSynchronize(stream)");
+    }
     return EMBER_OK;
 }
 

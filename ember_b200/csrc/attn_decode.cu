@@ -76,7 +76,8 @@ __device__ __forceinline__ void merge_state(float &m, float &l, float (&o)[N], f
     m = mn;
 }
 
-// grid = (splits, bh). LPK lanes share one key row; lanes whose column offset is >= d idle.
+// One-dimensional grid of bh * splits blocks (the splits of one row are neighbours). LPK lanes
+// share one key row; lanes whose column offset is >= d idle.
 template <typename T, int LPK>
 __global__ void __launch_bounds__(DEC_THREADS)
     decode_split_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *__restrict__ v,
@@ -86,8 +87,8 @@ __global__ void __launch_bounds__(DEC_THREADS)
 {
     constexpr int N = Vec<T>::N;
     constexpr int KPW = 32 / LPK;  // keys per warp-wide load
-    const int split = blockIdx.x;
-    const size_t bh = blockIdx.y;
+    const size_t bh = blockIdx.x / splits;
+    const int split = blockIdx.x - (unsigned)bh * splits;
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     const int g = lane / LPK;       // key slot inside the warp
     const int col = (lane % LPK) * N;  // first column this lane owns
@@ -249,7 +250,7 @@ __global__ void decode_combine_kernel(const float *__restrict__ ws_o, const floa
 template <typename T, int LPK>
 int launch_decode(const AttnArgs &a, int splits, int chunk, float *ws_o, float *ws_ml, cudaStream_t s)
 {
-    dim3 grid(splits, a.bh);
+    const unsigned grid = (unsigned)((long long)splits * a.bh);
     decode_split_kernel<T, LPK><<<grid, DEC_THREADS, 0, s>>>(
         (const T *)a.q, (const T *)a.k, (const T *)a.v, (T *)a.out, a.lse, ws_o, ws_ml, a.lk, a.d,
         chunk, splits, a.scale * LOG2E);
@@ -305,13 +306,13 @@ int decode_attention(const AttnArgs &a, int splits, void *workspace, DeviceState
         set_error("decode: head dimension %d must be a multiple of %d and at most %d", a.d, vec, 32 * vec);
         return EMBER_ERR_UNSUPPORTED;
     }
-    if (a.bh > 65535) {
-        set_error("decode: batch*heads %d exceeds 65535", a.bh);
-        return EMBER_ERR_UNSUPPORTED;
-    }
     int chunk = (a.lk + splits - 1) / splits;
     chunk = (chunk + 63) / 64 * 64;
     splits = (a.lk + chunk - 1) / chunk;  // drop empty trailing chunks; never exceeds the request
+    if ((long long)a.bh * splits > 0x7fffffffLL) {
+        set_error("decode: batch*heads %d times %d splits exceeds the grid limit", a.bh, splits);
+        return EMBER_ERR_UNSUPPORTED;
+    }
     float *ws_o = (float *)workspace;
     float *ws_ml = nullptr;
     if (splits > 1)

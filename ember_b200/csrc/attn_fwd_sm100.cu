@@ -125,9 +125,13 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
     lk = p.splits > 1 ? min(p.chunk, lk - k_row0) : lk;
     if (lk <= 0) {
         // An empty split (a sequence shorter than the others): its partial is "no weight". Every
-        // thread leaves here, before any barrier or tensor-memory allocation exists.
+        // thread leaves here, before any barrier or tensor-memory allocation exists. Without splits
+        // the (empty) sequence's result is defined as zeros with lse = -inf.
         if (p.lse && threadIdx.x < 256 && q_base + (int)threadIdx.x < p.lq)
             p.lse[(size_t)bh * p.lq + q_base + threadIdx.x] = -INFINITY;
+        if (p.splits == 1)
+            for (int i = threadIdx.x; i < 256 * HD; i += FWD_THREADS)
+                if (q_base + i / HD < p.lq) p.out[((size_t)bh * p.lq + q_base) * HD + i] = __float2bfloat16_rn(0.f);
         return;
     }
     const int off = lk - p.lq;
@@ -278,6 +282,21 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
                     tc_commit_elect(BAR(B_KEMPTY + (j + 1) % C::KSTAGES));  // our reads of K(j+1) are issued
                 }
                 ok = ok && mbar_wait(BAR(B_VFULL + j % C::VSTAGES), (j / C::VSTAGES) & 1, abort_flag, p.status, W_MMA_V);
+                if (p.seq_lens && j < nt && j * 128 + 128 > lk) {
+                    // Cache decode with a per-sequence length below the tensor map's extent: TMA only
+                    // zero-fills rows past the MAP's end, so V rows [lk, ...) of this tile hold whatever
+                    // the cache holds there, and 0 * Inf (or NaN) would poison the product although
+                    // their probabilities are exactly zero. Zero those rows in shared memory (a row is
+                    // 128 bytes of each 64-column sub-tile; the swizzle only permutes inside a row).
+                    uint8_t *vt = smem_gen + C::OFF_V + (j % C::VSTAGES) * C::TILE_BYTES;
+                    const int r0 = lk - j * 128;
+                    for (int i = lane; i < (128 - r0) * C::NSUB * 8; i += 32) {
+                        const int rr = r0 + i / (C::NSUB * 8), sub = (i / 8) % C::NSUB, ch = i % 8;
+                        *reinterpret_cast<uint4 *>(vt + sub * C::SUB_BYTES + rr * 128 + ch * 16) = make_uint4(0, 0, 0, 0);
+                    }
+                    fence_proxy_async();
+                    __syncwarp();
+                }
                 if (j < nt) {
                     issue_pv_half(j, 0);
                     issue_pv_half(j, 1);
@@ -515,6 +534,7 @@ __global__ void split_merge_kernel(const __nv_bfloat16 *__restrict__ o_part, con
         const float ls = lse_part[(unit * splits + s) * rows_per_unit + row];
         if (ls != -INFINITY) wsum += expf(ls - mx);
     }
+    const float inv = wsum > 0.f ? 1.f / wsum : 0.f;  // every split empty: zeros and lse = -inf
     for (int c = threadIdx.x; c < d; c += blockDim.x) {
         float acc = 0.f;
         for (int s = 0; s < splits; s++) {
@@ -522,9 +542,9 @@ __global__ void split_merge_kernel(const __nv_bfloat16 *__restrict__ o_part, con
             if (ls != -INFINITY)
                 acc += expf(ls - mx) * __bfloat162float(o_part[((unit * splits + s) * rows_per_unit + row) * (size_t)d + c]);
         }
-        out[((size_t)unit * rows_per_unit + row) * d + c] = __float2bfloat16_rn(acc / wsum);
+        out[((size_t)unit * rows_per_unit + row) * d + c] = __float2bfloat16_rn(acc * inv);
     }
-    if (lse && threadIdx.x == 0) lse[unit * rows_per_unit + row] = mx + logf(wsum);
+    if (lse && threadIdx.x == 0) lse[unit * rows_per_unit + row] = wsum > 0.f ? mx + logf(wsum) : -INFINITY;
 }
 
 template <int HD>

@@ -124,10 +124,54 @@ void copy_to_device(void *dst_device, const void *src_host, size_t bytes)
     DeviceState *st = device_state();
     if (!st) return;
     cudaError_t e = cudaMemcpyAsync(dst_device, src_host, bytes, cudaMemcpyHostToDevice, st->stream);
-    // Pageable sources are staged before the call returns; pinned ones are not, so wait: the
-    // reference's copy is synchronous (src/core/memory_gpu.cu:32) and callers may reuse src.
-    if (e == cudaSuccess) e = cudaStreamSynchronize(st->stream);
+    // The reference's copy is synchronous (src/core/memory_gpu.cu:32) and callers may reuse src as
+    // soon as the call returns. A pageable source has been staged by then, so nothing more is
+    // needed and uploads of several tensors queue up behind one another; a pinned (or managed)
+    // source is read by the DMA engine later, so wait for it.
+    if (e == cudaSuccess) {
+        cudaPointerAttributes attr;
+        const bool pageable = cudaPointerGetAttributes(&attr, src_host) == cudaSuccess && attr.type == cudaMemoryTypeUnregistered;
+        cudaGetLastError();  // older runtimes report an error for plain host pointers
+        if (!pageable) e = cudaStreamSynchronize(st->stream);
+    }
     if (e != cudaSuccess) cuda_fail(e, "copy_to_device");
+}
+
+void *ember_alloc_async(size_t bytes, void *stream)
+{
+    DeviceState *st = device_state();
+    if (!st) return nullptr;
+    void *p = nullptr;
+    cudaError_t e = cudaMallocAsync(&p, bytes ? bytes : 1, pick_stream(stream, st));
+    if (e != cudaSuccess) {
+        cuda_fail(e, "cudaMallocAsync");
+        cudaGetLastError();
+        return nullptr;
+    }
+    return p;
+}
+
+int ember_free_async(void *ptr, void *stream)
+{
+    if (!ptr) return EMBER_OK;
+    DeviceState *st = device_state();
+    if (!st) return EMBER_ERR_CUDA;
+    EMBER_CUDA_TRY(cudaFreeAsync(ptr, pick_stream(stream, st)));
+    return EMBER_OK;
+}
+
+int ember_pool_stats(size_t *reserved_bytes, size_t *used_bytes)
+{
+    int dev = 0;
+    EMBER_CUDA_TRY(cudaGetDevice(&dev));
+    cudaMemPool_t pool;
+    EMBER_CUDA_TRY(cudaDeviceGetDefaultMemPool(&pool, dev));
+    uint64_t r = 0, u = 0;
+    EMBER_CUDA_TRY(cudaMemPoolGetAttribute(pool, cudaMemPoolAttrReservedMemCurrent, &r));
+    EMBER_CUDA_TRY(cudaMemPoolGetAttribute(pool, cudaMemPoolAttrUsedMemCurrent, &u));
+    if (reserved_bytes) *reserved_bytes = (size_t)r;
+    if (used_bytes) *used_bytes = (size_t)u;
+    return EMBER_OK;
 }
 
 void copy_from_device(void *dst_host, const void *src_device, size_t bytes)

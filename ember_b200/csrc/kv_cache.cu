@@ -103,7 +103,8 @@ __device__ __forceinline__ void merge(float &m, float &l, float (&o)[N], float m
     m = mn;
 }
 
-// grid = (splits, batch * kv_heads). G query heads per K/V head; LPK lanes share one key row.
+// One-dimensional grid of splits * batch * kv_heads blocks (the splits of one K/V head are
+// neighbours). G query heads per K/V head; LPK lanes share one key row.
 template <typename T, int LPK, int G>
 __global__ void __launch_bounds__(KV_THREADS)
     decode_gqa_kernel(const T *__restrict__ q, const T *__restrict__ kc, const T *__restrict__ vc, T *__restrict__ out,
@@ -113,8 +114,8 @@ __global__ void __launch_bounds__(KV_THREADS)
     constexpr int N = V16<T>::N;
     constexpr int KPW = 32 / LPK;              // keys per warp-wide load
     constexpr int UNROLL = G <= 2 ? 4 : 2;     // loads of K and of V in flight per warp
-    const int split = blockIdx.x;
-    const int b = blockIdx.y / g.kv_heads, hkv = blockIdx.y - b * g.kv_heads;
+    const int unit = blockIdx.x / splits, split = blockIdx.x - unit * splits;
+    const int b = unit / g.kv_heads, hkv = unit - b * g.kv_heads;
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     const int slot = lane / LPK;               // key slot inside the warp
     const int col = (lane % LPK) * N;          // first column this lane owns
@@ -233,7 +234,7 @@ __global__ void __launch_bounds__(KV_THREADS)
             }
             const size_t row = (size_t)b * q_heads + hkv * G + h;  // which (batch, query head)
             if (splits == 1) {
-                const float inv = 1.f / ll;
+                const float inv = ll > 0.f ? 1.f / ll : 0.f;  // an empty sequence gives zeros and lse = -inf
                 if (col_ok) {
 #pragma unroll
                     for (int i = 0; i < N; i++) {
@@ -243,7 +244,7 @@ __global__ void __launch_bounds__(KV_THREADS)
                             out[row * g.d + col + i] = __float2bfloat16_rn(oo[i] * inv);
                     }
                 }
-                if (lse && lane == 0) lse[row] = (mm + log2f(ll)) * LN2_KV;
+                if (lse && lane == 0) lse[row] = ll > 0.f ? (mm + log2f(ll)) * LN2_KV : -INFINITY;
             } else {
                 float *po = ws_o + (row * splits + split) * (size_t)g.d;
                 if (col_ok) {
@@ -273,7 +274,7 @@ __global__ void gqa_combine_kernel(const float *__restrict__ ws_o, const float *
         const float ms = ml[2 * s];
         if (ms != -INFINITY) l += ml[2 * s + 1] * exp2f(ms - mx);
     }
-    const float inv = 1.f / l;
+    const float inv = l > 0.f ? 1.f / l : 0.f;  // no split saw a key: zeros and lse = -inf
     for (int c = threadIdx.x; c < d; c += blockDim.x) {
         float acc = 0.f;
         for (int s = 0; s < splits; s++) {
@@ -285,7 +286,7 @@ __global__ void gqa_combine_kernel(const float *__restrict__ ws_o, const float *
         else
             out[row * d + c] = __float2bfloat16_rn(acc * inv);
     }
-    if (lse && threadIdx.x == 0) lse[row] = (mx + log2f(l)) * LN2_KV;
+    if (lse && threadIdx.x == 0) lse[row] = l > 0.f ? (mx + log2f(l)) * LN2_KV : -INFINITY;
 }
 
 // Copies n_new rows per (batch, kv_head) from (batch, kv_heads, n_new, d) into the cache at
@@ -347,7 +348,7 @@ CacheGeom make_geom(const GqaArgs &a)
 template <typename T, int LPK, int G>
 int launch_gqa(const GqaArgs &a, int splits, int chunk, float *ws_o, float *ws_ml, cudaStream_t s)
 {
-    dim3 grid(splits, a.batch * a.kv_heads);
+    const unsigned grid = (unsigned)((long long)splits * a.batch * a.kv_heads);
     decode_gqa_kernel<T, LPK, G><<<grid, KV_THREADS, 0, s>>>((const T *)a.q, (const T *)a.kc, (const T *)a.vc, (T *)a.out,
                                                             a.lse, ws_o, ws_ml, make_geom(a), chunk, splits,
                                                             a.scale * LOG2E_KV);
@@ -427,8 +428,10 @@ int check_cache(const char *fn, int batch, int q_heads, int kv_heads, int lk, in
     } else {
         EMBER_REQUIRE(capacity > 0 && lk <= capacity, "%s: lk=%d exceeds the cache capacity %d", fn, lk, capacity);
     }
-    if ((long long)batch * kv_heads > 65535) {
-        set_error("%s: batch*kv_heads=%lld exceeds 65535", fn, (long long)batch * kv_heads);
+    // the decode grid is one-dimensional: splits (at most 256 by the library's choice, at most lk
+    // by request) times batch * kv_heads blocks
+    if ((long long)batch * kv_heads > (0x7fffffffLL >> 8)) {
+        set_error("%s: batch*kv_heads=%lld exceeds %lld", fn, (long long)batch * kv_heads, 0x7fffffffLL >> 8);
         return EMBER_ERR_UNSUPPORTED;
     }
     return EMBER_OK;
@@ -546,6 +549,11 @@ int ember_attention_decode_cache(const void *q, const void *k_cache, const void 
     int chunk = (lk + splits - 1) / splits;
     chunk = (chunk + 63) / 64 * 64;
     const int used = (lk + chunk - 1) / chunk;  // drop empty trailing chunks
+    if ((long long)used * batch * kv_heads > 0x7fffffffLL) {
+        set_error("ember_attention_decode_cache: %d splits of %d (batch, K/V head) pairs exceed the grid limit", used,
+                  batch * kv_heads);
+        return EMBER_ERR_UNSUPPORTED;
+    }
     // The partial layout follows the split count the workspace was sized for only when it is used
     // as is; recompute the second block's offset from the splits actually launched.
     float *ws_o = (float *)workspace;

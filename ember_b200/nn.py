@@ -8,6 +8,7 @@ the projections, so that no transpose runs in between.
 """
 from __future__ import annotations
 
+import abc
 import math
 
 import numpy as np
@@ -15,7 +16,69 @@ import numpy as np
 from .tensor import Tensor, attention_backward, attention_forward, linear_backward, linear_forward
 
 
-class Attention:
+class Layer(abc.ABC):
+    """The reference's layer contract (ember/nn/base.py:7-35): calling a layer runs ``forward`` and
+    remembers the input and the output (``x``, ``y``) for the explicit ``backward``; ``training``
+    defaults to True as it does there (base.py:11). Subclasses give ``forward``, ``backward``,
+    ``parameters``, ``gradients`` and ``reset``."""
+
+    x = None
+    y = None
+
+    def __call__(self, x, training: bool = True):
+        self._training = training
+        self.x = x
+        self.y = self.forward(x, training)
+        return self.y
+
+    @abc.abstractmethod
+    def forward(self, x, training: bool = True): ...
+
+    @abc.abstractmethod
+    def backward(self, grad_y): ...
+
+    @abc.abstractmethod
+    def parameters(self) -> list: ...
+
+    @abc.abstractmethod
+    def gradients(self) -> list: ...
+
+    @abc.abstractmethod
+    def reset(self) -> None: ...
+
+
+class Sequential(Layer):
+    """Layers applied one after the other, gradients walked back in reverse (the reference's
+    container of the same name, ember/nn/base.py:50-75). ``Linear`` and ``MultiHeadAttention`` map
+    one tensor to one tensor and compose here; ``Attention`` maps a (q, k, v) triple to one tensor and
+    returns a triple from ``backward``, so it can only stand first."""
+
+    def __init__(self, *layers: Layer):
+        self.layers = tuple(layers)
+
+    def forward(self, x, training: bool = True):
+        for layer in self.layers:
+            x = layer(x, training)
+        return x
+
+    def backward(self, grad_y):
+        for layer in self.layers[::-1]:
+            grad_y = layer.backward(grad_y)
+        return grad_y
+
+    def parameters(self) -> list:
+        return [p for layer in self.layers for p in layer.parameters()]
+
+    def gradients(self) -> list:
+        return [g for layer in self.layers for g in layer.gradients()]
+
+    def reset(self) -> None:
+        self.x = self.y = None
+        for layer in self.layers:
+            layer.reset()
+
+
+class Attention(Layer):
     """Scaled-dot-product attention over a ``(q, k, v)`` triple of (B, H, L, D) tensors."""
 
     def __init__(self, causal: bool = False, scale: float | None = None):
@@ -25,12 +88,7 @@ class Attention:
         self.y = None
         self._lse = None
 
-    def __call__(self, x, training: bool = False) -> Tensor:
-        self.x = x
-        self.y = self.forward(x, training)
-        return self.y
-
-    def forward(self, x, training: bool = False) -> Tensor:
+    def forward(self, x, training: bool = True) -> Tensor:
         q, k, v = x
         out, lse = attention_forward(q, k, v, self.scale, self.causal)
         self._lse = lse
@@ -53,7 +111,7 @@ class Attention:
         self.x = self.y = self._lse = None
 
 
-class Linear:
+class Linear(Layer):
     """``y = b + x @ w`` with w of shape (in_features, out_features), as the reference's Linear
     (ember/nn/layers.py:9-56). Weights start uniform in +-1/sqrt(in_features) and the bias at zero
     (layers.py:26-33); ``seed`` makes that reproducible."""
@@ -76,11 +134,6 @@ class Linear:
     def gradients(self):
         return [self.grad_w, self.grad_b]
 
-    def __call__(self, x: Tensor, training: bool = True) -> Tensor:
-        self.x = x
-        self.y = self.forward(x, training)
-        return self.y
-
     def forward(self, x: Tensor, training: bool = True) -> Tensor:
         self.x = x
         self.y = linear_forward(x, self.w, self.b)
@@ -92,7 +145,7 @@ class Linear:
         return grad_x
 
 
-class MultiHeadAttention:
+class MultiHeadAttention(Layer):
     """Self-attention block over x of shape (B, L, E): q, k, v = split(x @ w_qkv + b_qkv) per head,
     attention, then the output projection. Parameters: w_qkv (E, 3E), b_qkv (3E), w_o (E, E), b_o (E).
     The q/k/v projection writes (3, B, H, L, D) and the output projection reads attention's
@@ -127,11 +180,6 @@ class MultiHeadAttention:
         _, B, H, L, D = qkv.shape
         n = B * H * L * D
         return tuple(qkv.view(i * n, (B, H, L, D)) for i in range(3))
-
-    def __call__(self, x: Tensor, training: bool = True) -> Tensor:
-        self.x = x
-        self.y = self.forward(x, training)
-        return self.y
 
     def forward(self, x: Tensor, training: bool = True) -> Tensor:
         if len(x.shape) != 3 or x.shape[-1] != self.embed_dim:

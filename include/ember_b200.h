@@ -69,6 +69,20 @@ EMBER_API void copy_to_device(void *dst_device, const void *src_host, size_t byt
 EMBER_API void copy_from_device(void *dst_host, const void *src_device, size_t bytes);
 EMBER_API void sync_device(void);
 
+/* ---- the same allocator in the order of a stream of the caller's choice (no counterpart in the
+ *      reference, whose cudaMalloc/cudaFree per tensor synchronise the device:
+ *      src/core/memory_gpu.cu:10-28, TODO.md:12). free_memory releases a block in the order of
+ *      the LIBRARY stream: a block that a kernel on another stream may still be using must either
+ *      be released with ember_free_async on that stream, or only after that stream has been
+ *      synchronised; otherwise the pool may hand the block to the next allocation while the kernel
+ *      still runs. stream NULL = the library stream. ember_alloc_async returns NULL on failure
+ *      (text in ember_last_error()). Freed blocks stay in the device's pool (release threshold
+ *      unlimited) and are reused without a new driver allocation; ember_pool_stats reports what the
+ *      pool currently holds from the driver (reserved) and has handed out (used). ---- */
+EMBER_API void *ember_alloc_async(size_t bytes, void *stream);
+EMBER_API int ember_free_async(void *ptr, void *stream);
+EMBER_API int ember_pool_stats(size_t *reserved_bytes, size_t *used_bytes);
+
 /* ---- additions the attention path needs from src/core (no counterpart in the
  *      reference, which is single-device, default-stream, float32-only) ---- */
 EMBER_API int ember_set_device(int device);

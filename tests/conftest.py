@@ -74,3 +74,24 @@ def golden_inputs(meta, with_dout=False):
 def seeded(shape, seed, scale=1.0):
     rng = np.random.default_rng(seed)
     return (rng.standard_normal(shape, dtype=np.float32) * np.float32(scale)).astype(np.float32)
+
+
+class Guarded:
+    """A device buffer with a poisoned band on each side, standing in for a memory checker: the
+    kernels under test write into ``.t`` (a torch tensor view in the middle of a larger byte
+    buffer whose first and last ``band`` bytes hold 0x7F) and ``check()`` asserts afterwards that no
+    byte of either band changed, i.e. that nothing was written outside the tensor."""
+
+    def __init__(self, torch, shape, dtype, device, band=32 * 1024):
+        n = 1
+        for s in shape:
+            n *= int(s)
+        es = torch.empty((), dtype=dtype).element_size()
+        self.band = band
+        self.raw = torch.full((2 * band + n * es,), 0x7F, dtype=torch.uint8, device=device)
+        self.t = self.raw[band:band + n * es].view(dtype).view(*shape)
+        self._torch = torch
+
+    def check(self, name=""):
+        lo, hi = self.raw[:self.band], self.raw[-self.band:]
+        assert bool((lo == 0x7F).all()) and bool((hi == 0x7F).all()), f"write outside the tensor {name}"

@@ -26,8 +26,11 @@ import tempfile
 
 import numpy as np
 
-REF = os.environ.get("EMBER_REFERENCE", "/root/reference")
 HERE = os.path.dirname(os.path.abspath(__file__))
+# the reference checkout: $EMBER_REFERENCE, else a folder named "reference" beside this repository
+REF = os.environ.get("EMBER_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(HERE))), "reference")
+if not os.path.isdir(os.path.join(REF, "ember")):
+    raise SystemExit("make_golden.py: set EMBER_REFERENCE to a checkout of the reference project")
 sys.path.insert(0, HERE)
 from inputs import normal  # noqa: E402
 

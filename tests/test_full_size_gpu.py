@@ -104,6 +104,20 @@ def test_c3_causal_backward_full_size(env):
     for g, r, name in zip(grads, refs, ("dq", "dk", "dv")):
         err = (g.float() - r).abs().max().item()
         assert err <= 2e-2 * r.abs().max().item(), (name, err)
+    # The last (batch, head) slice against the CPU oracle, on the rows the oracle can afford: the last
+    # 512 query rows see every key, and under the causal mask the last 512 keys are seen by those
+    # rows only. The oracle run on (those 512 queries, all 8192 keys) with the bottom-right aligned
+    # mask therefore gives dQ of those rows and dK/dV of the last 512 keys of the full problem exactly
+    # (about 5 Gflop on the host instead of 86 for the whole slice). The first 512 rows/keys likewise
+    # give dQ[:512] from the oracle on the (512 x 512) top-left problem.
+    R = 512
+    qs, ks, vs, gs = (t[-1, -1].float().cpu().numpy() for t in (q, k, v, do))
+    rdq, rdk, rdv = cpu_oracle.attention_bwd(qs[-R:], ks, vs, gs[-R:], None, True)
+    got = [g[-1, -1].float().cpu().numpy() for g in grads]
+    for name, a, b in (("dq", got[0][-R:], rdq), ("dk", got[1][-R:], rdk[-R:]), ("dv", got[2][-R:], rdv[-R:])):
+        assert np.abs(a - b).max() <= 2e-2 * np.abs(b).max(), (name, np.abs(a - b).max(), np.abs(b).max())
+    rdq0, _, _ = cpu_oracle.attention_bwd(qs[:R], ks[:R], vs[:R], gs[:R], None, True)
+    assert np.abs(got[0][:R] - rdq0).max() <= 2e-2 * np.abs(rdq0).max()
     # linearity in dO: doubling the upstream gradient doubles every gradient bit for bit (scaling by
     # 2 is exact in every step), except where the value is a float32 denormal (around 1e-38: the first
     # causal rows, whose dS cancels to almost nothing)
@@ -112,6 +126,38 @@ def test_c3_causal_backward_full_size(env):
         a2 = _bf16(a.float() * 2)
         differs = a2 != b
         assert (b.float().abs()[differs] < 1e-30).all()
+
+
+def test_c5_long_sequence_units(env):
+    """The multi-GPU sweep's longest shape (H=64 heads of D=128 at L=16384, bf16, causal), on three
+    of its 128 (batch*head) units: forward and backward of the tcgen05 kernels against the
+    float32-arithmetic kernels on all three (the first shape with more than 2^28 score elements per
+    unit), and against the CPU oracle on the last 256 query rows / keys of the last unit."""
+    L, dev, sp = env
+    BH, S, D = 3, 16384, 128
+    q, k, v = (_rand((1, BH, S, D), s, 0.5, dev) for s in (21, 22, 23))
+    do = _rand((1, BH, S, D), 24, 1.0, dev)
+    o, lse = _fwd(L, sp, q, k, v, True, _lib.EMBER_BF16)
+    grads = _bwd(L, sp, q, k, v, o, lse, do, True, _lib.EMBER_BF16)
+    qf, kf, vf, dof = q.float(), k.float(), v.float(), do.float()
+    of, lsef = _fwd(L, sp, qf, kf, vf, True, _lib.EMBER_F32)
+    refs = _bwd(L, sp, qf, kf, vf, of, lsef, dof, True, _lib.EMBER_F32)
+    torch.cuda.synchronize()
+    _no_fault(L, sp)
+    assert (o.float() - of).abs().max().item() <= 2e-2
+    assert (lse - lsef).abs().max().item() <= 2e-2
+    for g, r, name in zip(grads, refs, ("dq", "dk", "dv")):
+        err = (g.float() - r).abs().max().item()
+        assert err <= 2e-2 * r.abs().max().item(), (name, err)
+    R = 256
+    qs, ks, vs, gs = (t[0, -1].float().cpu().numpy() for t in (q, k, v, do))
+    ro, rl = cpu_oracle.attention_fwd(qs[-R:], ks, vs, None, True)
+    assert np.abs(o[0, -1, -R:].float().cpu().numpy() - ro).max() <= 2e-2
+    assert np.abs(lse[0, -1, -R:].cpu().numpy() - rl).max() <= 2e-2
+    rdq, rdk, rdv = cpu_oracle.attention_bwd(qs[-R:], ks, vs, gs[-R:], None, True)
+    got = [g[0, -1].float().cpu().numpy() for g in grads]
+    for name, a, b in (("dq", got[0][-R:], rdq), ("dk", got[1][-R:], rdk[-R:]), ("dv", got[2][-R:], rdv[-R:])):
+        assert np.abs(a - b).max() <= 2e-2 * np.abs(b).max(), (name, np.abs(a - b).max(), np.abs(b).max())
 
 
 def test_c4_decode_full_size(env):

@@ -194,3 +194,77 @@ def test_unsupported_group_is_reported(env):
     with pytest.raises(ValueError):
         _lib.check(L.ember_attention_decode_cache(t.data_ptr(), t.data_ptr(), t.data_ptr(), t.data_ptr(), None, 1, 3, 2, 8, 8, 8,
                                                   1.0, _lib.EMBER_F32, None, None, 0, 0, 1, None, 0, sp))
+
+
+@pytest.mark.parametrize("cfg", [
+    # B, Hq, Hkv, capacity, D, splits: grouped heads (tensor-core path for bf16) and one head per K/V head
+    (2, 8, 2, 700, 128, 0),
+    (2, 8, 2, 700, 128, 3),
+    (3, 4, 4, 520, 64, 2),
+])
+def test_cache_rows_past_the_sequence_length_are_never_used(env, cfg):
+    """The rows of a cache beyond seq_lens[b] were never written by the caller and may hold anything.
+    Here they hold bf16 NaN and Inf bit patterns (written by the host; nothing faults): the result
+    must be finite and equal to the oracle's on the filled part, on both kernel families."""
+    L, dev, sp = env
+    B, Hq, Hkv, cap, D, splits = cfg
+    rng = np.random.default_rng(17 + cap + Hq)
+    q = _round(rng.standard_normal((B, Hq, D), dtype=np.float32) * 0.5, True)
+    k = _round(rng.standard_normal((B, Hkv, cap, D), dtype=np.float32) * 0.5, True)
+    v = _round(rng.standard_normal((B, Hkv, cap, D), dtype=np.float32) * 0.5, True)
+    lens = np.array([cap - 150 * b - 61 for b in range(B)], np.int32)   # none a multiple of 128
+    tq, tk, tv = _t(q, dev, True), _t(k, dev, True), _t(v, dev, True)
+    for b in range(B):
+        n = int(lens[b])
+        tk[b, :, n:] = float("nan")
+        tv[b, :, n::2] = float("inf")
+        tv[b, :, n + 1::2] = float("nan")
+    tl = torch.from_numpy(lens).to(dev)
+    ro, rl = _oracle(q, k, v, lens, Hq // Hkv)
+    o, l = _decode(L, sp, dev, tq, tk, tv, B, Hq, Hkv, cap, cap, D, True, lens=tl, splits=splits)
+    assert np.isfinite(o).all() and np.isfinite(l).all()
+    assert np.abs(o - ro).max() <= 2e-2 and np.abs(l - rl).max() <= 2e-2
+
+
+@pytest.mark.parametrize("cfg", [(2, 8, 2, 400, 128, 0), (2, 8, 2, 400, 128, 2), (2, 4, 4, 400, 64, 0), (2, 4, 4, 400, 64, 3)])
+def test_an_empty_sequence_gives_zeros_and_minus_infinity(env, cfg):
+    """seq_lens[b] == 0: that sequence's output rows are zeros and its lse is -inf; the others are
+    unaffected."""
+    L, dev, sp = env
+    B, Hq, Hkv, cap, D, splits = cfg
+    rng = np.random.default_rng(5)
+    q = _round(rng.standard_normal((B, Hq, D), dtype=np.float32) * 0.5, True)
+    k = _round(rng.standard_normal((B, Hkv, cap, D), dtype=np.float32) * 0.5, True)
+    v = _round(rng.standard_normal((B, Hkv, cap, D), dtype=np.float32) * 0.5, True)
+    lens = np.array([0, cap - 7], np.int32)
+    tl = torch.from_numpy(lens).to(dev)
+    o, l = _decode(L, sp, dev, _t(q, dev, True), _t(k, dev, True), _t(v, dev, True), B, Hq, Hkv, cap, cap, D, True, lens=tl,
+                   splits=splits)
+    assert (o[0] == 0).all() and np.isneginf(l[0]).all()
+    ro, rl = _oracle(q[1:], k[1:], v[1:], lens[1:], Hq // Hkv)
+    assert np.abs(o[1:] - ro).max() <= 2e-2 and np.abs(l[1:] - rl).max() <= 2e-2
+
+
+def test_decode_with_more_than_65535_batch_heads(env):
+    """batch*heads = 70 000 rows (a grid dimension of its own would stop at 65 535): sampled rows
+    against the oracle, all rows finite."""
+    L, dev, sp = env
+    BH, Lk, D = 70000, 512, 64
+    g = torch.Generator(device=dev).manual_seed(9)
+    q = (torch.randn((BH, 1, D), generator=g, device=dev) * 0.5).to(torch.bfloat16)
+    k = (torch.randn((BH, Lk, D), generator=g, device=dev) * 0.5).to(torch.bfloat16)
+    v = (torch.randn((BH, Lk, D), generator=g, device=dev) * 0.5).to(torch.bfloat16)
+    for splits in (1, 2):
+        o = torch.empty_like(q)
+        lse = torch.empty((BH,), device=dev, dtype=torch.float32)
+        n = L.ember_attention_workspace_bytes(_lib.EMBER_OP_DECODE, BH, 1, Lk, D, 1, splits)
+        ws = torch.empty(max(n, 256), device=dev, dtype=torch.uint8)
+        _lib.check(L.ember_attention_decode(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), BH, Lk, D,
+                                            1.0 / math.sqrt(D), 1, splits, ws.data_ptr(), n, sp))
+        torch.cuda.synchronize()
+        assert torch.isfinite(o.float()).all() and torch.isfinite(lse).all()
+        for r in (0, 65535, 65536, 69999):
+            ro, rl = cpu_oracle.attention_fwd(q[r].float().cpu().numpy(), k[r].float().cpu().numpy(), v[r].float().cpu().numpy(),
+                                              None, False)
+            assert np.abs(o[r].float().cpu().numpy() - ro).max() <= 2e-2
+            assert abs(float(lse[r]) - float(rl[0])) <= 2e-2

@@ -91,3 +91,36 @@ def test_multi_head_attention_matches_composed_oracle(em, cfg):
     for name, g, r in zip(("y", "grad_x", "grad_w_qkv", "grad_b_qkv", "grad_w_o", "grad_b_o"), got, ref):
         assert g.shape == r.shape, name
         assert _rel(g.to_np(), r) <= tol, (name, _rel(g.to_np(), r))
+
+
+def test_layers_subclass_layer_and_compose_in_sequential(em):
+    """Linear and MultiHeadAttention are ``Layer`` subclasses (single tensor in, single tensor out)
+    and compose in ``Sequential`` the way the reference's layers do (ember/nn/base.py:50-75):
+    forward in order, backward in reverse, parameters and gradients concatenated; ``training``
+    defaults to True as in the reference's ``Layer.__call__``."""
+    nn = em.nn
+    E, H, B, L = 64, 2, 2, 32
+    lin1, mha, lin2 = nn.Linear(E, E, seed=1), nn.MultiHeadAttention(E, H, causal=True, seed=2), nn.Linear(E, 24, seed=3)
+    net = nn.Sequential(lin1, mha, lin2)
+    for layer in (lin1, mha, lin2, net, nn.Attention()):
+        assert isinstance(layer, nn.Layer)
+    rng = np.random.default_rng(4)
+    x, g = rng.standard_normal((B, L, E), dtype=np.float32), rng.standard_normal((B, L, 24), dtype=np.float32)
+    y = net(em.Tensor(x))
+    assert net._training is True and lin1._training is True
+    # the same three steps by hand
+    h1 = lin1.forward(em.Tensor(x))
+    h2 = mha.forward(h1)
+    y2 = lin2.forward(h2)
+    assert np.array_equal(y.to_np(), y2.to_np())
+    gx = net.backward(em.Tensor(g))
+    gx2 = lin1.backward(mha.backward(lin2.backward(em.Tensor(g))))
+    assert np.array_equal(gx.to_np(), gx2.to_np())
+    assert len(net.parameters()) == 2 + 4 + 2 and len(net.gradients()) == 8
+    assert all(t is not None for t in net.gradients())
+    net.reset()
+    assert net.x is None and lin1.x is None and mha.x is None
+    att = nn.Attention(causal=True)
+    q = em.Tensor(rng.standard_normal((1, 2, 16, 32), dtype=np.float32))
+    att((q, q, q))
+    assert att._training is True
