@@ -41,6 +41,8 @@ SIGNATURES = {
     "ember_selftest_wait_timeout": (_i, [_vp]),
     "ember_attention_fwd": (_i, [_vp] * 5 + [_i] * 4 + [_f, _i, _i, _vp]),
     "ember_attention_bwd": (_i, [_vp] * 9 + [_i] * 4 + [_f, _i, _i, _vp, _sz, _vp]),
+    "ember_set_deterministic": (_i, [_i]),
+    "ember_get_deterministic": (_i, []),
     "ember_attention_decode": (_i, [_vp] * 5 + [_i] * 3 + [_f, _i, _i, _vp, _sz, _vp]),
     "ember_attention_decode_static": (_i, [_vp] * 5 + [_i] * 3 + [_f, _i, _i, _vp]),
     "ember_attention_decode_static_capacity": (_sz, []),

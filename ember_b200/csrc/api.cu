@@ -2,6 +2,7 @@
 // reference's binding (shape mismatches are the caller's ValueError), then dispatch to the
 // tcgen05 kernels (bf16, head dimension 64 or 128) or the CUDA-core kernels (everything else).
 #include <math.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 #include "kernels.cuh"
@@ -21,7 +22,28 @@ int check_common(const char *fn, int bh, int lq, int lk, int d, int dtype, float
 
 bool aligned(const void *p, size_t a) { return ((uintptr_t)p & (a - 1)) == 0; }
 
-size_t bwd_workspace_bytes(int bh, int lq) { return align_up((size_t)bh * lq * sizeof(float), 256); }
+size_t delta_bytes(int bh, int lq) { return align_up((size_t)bh * lq * sizeof(float), 256); }
+
+// -1: not read yet; the environment variable EMBER_DETERMINISTIC=1 sets the initial value
+int g_deterministic = -1;
+bool deterministic_mode()
+{
+    if (g_deterministic < 0) {
+        const char *e = getenv("EMBER_DETERMINISTIC");
+        g_deterministic = (e && e[0] && e[0] != '0') ? 1 : 0;
+    }
+    return g_deterministic != 0;
+}
+
+bool tensor_core_shape(int d, int dtype) { return dtype == EMBER_BF16 && (d == 64 || d == 128); }
+
+// delta vector, then (single-pass tensor-core backward only) the float32 dQ accumulator
+size_t bwd_workspace_bytes(int bh, int lq, int d, int dtype)
+{
+    size_t n = delta_bytes(bh, lq);
+    if (tensor_core_shape(d, dtype) && !deterministic_mode()) n += align_up(sm100_bwd_accumulator_bytes(bh, lq, d), 256);
+    return n;
+}
 
 }  // namespace
 
@@ -59,7 +81,7 @@ int ember_attention_bwd(const void *q, const void *k, const void *v, const void 
     EMBER_REQUIRE(q && k && v && out && lse && dout && dq && dk && dv, "ember_attention_bwd: NULL tensor pointer");
     EMBER_REQUIRE(!causal || lq <= lk, "ember_attention_bwd: causal attention needs lq <= lk, got lq=%d lk=%d",
                   lq, lk);
-    const size_t need = bwd_workspace_bytes(batch_heads, lq);
+    const size_t need = bwd_workspace_bytes(batch_heads, lq, d, dtype);
     if (!workspace || workspace_bytes < need) {
         set_error("ember_attention_bwd: workspace of %zu bytes needed, %zu given", need, workspace_bytes);
         return EMBER_ERR_WORKSPACE;
@@ -73,9 +95,22 @@ int ember_attention_bwd(const void *q, const void *k, const void *v, const void 
     a.bh = batch_heads; a.lq = lq; a.lk = lk; a.d = d;
     a.scale = scale; a.causal = causal ? 1 : 0; a.dtype = dtype;
     cudaStream_t s = pick_stream(stream, st);
-    if (sm100_bwd_supported(a)) return sm100_attention_bwd(a, (float *)workspace, st, s);
+    if (sm100_bwd_supported(a)) {
+        const bool det = deterministic_mode();
+        float *acc = det ? nullptr : (float *)((char *)workspace + delta_bytes(batch_heads, lq));
+        return sm100_attention_bwd(a, (float *)workspace, acc, det, st, s);
+    }
     return simt_attention_bwd(a, (float *)workspace, s);
 }
+
+int ember_set_deterministic(int on)
+{
+    const int before = deterministic_mode() ? 1 : 0;
+    g_deterministic = on ? 1 : 0;
+    return before;
+}
+
+int ember_get_deterministic(void) { return deterministic_mode() ? 1 : 0; }
 
 int ember_attention_decode_splits(int batch_heads, int lk, int d, int dtype)
 {
@@ -116,7 +151,7 @@ size_t ember_attention_workspace_bytes(int op, int batch_heads, int lq, int lk, 
 {
     if (batch_heads <= 0 || d <= 0) return 0;
     switch (op) {
-        case EMBER_OP_BWD: return lq > 0 ? bwd_workspace_bytes(batch_heads, lq) : 0;
+        case EMBER_OP_BWD: return lq > 0 ? bwd_workspace_bytes(batch_heads, lq, d, dtype) : 0;
         case EMBER_OP_DECODE: {
             if (lk <= 0) return 0;
             int splits = num_splits > 0 ? num_splits : ember_attention_decode_splits(batch_heads, lk, d, dtype);

@@ -743,6 +743,538 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
     if (warp == W_ALLOC) tmem_dealloc(tmem, 512);
 }
 
+// ------------------------------------------------------------------------------------------------
+// Single pass: dK, dV and dQ from one sweep over the (key tile, query tile) pairs
+// ------------------------------------------------------------------------------------------------
+// The two-kernel form above multiplies seven 128x128 tile products for the five the gradients need
+// (the dQ pass forms S and dP a second time). Here the CTA that owns a key tile also forms
+//     dQ(i) = dS(i) K        (this key tile's contribution to the gradient of query tile i)
+// and adds it into a float32 accumulator in global memory with a bulk reduce-add; a small kernel
+// afterwards scales and converts that accumulator to bf16. Changes against the dK/dV kernel:
+//   * dS^T goes to SHARED memory (bf16, the 128-byte-swizzled layout a TMA tile has) instead of
+//     tensor memory: the same 32 KB buffer is the K-major A operand of dK += dS^T Q (keys = M along
+//     rows, queries = K along the row) and the MN-major A operand of dQ = dS K (queries = M along the
+//     row, keys = K across rows); K itself, resident in shared memory, is the MN-major B operand.
+//   * the dP^T columns of tensor memory are dead once the compute warps have read them, so dQ(i)
+//     is accumulated there (tensor memory is full otherwise at HD = 128); four drain warps copy a
+//     whole row of it into registers at once while dK(i) is multiplied (dP^T(i+1) waits for that),
+//     then pass it through shared staging buffers to cp.reduce.async.bulk add.f32. (Adding straight
+//     from registers with red.global measured slower: the additions back up in the load/store path
+//     that the compute warps' shared-memory and barrier traffic also uses.)
+//   * with all operands of S^T, dP^T, dK and dQ read from shared memory (128 bytes per clock, which
+//     one 128x128x16 product per 64 clocks uses up by itself), the kernel is bound by shared-memory
+//     bandwidth: about 512 KB per tile pair (288 KB of operands, 96 KB written by TMA and the dS^T
+//     stores, 128 KB through the staging buffers) = 4000 clocks, against 3750 for the two kernels
+//     above together, which in practice take 5800.
+//   * the accumulator's layout is private to the two kernels: per (unit, query tile, lane quarter,
+//     32-column chunk) one contiguous 4 KB block holding [4-column group][row][4 floats], which makes
+//     the staging writes conflict-free and every bulk operation one contiguous block.
+// The float32 additions into the accumulator arrive in no fixed order, so dQ is reproducible only
+// to rounding (dK and dV stay bit-reproducible); the two-kernel form remains available for callers
+// who need run-to-run identical bits.
+//
+//   warps 0-7   compute (as above)            warp 8 / 9   MMA issue: score chain / gradient chain
+//   warp 10     TMA producer                   warp 11      tensor-memory allocation
+//   warps 12-15 drain dQ(i) from tensor memory into the global accumulator
+constexpr int SP_THREADS = (NCW + 8) * 32;
+constexpr int W_DRAIN0 = NCW + 4;
+
+template <int HD>
+struct SpCfg {
+    static constexpr int NSUB = HD / 64;
+    static constexpr int SUB_BYTES = 128 * 128;
+    static constexpr int TILE_BYTES = NSUB * SUB_BYTES;
+    // Shared memory at HD = 128 holds seven 32 KB tiles: K, V, dS^T and the drain staging leave three
+    // for the streamed operands, two for Q (in use from S^T(i) until dK(i)) and one for dO.
+    static constexpr int NA = HD == 128 ? 2 : 3, NB = HD == 128 ? 1 : 2;
+    static constexpr int DS_BYTES = 2 * SUB_BYTES;       // 128 keys x 128 queries, bf16
+    static constexpr int STAGE_WARP_BYTES = 2 * 4096;    // two 4 KB chunk buffers per drain warp
+    static constexpr int OFF_RES0 = 0;                   // K
+    static constexpr int OFF_RES1 = TILE_BYTES;          // V
+    static constexpr int OFF_A = 2 * TILE_BYTES;         // Q ring
+    static constexpr int OFF_B = OFF_A + NA * TILE_BYTES;  // dO ring
+    static constexpr int OFF_DS = OFF_B + NB * TILE_BYTES;
+    static constexpr int OFF_STAGE = OFF_DS + DS_BYTES;
+    static constexpr int OFF_BAR = OFF_STAGE + 4 * STAGE_WARP_BYTES;
+    static constexpr int OFF_ROWVEC = OFF_BAR + 192;
+    static constexpr int USED_BYTES = OFF_ROWVEC + 2048;
+    static constexpr int SMEM_BYTES = HD == 128 ? 232448 : USED_BYTES + 1024;
+    static constexpr int T_S = 0, T_DP = 128, T_ACC0 = 256, T_ACC1 = 256 + HD;
+    static constexpr int B_RES = 0, B_FULLA = 1, B_EMPTYA = B_FULLA + NA, B_FULLB = B_EMPTYA + NA,
+                         B_EMPTYB = B_FULLB + NB,
+                         B_S = B_EMPTYB + NB,   // S^T of the current tile is in tensor memory
+                         B_DP = B_S + 1,        // dP^T is in tensor memory
+                         B_P = B_DP + 1,        // P^T written (one arrival per compute warp)
+                         B_DS = B_P + 1,        // dS^T written to shared memory (one arrival per compute warp)
+                         B_DSFREE = B_DS + 1,   // dQ(i) and dK(i) have read dS^T(i)
+                         B_DQ = B_DSFREE + 1,   // dQ(i) is in tensor memory
+                         B_DQFREE = B_DQ + 1,   // the drain warps have copied dQ(i) out (4 arrivals)
+                         B_ACC = B_DQFREE + 1, NUM_BARS = B_ACC + 1;
+    static_assert(8 * NUM_BARS + 8 <= 192, "barrier block");
+    static_assert(HD != 128 || USED_BYTES + 800 <= SMEM_BYTES, "shared memory layout");
+};
+
+struct SpParams {
+    __nv_bfloat16 *dk, *dv;
+    float *dq_acc;  // [unit][query tile][lane quarter][HD/32 chunks][1024] float32, zero on entry
+    const float *lse, *delta;
+    int lq, lk, causal;
+    float scale, scale_log2;
+    DeviceStatus *status;
+    WorkOrder order;
+};
+
+// Adds four float32 values to four consecutive accumulator words (16-byte aligned) in global memory.
+__device__ __forceinline__ void red_add_f32x4(float *gdst, uint32_t a, uint32_t b, uint32_t c, uint32_t d)
+{
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(gdst), "f"(__uint_as_float(a)), "f"(__uint_as_float(b)),
+                 "f"(__uint_as_float(c)), "f"(__uint_as_float(d))
+                 : "memory");
+}
+
+__device__ __forceinline__ void bulk_reduce_add_f32(float *gdst, uint32_t smem_src, uint32_t bytes)
+{
+    asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;" ::"l"(gdst), "r"(smem_src),
+                 "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read_1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
+#ifndef BWD_RED_CHUNKS
+#define BWD_RED_CHUNKS 0  // of the HD/32 column chunks of a dQ row, how many are added straight from registers
+#endif
+
+#ifdef EMBER_BWD_TRACE
+// Development aid (not compiled into the library): one CTA records clock64() at the hand-over points
+// of its first iterations.
+__device__ long long g_bwd_trace[64 * 32];
+#define TR(slot, it)                                                                          \
+    do {                                                                                      \
+        if (blockIdx.x == gridDim.x / 2 && (it) < 64) g_bwd_trace[(it) * 32 + (slot)] = clock64(); \
+    } while (0)
+#else
+#define TR(slot, it) \
+    do {             \
+    } while (0)
+#endif
+
+template <int HD>
+__global__ void __launch_bounds__(SP_THREADS, 1)
+    sm100_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                           const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
+                           const SpParams p)
+{
+    using C = SpCfg<HD>;
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    if (!smem_layout_fits<C>(smem_u32(smem_raw), smem_base, p.status)) return;
+    const uint32_t bar0 = smem_base + C::OFF_BAR;
+    auto BAR = [&](int i) { return bar0 + 8u * (uint32_t)i; };
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem_gen + C::OFF_BAR + 8 * C::NUM_BARS);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    float *rowvec = reinterpret_cast<float *>(smem_gen + C::OFF_ROWVEC);
+
+    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    int bh, rank;
+    work_item(p.order, blockIdx.x, bh, rank);
+    const int k0 = rank * 128;  // under a causal mask the first key blocks are seen by the most queries
+    const int off = p.lk - p.lq;
+    const int i_begin = p.causal ? max(0, k0 - off) / 128 : 0;  // first query tile that sees key k0
+    const int nqt = (p.lq + 127) / 128;
+    const int n = nqt - i_begin;
+
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        mbar_init(BAR(C::B_RES), 1);
+        for (int s = 0; s < C::NA; s++) {
+            mbar_init(BAR(C::B_FULLA + s), 1);
+            mbar_init(BAR(C::B_EMPTYA + s), 2);  // released by both MMA warps
+        }
+        for (int s = 0; s < C::NB; s++) {
+            mbar_init(BAR(C::B_FULLB + s), 1);
+            mbar_init(BAR(C::B_EMPTYB + s), 2);  // dO is read by both chains (dP^T and dV)
+        }
+        mbar_init(BAR(C::B_S), 1);
+        mbar_init(BAR(C::B_DP), 1);
+        mbar_init(BAR(C::B_P), NCW);
+        mbar_init(BAR(C::B_DS), NCW);
+        mbar_init(BAR(C::B_DSFREE), 1);
+        mbar_init(BAR(C::B_DQ), 1);
+        mbar_init(BAR(C::B_DQFREE), 4);
+        mbar_init(BAR(C::B_ACC), 2);
+        fence_mbar_init();
+    }
+    if (warp == W_ALLOC) {
+        tmem_alloc(smem_u32(tmem_slot), 512);
+        tmem_relinquish();
+    }
+    if (warp == W_TMA && lane == 0) {
+        prefetch_tensormap(&tm_q);
+        prefetch_tensormap(&tm_k);
+        prefetch_tensormap(&tm_v);
+        prefetch_tensormap(&tm_do);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp >= W_DRAIN0) {
+        // -------------------------------------------------------------------- drain dQ(i)
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 136;");  // holds a whole 128-column row of dQ(i)
+        const int w = warp - W_DRAIN0;  // == warp % 4: the tensor-memory lane quarter this warp may read
+        const uint32_t t_dq = tmem + ((uint32_t)(w * 32) << 16) + C::T_DP;
+        uint8_t *stage = smem_gen + C::OFF_STAGE + w * C::STAGE_WARP_BYTES;
+        const uint32_t stage_u32 = smem_base + C::OFF_STAGE + w * C::STAGE_WARP_BYTES;
+        bool ok = true;
+        int cnt = 0;
+        for (int i = 0; i < n; i++) {
+            ok = ok && mbar_wait(BAR(C::B_DQ), i & 1, abort_flag, p.status, WB_ACC);
+            tc_fence_after();
+            if (w == 0 && lane == 0) TR(16, i);
+            float *gdst = p.dq_acc + ((((size_t)bh * nqt + (i_begin + i)) * 4 + w) * (HD / 32)) * 1024;
+            // The whole row leaves tensor memory at once, so that dP^T(i+1) can overwrite it while the
+            // chunks go through the staging buffers.
+            uint32_t u[HD / 32][32];
+#pragma unroll
+            for (int c = 0; c < HD / 32; c++) tmem_ld_32x32b_x32(t_dq + c * 32, u[c]);
+            tmem_wait_ld();
+            warp_arrive(BAR(C::B_DQFREE), lane);
+            if (w == 0 && lane == 0) TR(17, i);
+#pragma unroll
+            for (int c = 0; c < HD / 32; c++) {
+                if (c < BWD_RED_CHUNKS) {
+                    // one instruction adds 32 lanes x 16 bytes = 512 consecutive bytes of the accumulator
+                    if (ok) {
+#pragma unroll
+                        for (int cg = 0; cg < 8; cg++)
+                            red_add_f32x4(gdst + c * 1024 + cg * 128 + lane * 4, u[c][4 * cg], u[c][4 * cg + 1], u[c][4 * cg + 2],
+                                          u[c][4 * cg + 3]);
+                    }
+                    continue;
+                }
+                // the bulk operation that read this buffer two chunks ago must be done with it
+                if (lane == 0) bulk_wait_read_1();
+                __syncwarp();
+                uint8_t *buf = stage + (cnt & 1) * 4096;
+#pragma unroll
+                for (int cg = 0; cg < 8; cg++)
+                    *reinterpret_cast<uint4 *>(buf + (cg * 32 + lane) * 16) =
+                        make_uint4(u[c][4 * cg], u[c][4 * cg + 1], u[c][4 * cg + 2], u[c][4 * cg + 3]);
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) {
+                    if (ok) bulk_reduce_add_f32(gdst + c * 1024, stage_u32 + (cnt & 1) * 4096, 4096);
+                    bulk_commit();
+                }
+                cnt++;
+            }
+        }
+        if (lane == 0) bulk_wait_all();
+    } else if (warp >= NCW) {
+        reg_dealloc_40();
+        if (warp == W_TMA && lane == 0) {
+            // ---------------------------------------------------------------- TMA producer
+            mbar_arrive_expect_tx(BAR(C::B_RES), 2 * C::TILE_BYTES);
+            for (int s = 0; s < C::NSUB; s++) {
+                tma_load_3d(smem_base + C::OFF_RES0 + s * C::SUB_BYTES, &tm_k, BAR(C::B_RES), s * 64, k0, bh);
+                tma_load_3d(smem_base + C::OFF_RES1 + s * C::SUB_BYTES, &tm_v, BAR(C::B_RES), s * 64, k0, bh);
+            }
+            int issued_a = 0, issued_b = 0;
+            for (int i = 0; i < n; i++) {
+                const int sa = i % C::NA, sb = i % C::NB;
+                const int q0 = (i_begin + i) * 128;
+                if (!mbar_wait(BAR(C::B_EMPTYA + sa), ((i / C::NA) & 1) ^ 1, abort_flag, p.status, WB_EMPTY)) break;
+                mbar_arrive_expect_tx(BAR(C::B_FULLA + sa), C::TILE_BYTES);
+                for (int s = 0; s < C::NSUB; s++)
+                    tma_load_3d(smem_base + C::OFF_A + sa * C::TILE_BYTES + s * C::SUB_BYTES, &tm_q,
+                                BAR(C::B_FULLA + sa), s * 64, q0, bh);
+                issued_a = i + 1;
+                if (!mbar_wait(BAR(C::B_EMPTYB + sb), ((i / C::NB) & 1) ^ 1, abort_flag, p.status, WB_EMPTY)) break;
+                mbar_arrive_expect_tx(BAR(C::B_FULLB + sb), C::TILE_BYTES);
+                for (int s = 0; s < C::NSUB; s++)
+                    tma_load_3d(smem_base + C::OFF_B + sb * C::TILE_BYTES + s * C::SUB_BYTES, &tm_do,
+                                BAR(C::B_FULLB + sb), s * 64, q0, bh);
+                issued_b = i + 1;
+            }
+            drain_copies<C>(bar0, issued_a, issued_b);
+        } else if (warp == W_MMA_A || warp == W_MMA_B) {  // all 32 lanes, converged; one elected lane issues
+            // ---------------------------------------------------------------- MMA issue
+            constexpr uint32_t IDESC_SS = idesc_bf16_f32(128, 128, 0, 0);
+            constexpr uint32_t IDESC_TS = idesc_bf16_f32(128, HD, 0, 1);   // dV: A from tensor memory; dK: A K-major
+            constexpr uint32_t IDESC_DQ = idesc_bf16_f32(128, HD, 1, 1);   // A = dS^T read MN-major, B = K MN-major
+            const uint32_t ka = smem_base + C::OFF_RES0, va = smem_base + C::OFF_RES1, dsa = smem_base + C::OFF_DS;
+            const uint32_t k_lo = desc_lo(ka, 16), v_lo = desc_lo(va, 16);
+            auto q_addr = [&](int i) { return smem_base + C::OFF_A + (i % C::NA) * C::TILE_BYTES; };
+            auto do_addr = [&](int i) { return smem_base + C::OFF_B + (i % C::NB) * C::TILE_BYTES; };
+            bool ok = mbar_wait(BAR(C::B_RES), 0, abort_flag, p.status, WB_RES);
+            if (warp == W_MMA_A) {
+                // score chain: S^T(0); then per tile dV(i) (reads P^T, dO) and S^T(i+1) (overwrites P^T)
+                auto issue_st = [&](int i) {  // S^T = K Q^T
+                    const uint32_t q_lo = desc_lo(q_addr(i), 16);
+#pragma unroll
+                    for (int ks = 0; ks < HD / 16; ks++) {
+                        const uint32_t o16 = ((ks / 4) * C::SUB_BYTES + (ks % 4) * 32) >> 4;
+                        mma_ss_lo(tmem + C::T_S, k_lo + o16, q_lo + o16, IDESC_SS, ks > 0);
+                    }
+                    tc_commit_elect(BAR(C::B_S));
+                };
+                ok = ok && mbar_wait(BAR(C::B_FULLA + 0), 0, abort_flag, p.status, WB_FULL);
+                tc_fence_after();
+                issue_st(0);
+                for (int i = 0; i < n && ok; i++) {
+                    const uint32_t domn_lo = desc_lo(do_addr(i), C::SUB_BYTES);
+                    ok = ok && mbar_wait(BAR(C::B_FULLB + i % C::NB), (i / C::NB) & 1, abort_flag, p.status, WB_FULL);
+                    ok = ok && mbar_wait(BAR(C::B_P), i & 1, abort_flag, p.status, WB_P);
+                    tc_fence_after();
+                    if (lane == 0) TR(8, i);
+#pragma unroll
+                    for (int ks = 0; ks < 8; ks++)  // dV += P^T dO
+                        mma_ts_lo(tmem + C::T_ACC0, tmem + C::T_S + ks * 8, domn_lo + ks * (2048 >> 4), IDESC_TS,
+                                  (i > 0 || ks > 0) ? 1u : 0u);
+                    tc_commit_elect(BAR(C::B_EMPTYB + i % C::NB));  // this chain's last read of dO(i)
+                    if (i + 1 < n) {
+                        ok = ok && mbar_wait(BAR(C::B_FULLA + (i + 1) % C::NA), ((i + 1) / C::NA) & 1, abort_flag,
+                                             p.status, WB_FULL);
+                        tc_fence_after();
+                        issue_st(i + 1);  // overwrites P^T(i): ordered after dV(i) by issue order
+                    }
+                    if (lane == 0) TR(9, i);
+                    tc_commit_elect(BAR(C::B_EMPTYA + i % C::NA));  // this chain's last read of Q(i) was S^T(i)
+                }
+                tc_commit_elect(BAR(C::B_ACC));
+            } else {
+                // gradient chain: dP^T(0); then per tile dQ(i), dK(i) (both read dS^T from shared memory)
+                // and dP^T(i+1), which overwrites dQ(i) and therefore waits for the drain warps
+                auto issue_dpt = [&](int i) {  // dP^T = V dO^T
+                    const uint32_t do_lo = desc_lo(do_addr(i), 16);
+#pragma unroll
+                    for (int ks = 0; ks < HD / 16; ks++) {
+                        const uint32_t o16 = ((ks / 4) * C::SUB_BYTES + (ks % 4) * 32) >> 4;
+                        mma_ss_lo(tmem + C::T_DP, v_lo + o16, do_lo + o16, IDESC_SS, ks > 0);
+                    }
+                    tc_commit_elect(BAR(C::B_DP));
+                    tc_commit_elect(BAR(C::B_EMPTYB + i % C::NB));  // this chain's only read of dO(i)
+                };
+                const uint32_t ds_lo = desc_lo(dsa, 16), dsmn_lo = desc_lo(dsa, C::SUB_BYTES);
+                const uint32_t kmn_lo = desc_lo(ka, C::SUB_BYTES);
+                ok = ok && mbar_wait(BAR(C::B_FULLB + 0), 0, abort_flag, p.status, WB_FULL);
+                tc_fence_after();
+                issue_dpt(0);
+                for (int i = 0; i < n && ok; i++) {
+                    const uint32_t qmn_lo = desc_lo(q_addr(i), C::SUB_BYTES);
+                    ok = ok && mbar_wait(BAR(C::B_FULLA + i % C::NA), (i / C::NA) & 1, abort_flag, p.status, WB_FULL);
+                    ok = ok && mbar_wait(BAR(C::B_DS), i & 1, abort_flag, p.status, WB_DS);
+                    tc_fence_after();
+                    if (lane == 0) TR(12, i);
+#pragma unroll
+                    for (int ks = 0; ks < 8; ks++)  // dQ(i) = dS K: 16 keys per step
+                        mma_ss_lo(tmem + C::T_DP, dsmn_lo + ks * (2048 >> 4), kmn_lo + ks * (2048 >> 4), IDESC_DQ, ks > 0);
+                    tc_commit_elect(BAR(C::B_DQ));  // the drain warps copy dQ(i) out while dK(i) is multiplied
+#pragma unroll
+                    for (int ks = 0; ks < 8; ks++) {  // dK += dS^T Q: 16 queries per step
+                        const uint32_t o16 = ((ks / 4) * C::SUB_BYTES + (ks % 4) * 32) >> 4;
+                        mma_ss_lo(tmem + C::T_ACC1, ds_lo + o16, qmn_lo + ks * (2048 >> 4), IDESC_TS, (i > 0 || ks > 0) ? 1u : 0u);
+                    }
+                    tc_commit_elect(BAR(C::B_DSFREE));
+                    tc_commit_elect(BAR(C::B_EMPTYA + i % C::NA));  // this chain's last read of Q(i)
+                    if (lane == 0) TR(13, i);
+                    if (i + 1 < n) {
+                        ok = ok && mbar_wait(BAR(C::B_DQFREE), i & 1, abort_flag, p.status, WB_ACC);
+                        if (lane == 0) TR(14, i);
+                        ok = ok && mbar_wait(BAR(C::B_FULLB + (i + 1) % C::NB), ((i + 1) / C::NB) & 1, abort_flag,
+                                             p.status, WB_FULL);
+                        tc_fence_after();
+                        issue_dpt(i + 1);
+                        if (lane == 0) TR(15, i);
+                    }
+                }
+                tc_commit_elect(BAR(C::B_ACC));
+            }
+        }
+    } else {
+        // -------------------------------------------------------------------- compute
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 168;");  // 8 x 32 x 168 + 4 x 32 x 40 + 4 x 32 x 136 == 65536
+        const int h = warp / 4;                // which 64-column half of the 128 score columns (queries)
+        const int r = threadIdx.x % 128;       // TMEM lane == key row inside the tile
+        const int key = k0 + r;
+        const uint32_t lane_sel = (uint32_t)((warp % 4) * 32) << 16;
+        const uint32_t t_s = tmem + lane_sel + C::T_S, t_dp = tmem + lane_sel + C::T_DP;
+        const float c = p.scale_log2;
+        const float *lse_g = p.lse + (size_t)bh * p.lq;
+        const float *delta_g = p.delta + (size_t)bh * p.lq;
+        // this thread's 128 bytes of dS^T: row r of the sub-tile of its 64 queries; 16-byte chunk j of
+        // the row lies at chunk position j ^ (r % 8) (the 128-byte swizzle of the MMA descriptors)
+        uint8_t *ds_row = smem_gen + C::OFF_DS + h * C::SUB_BYTES + r * 128;
+        bool ok = true;
+        const float *rowvec_src = (threadIdx.x < 128 ? lse_g : delta_g);
+        auto fetch_raw = [&](int i) -> float {
+            const int qrow = (i_begin + i) * 128 + (threadIdx.x & 127);
+            float v = 0.f;
+            if (i < n && qrow < p.lq) asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v) : "l"(rowvec_src + qrow));
+            return v;
+        };
+        float raw_next = fetch_raw(0);
+        for (int i = 0; i < n; i++) {
+            const int q0 = (i_begin + i) * 128;
+            float *rv = rowvec + (i & 1) * 256;
+            {
+                const bool in_range = q0 + (threadIdx.x & 127) < p.lq;
+                rv[threadIdx.x] = threadIdx.x < 128 ? (in_range ? -raw_next * LOG2E_B : -INFINITY) : (in_range ? raw_next : 0.f);
+            }
+            raw_next = fetch_raw(i + 1);
+            // ---- phase 1: P^T = exp2(S^T * c - lse2), bf16 into tensor memory for dV += P^T dO
+            ok = ok && mbar_wait(BAR(C::B_S), i & 1, abort_flag, p.status, WB_S);
+            tc_fence_after();
+            if (threadIdx.x == 0) TR(0, i);
+            float pv[64];
+            tmem_ld_cols<64>(t_s + h * 64, pv);
+            // every thread has read its scores (the bf16 P^T overwrites columns another thread of the
+            // same lane still needs) and the lse/delta vectors are visible
+            named_bar_sync(1, NCT);
+            if (threadIdx.x == 0) TR(1, i);
+            if (p.causal && (k0 + 127 > q0 + off)) {  // tile crossed by the diagonal: mask before the exp
+                const float masked = c > 0.f ? -INFINITY : INFINITY;
+#pragma unroll
+                for (int cc = 0; cc < 64; cc++)
+                    if (key > q0 + h * 64 + cc + off) pv[cc] = masked;
+            }
+            const f32x2 c2 = pack2(c, c);
+#pragma unroll
+            for (int ch = 0; ch < 4; ch++) {
+                uint32_t pk[8];
+#pragma unroll
+                for (int x = 0; x < 8; x++) {
+                    const int cc = ch * 16 + 2 * x;
+                    const f32x2 x2 = fma2(pack2(pv[cc], pv[cc + 1]), c2, *reinterpret_cast<const f32x2 *>(&rv[h * 64 + cc]));
+                    float p0, p1;
+                    exp2_pair(x2, x, p0, p1);
+                    pv[cc] = p0;
+                    pv[cc + 1] = p1;
+                    pk[x] = pack_bf16(p0, p1);
+                }
+                tmem_st_x8(t_s + h * 32 + ch * 8, pk);  // 16 score columns -> 8 packed columns
+            }
+            tmem_wait_st();
+            warp_arrive(BAR(C::B_P), lane);
+            if (threadIdx.x == 0) TR(2, i);
+
+            // ---- phase 2: dS^T = P^T * (dP^T - delta), bf16 into shared memory for dQ = dS K and dK += dS^T Q
+            ok = ok && mbar_wait(BAR(C::B_DP), i & 1, abort_flag, p.status, WB_DP);
+            if (i > 0) ok = ok && mbar_wait(BAR(C::B_DSFREE), (i - 1) & 1, abort_flag, p.status, WB_DS);
+            tc_fence_after();
+            if (threadIdx.x == 0) TR(3, i);
+#pragma unroll
+            for (int half = 0; half < 2; half++) {
+                float dp[32];
+                tmem_ld_cols<32>(t_dp + h * 64 + half * 32, dp);
+#pragma unroll
+                for (int q4 = 0; q4 < 4; q4++) {  // 8 queries = one 16-byte chunk
+                    uint32_t w4[4];
+#pragma unroll
+                    for (int x = 0; x < 4; x++) {
+                        const int cd = q4 * 8 + 2 * x, cc = half * 32 + cd;
+                        const f32x2 ds2 = mul2(pack2(pv[cc], pv[cc + 1]),
+                                               sub2(pack2(dp[cd], dp[cd + 1]), *reinterpret_cast<const f32x2 *>(&rv[128 + h * 64 + cc])));
+                        float d0, d1;
+                        unpack2(ds2, d0, d1);
+                        w4[x] = pack_bf16(d0, d1);
+                    }
+                    const int chunk = half * 4 + q4;
+                    *reinterpret_cast<uint4 *>(ds_row + ((chunk ^ (r & 7)) << 4)) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+                }
+            }
+            fence_proxy_async();  // the MMAs read dS^T through the async proxy
+            warp_arrive(BAR(C::B_DS), lane);
+            if (threadIdx.x == 0) TR(4, i);
+        }
+        ok = ok && mbar_wait(BAR(C::B_ACC), 0, abort_flag, p.status, WB_ACC);
+        tc_fence_after();
+        // dV through the V tile's buffer, dK (times the softmax scale) through the K tile's: both
+        // resident tiles are dead once the last MMAs have completed.
+        stage_acc<HD>(tmem + lane_sel + C::T_ACC0, smem_gen + C::OFF_RES1, r, h, 1.f);
+        stage_acc<HD>(tmem + lane_sel + C::T_ACC1, smem_gen + C::OFF_RES0, r, h, p.scale);
+        named_bar_sync(3, NCT);
+        const int rows_valid = ok ? min(128, p.lk - k0) : 0;
+        const size_t gtile = ((size_t)bh * p.lk + k0) * HD;
+        store_staged<HD>(smem_gen + C::OFF_RES1, p.dv + gtile, rows_valid, warp, lane);
+        store_staged<HD>(smem_gen + C::OFF_RES0, p.dk + gtile, rows_valid, warp, lane);
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == W_ALLOC) tmem_dealloc(tmem, 512);
+}
+
+// dq = bf16(scale * accumulator): one block per (unit, query tile), thread t owns row t of the tile
+// (lane quarter t / 32, lane t % 32 of the accumulator's block layout).
+template <int HD>
+__global__ void __launch_bounds__(128) dq_finish_kernel(const float *__restrict__ acc, __nv_bfloat16 *__restrict__ dq, int lq,
+                                                        int nqt, float scale)
+{
+    const size_t tile = blockIdx.x;  // unit * nqt + query tile
+    const int qt = (int)(tile % nqt);
+    const size_t unit = tile / nqt;
+    const int w = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const int row = qt * 128 + threadIdx.x;
+    if (row >= lq) return;
+    const float4 *src = reinterpret_cast<const float4 *>(acc + ((tile * 4 + w) * (HD / 32)) * 1024);
+    __nv_bfloat16 *dst = dq + (unit * lq + row) * HD;
+#pragma unroll
+    for (int c = 0; c < HD / 32; c++) {
+#pragma unroll
+        for (int cg = 0; cg < 8; cg += 2) {
+            const float4 a = src[c * 256 + cg * 32 + lane], b = src[c * 256 + (cg + 1) * 32 + lane];
+            uint4 o;
+            o.x = pack_bf16(a.x * scale, a.y * scale);
+            o.y = pack_bf16(a.z * scale, a.w * scale);
+            o.z = pack_bf16(b.x * scale, b.y * scale);
+            o.w = pack_bf16(b.z * scale, b.w * scale);
+            *reinterpret_cast<uint4 *>(dst + c * 32 + cg * 4) = o;
+        }
+    }
+}
+
+template <int HD>
+int launch_fused(const AttnArgs &a, float *delta, float *dq_acc, DeviceState *st, cudaStream_t s)
+{
+    using C = SpCfg<HD>;
+    static_assert(NCW == 8, "the single-pass kernel is written for eight compute warps");
+    int rc = launch_delta(a, delta, s);
+    if (rc) return rc;
+    const int nqt = (a.lq + 127) / 128;
+    EMBER_CUDA_TRY(cudaMemsetAsync(dq_acc, 0, (size_t)a.bh * nqt * 128 * HD * sizeof(float), s));
+    CUtensorMap tq, tk, tv, tdo;
+    if ((rc = make_tensor_map_bf16_3d(&tq, a.q, HD, a.lq, a.bh, 64, 128)) != EMBER_OK) return rc;
+    if ((rc = make_tensor_map_bf16_3d(&tk, a.k, HD, a.lk, a.bh, 64, 128)) != EMBER_OK) return rc;
+    if ((rc = make_tensor_map_bf16_3d(&tv, a.v, HD, a.lk, a.bh, 64, 128)) != EMBER_OK) return rc;
+    if ((rc = make_tensor_map_bf16_3d(&tdo, a.dout, HD, a.lq, a.bh, 64, 128)) != EMBER_OK) return rc;
+    SpParams p;
+    p.dk = (__nv_bfloat16 *)a.dk;
+    p.dv = (__nv_bfloat16 *)a.dv;
+    p.dq_acc = dq_acc;
+    p.lse = a.lse;
+    p.delta = delta;
+    p.lq = a.lq;
+    p.lk = a.lk;
+    p.causal = a.causal;
+    p.scale = a.scale;
+    p.scale_log2 = a.scale * LOG2E_B;
+    p.status = st->status;
+    auto k1 = sm100_bwd_fused_kernel<HD>;
+    EMBER_CUDA_TRY(cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+    const size_t touched = ((size_t)a.lq + a.lk) * HD * 2 * 4 + (size_t)a.lq * HD * 4;  // + the float32 dQ accumulator
+    p.order = make_work_order(a.bh, (a.lk + 127) / 128, st->sm_count, touched, a.causal != 0);
+    k1<<<dim3((unsigned)(p.order.units * p.order.blocks)), SP_THREADS, C::SMEM_BYTES, s>>>(tq, tk, tv, tdo, p);
+    EMBER_CUDA_TRY(cudaGetLastError());
+    dq_finish_kernel<HD><<<(unsigned)((size_t)a.bh * nqt), 128, 0, s>>>(dq_acc, (__nv_bfloat16 *)a.dq, a.lq, nqt, a.scale);
+    EMBER_CUDA_TRY(cudaGetLastError());
+    return EMBER_OK;
+}
+
 template <int HD>
 int launch(const AttnArgs &a, float *delta, DeviceState *st, cudaStream_t s)
 {
@@ -795,9 +1327,23 @@ bool sm100_bwd_supported(const AttnArgs &a)
     return (bits & 15) == 0;
 }
 
-int sm100_attention_bwd(const AttnArgs &a, float *delta, DeviceState *st, cudaStream_t s)
+#ifdef EMBER_BWD_TRACE
+extern "C" EMBER_API int ember_debug_bwd_trace(long long *host)
 {
-    return a.d == 128 ? launch<128>(a, delta, st, s) : launch<64>(a, delta, st, s);
+    return (int)cudaMemcpyFromSymbol(host, g_bwd_trace, sizeof(long long) * 64 * 32);
+}
+#endif
+
+// Bytes of float32 dQ accumulator the single-pass kernel needs after the delta vector.
+size_t sm100_bwd_accumulator_bytes(int bh, int lq, int d)
+{
+    return (size_t)bh * ((lq + 127) / 128) * 128 * d * sizeof(float);
+}
+
+int sm100_attention_bwd(const AttnArgs &a, float *delta, float *dq_acc, bool deterministic, DeviceState *st, cudaStream_t s)
+{
+    if (deterministic || !dq_acc) return a.d == 128 ? launch<128>(a, delta, st, s) : launch<64>(a, delta, st, s);
+    return a.d == 128 ? launch_fused<128>(a, delta, dq_acc, st, s) : launch_fused<64>(a, delta, dq_acc, st, s);
 }
 
 }  // namespace ember

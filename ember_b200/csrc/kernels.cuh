@@ -28,7 +28,10 @@ int launch_delta(const AttnArgs &a, float *delta, cudaStream_t s);
 bool sm100_fwd_supported(const AttnArgs &a);
 int sm100_attention_fwd(const AttnArgs &a, DeviceState *st, cudaStream_t s);
 bool sm100_bwd_supported(const AttnArgs &a);
-int sm100_attention_bwd(const AttnArgs &a, float *delta, DeviceState *st, cudaStream_t s);
+// deterministic: two kernels (dK/dV, then dQ), bit-reproducible; otherwise one pass that adds its dQ
+// contributions into dq_acc (sm100_bwd_accumulator_bytes of float32 scratch after the delta vector).
+size_t sm100_bwd_accumulator_bytes(int bh, int lq, int d);
+int sm100_attention_bwd(const AttnArgs &a, float *delta, float *dq_acc, bool deterministic, DeviceState *st, cudaStream_t s);
 
 // Decode over a contiguous key/value cache with grouped-query heads on the tensor cores
 // (attn_fwd_sm100.cu: the forward kernel with the group's query heads as the rows of one tile and the

@@ -121,11 +121,26 @@ EMBER_API int ember_attention_fwd(const void *q, const void *k, const void *v, v
  *      ember/loss/losses.py:53-56): dV = P^T dO, dP = dO V^T, dS = P*(dP - delta)*scale,
  *      dQ = dS K, dK = dS^T Q, with P recomputed from the saved lse.
  *      workspace: ember_attention_workspace_bytes(EMBER_OP_BWD, ...) bytes of
- *      device memory, 256-byte aligned, contents undefined on entry. ---- */
+ *      device memory, 256-byte aligned, contents undefined on entry (the row sums of dO*O,
+ *      and for the single-pass bf16 kernel a float32 dQ accumulator of lq rounded up to 128 rows
+ *      per batch_head, which the call clears itself). ---- */
 EMBER_API int ember_attention_bwd(const void *q, const void *k, const void *v, const void *out,
                         const float *lse, const void *dout, void *dq, void *dk, void *dv,
                         int batch_heads, int lq, int lk, int d, float scale, int causal, int dtype,
                         void *workspace, size_t workspace_bytes, void *stream);
+
+/* ---- run-to-run reproducibility of the backward (no counterpart in the reference, whose CPU
+ *      loops are sequential). By default the bf16 tensor-core backward makes ONE pass over the
+ *      (key tile, query tile) pairs and adds each key tile's contribution to dQ into a float32
+ *      accumulator in the workspace; those additions arrive in no fixed order, so dQ is
+ *      reproducible to float32 rounding only (dK, dV and everything else are bit-reproducible).
+ *      ember_set_deterministic(1) selects the two-kernel form (dK/dV, then a separate dQ pass that
+ *      recomputes the scores): bit-identical results from run to run at about 1.4x the tile
+ *      products. The setting is process-wide; its initial value is 1 when the environment variable
+ *      EMBER_DETERMINISTIC is set to something other than 0. Returns the previous setting.
+ *      Change it only between calls; workspace sizes depend on it (query them after changing). ---- */
+EMBER_API int ember_set_deterministic(int on);
+EMBER_API int ember_get_deterministic(void);
 
 /* ---- single-query decode against a long key/value cache (lq == 1, no mask),
  *      split over the key axis with a log-sum-exp combine. Same reference path as
