@@ -51,6 +51,10 @@ SIGNATURES = {
     "ember_attention_kernel_name": (ctypes.c_char_p, [_i] * 5),
     "ember_work_order_item": (_i, [_i, _i, _i, _sz, _i, _i, ctypes.POINTER(_i), ctypes.POINTER(_i)]),
     "ember_attention_fwd_host": (_i, [_vp] * 5 + [_i] * 4 + [ctypes.c_float, _i, _i]),
+    "ember_comm_unique_id": (_i, [_vp]),
+    "ember_comm_init": (_i, [ctypes.POINTER(_vp), _vp, _i, _i, _i]),
+    "ember_comm_destroy": (_i, [_vp]),
+    "ember_gather_outputs": (_i, [_vp, _vp, _sz, _vp, _vp]),
     "ember_linear_fwd": (_i, [_vp] * 4 + [ctypes.c_longlong] + [_i] * 7 + [_vp]),
     "ember_linear_bwd": (_i, [_vp] * 6 + [ctypes.c_longlong] + [_i] * 7 + [_vp]),
     "ember_linear_kernel_name": (ctypes.c_char_p, [_i, ctypes.c_longlong] + [_i] * 7),

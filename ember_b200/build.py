@@ -19,7 +19,7 @@ LIB = os.path.join(HERE, "libember_b200.so")
 
 SOURCES = ["core.cu", "tma_host.cu", "attn_simt.cu", "attn_decode.cu", "attn_fwd_sm100.cu",
            "attn_bwd_sm100.cu", "api.cu", "gemm_simt.cu", "gemm_sm100.cu", "linear_api.cu",
-           "softmax_ce.cu", "kv_cache.cu"]
+           "softmax_ce.cu", "kv_cache.cu", "comm.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr"]
 
@@ -62,7 +62,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
                 if verbose and out:
                     print(out)
     if jobs or not os.path.exists(LIB):
-        run([_nvcc(), "-shared", "-o", LIB, *objs, "-cudart", "shared"])
+        run([_nvcc(), "-shared", "-o", LIB, *objs, "-cudart", "shared", "-ldl"])
     build_binding(force or bool(jobs))
     return LIB
 

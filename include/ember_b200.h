@@ -206,6 +206,27 @@ EMBER_API int ember_work_order_item(int units, int blocks, int sm_count, size_t 
  * arguments: "sm100_tcgen05" or "simt_f32". For tests and the benchmark. */
 EMBER_API const char *ember_attention_kernel_name(int op, int lq, int lk, int d, int dtype);
 
+/* ---- Optional gather of the per-rank output slabs (no counterpart in the reference, which has no
+ *      communication layer: its CMakeLists.txt:63,102 link only cuBLAS).
+ *
+ * The path shards over (batch * head) with no exchange in forward or backward. When a caller wants
+ * the whole result on every rank, rank r of `world` passes its slab (equal sizes on all ranks)
+ * and receives the concatenation in rank order: one ncclAllGather over NVLink inside a box,
+ * enqueued on `stream` (NULL = the library stream). NCCL is loaded at run time (libnccl.so.2, or the
+ * path in the environment variable EMBER_NCCL_LIB); without it these calls return
+ * EMBER_ERR_UNSUPPORTED and everything else works.
+ *
+ * Set-up: one rank calls ember_comm_unique_id and hands the EMBER_COMM_ID_BYTES bytes to the others
+ * by any host-side means (a file, a socket, the launcher's key/value store); every rank then calls
+ * ember_comm_init with its device current. A rank that never arrives makes the others return
+ * EMBER_ERR_TIMEOUT after timeout_ms (<= 0: wait without limit) with nothing left running on the
+ * GPU. out_full may alias the slab (in place: out_slab == out_full + rank * slab_bytes). ---- */
+#define EMBER_COMM_ID_BYTES 128
+EMBER_API int ember_comm_unique_id(void *id_out);
+EMBER_API int ember_comm_init(void **comm, const void *id, int rank, int world, int timeout_ms);
+EMBER_API int ember_comm_destroy(void *comm);
+EMBER_API int ember_gather_outputs(void *out_full, const void *out_slab, size_t slab_bytes, void *comm, void *stream);
+
 /* ---- The Linear layers either side of attention -----------------------------
  *
  * Replaces the reference's Linear layer (ember/nn/layers.py:9-56), which composes
