@@ -269,9 +269,12 @@ def run_gpu_arm(args):
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device; there is no CPU fallback for the attention path")
     torch.cuda.set_device(local_rank)
+    # stdout carries exactly one JSON line: anything a library prints there while the benchmark runs
+    # (NCCL's version banner, for one) goes to stderr instead
+    sys.stdout.flush()
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
     if world > 1:
-        if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":  # keeps stdout to the one JSON line
-            os.environ["NCCL_DEBUG"] = "WARN"
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     L = _lib.lib()
     _lib.check(L.ember_set_device(local_rank))
@@ -296,11 +299,16 @@ def run_gpu_arm(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    from ember_b200 import synth
+
     B, H, S, D = (WORKLOAD[x] for x in "BHLD")
     scale = 1.0 / math.sqrt(D)
-    gen = torch.Generator(device=dev).manual_seed(1000 + rank)
-    q, k, v = ((torch.randn((B, H, S, D), generator=gen, device=dev, dtype=torch.float32) * 0.5).to(torch.bfloat16)
-               for _ in range(3))
+    # Inputs are keyed by the GLOBAL element index: the job is world x (B*H) units, rank r holds units
+    # [r*B*H, (r+1)*B*H), and a unit's values do not depend on the number of ranks.
+    BH = B * H
+    u0 = rank * BH
+    q, k, v = (synth.units_torch(torch, seed, u0, u0 + BH, S, D, dev, 0.5, torch.bfloat16).view(B, H, S, D)
+               for seed in (1001, 1002, 1003))
     out = torch.empty_like(q)
     lse = torch.empty((B, H, S), device=dev, dtype=torch.float32)
     flops_step = 4.0 * B * H * S * S * D / 2.0
@@ -327,6 +335,8 @@ def run_gpu_arm(args):
     value = world * flops_step / (ms_step * 1e-3) / 1e12
     where = ctypes.c_int(0)
     _lib.check(L.ember_check_device_status(sptr, ctypes.byref(where)))
+    sustained = run_sustained(torch, fwd, stream, sampler, ms_step, flops_step, world, peaks, barrier, max_over_ranks)
+    identity = check_identity(L, _lib, torch, dist, synth, dev, sptr, out, lse, rank, world, BH, S, D, scale)
 
     # ---- end to end through the C ABI with host buffers (pinned), copies inside the timed region:
     # ember_attention_fwd_host takes host tensors (the reference's own calling pattern), streams the
@@ -358,7 +368,9 @@ def run_gpu_arm(args):
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": WORKLOAD["name"], "per_gpu": True, "causal": True, "scale": scale,
-                   "inputs": "N(0,1)*0.5 seeded per rank, resident in HBM",
+                   "inputs": "approx. N(0,1)*0.5 keyed by the global element index (rank r holds units "
+                             "[r*128, (r+1)*128) of a world*128-unit job), resident in HBM",
+                   "identity_1_vs_n": identity,
                    "l2": "inputs (403 MB per step) larger than L2 (126 MB); no flush",
                    "kernel": L.ember_attention_kernel_name(0, S, S, D, 1).decode()},
         "roofline": {"bound": "tensor", "achieved": flops_step / (ms_step * 1e-3) / 1e12, "peak": peaks["bf16_tflops"],
@@ -374,13 +386,20 @@ def run_gpu_arm(args):
                 "ms_per_step": e2e_s * 1e3, "steps": e2e_steps, "result_matches_device_run": e2e_ok},
         "gpu_launches": args.steps,
         "clocks": clocks,
+        "sustained": sustained,
     }
 
+    if world > 1:
+        line["gather"] = run_gather(L, _lib, torch, dist, dev, sptr, stream, out, rank, world)
     sweep = None
     if not args.no_extra:
-        sweep = run_c5_sweep(L, _lib, torch, dist, dev, sptr, stream, rank, world)
+        sweep = run_c5_sweep(L, _lib, torch, dist, dev, sptr, stream, rank, world, sampler)
     if rank == 0 and world == 1:
         cb, _ = cpu_baseline_value(rows=1024, threads=min(host_threads(), 64), repeats=1)
+        # the reference is single-threaded (src/tensor/operators_cpu.c:47-67 has no parallel loop), so
+        # its own figure is the one-thread one; the all-threads figure above runs independent slices
+        one, _ = cpu_baseline_value(rows=512, threads=1, repeats=1)
+        cb["single_thread"] = {"value": one["value"], "unit": "TFLOP/s", "cores": 1, "sample": one["sample"]}
         line["cpu_baseline"] = cb
         if not args.no_extra:
             line["extra"] = run_extras(L, _lib, torch, dev, sptr, stream, peaks)
@@ -388,28 +407,147 @@ def run_gpu_arm(args):
         line.setdefault("extra", {})["scaling_sweep_fwd_bwd_128_heads"] = {
             "scaling": "strong", "note": "causal fwd+bwd, bf16, D=128, 128 (batch*head) units split over the GPUs",
             **sweep}
+        # a compact copy where every reader of the line finds it: whole-job TFLOP/s and ms per length
+        line["config"]["c5_strong"] = {
+            "what": "causal fwd+bwd bf16 H=64 D=128, 128 (batch*head) units split over n_gpus (strong scaling)",
+            **{key: {"tflops": round(val["tflops_total"], 1), "ms": round(val["ms_fwd_bwd"], 4),
+                     "sm_mhz_min": min(val["sm_mhz_per_rank"]), "sm_mhz_max": max(val["sm_mhz_per_rank"])}
+               for key, val in sweep.items() if key.startswith("L")},
+            "identity_1_vs_n": sweep.get("identity_1_vs_n")}
     if world > 1:
         dist.destroy_process_group()
+    sys.stdout.flush()
+    os.dup2(real_stdout, 1)
+    os.close(real_stdout)
     if rank == 0:
         print(json.dumps(line), flush=True)
 
 
-def run_c5_sweep(L, _lib, torch, dist, dev, sptr, stream, rank, world):
+def run_gather(L, _lib, torch, dist, dev, sptr, stream, out, rank, world):
+    """The optional result gather (not on the data path): every rank's output slab into one full
+    tensor on every rank with ember_gather_outputs (ncclAllGather over NVLink), timed on its own."""
+    from ember_b200.comm import Communicator
+
+    store = dist.PrefixStore("ember_bench_gather", dist.distributed_c10d._get_default_store())
+    comm = Communicator(rank, world, store, timeout_s=120.0)
+    nbytes = out.numel() * out.element_size()
+    full = torch.empty((world,) + tuple(out.shape), dtype=out.dtype, device=dev)
+    for _ in range(2):
+        comm.gather_into(full.data_ptr(), out.data_ptr(), nbytes, sptr)
+    dist.barrier()
+    torch.cuda.synchronize()
+    reps = 5
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record(stream)
+    for _ in range(reps):
+        comm.gather_into(full.data_ptr(), out.data_ptr(), nbytes, sptr)
+    b.record(stream)
+    torch.cuda.synchronize()
+    t = torch.tensor([a.elapsed_time(b) / reps], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    # every slab of the gathered tensor carries its owner's checksum
+    mine = torch.tensor([unit_checksum(torch, out.view(-1, out.shape[-2], out.shape[-1])[0])], dtype=torch.int64, device=dev)
+    owners = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(owners, mine)
+    ok = all(unit_checksum(torch, full[r].view(-1, out.shape[-2], out.shape[-1])[0]) == int(owners[r].item()) for r in range(world))
+    ok = ok and bool(torch.equal(full[rank], out))
+    comm.close()
+    return {"ms": ms, "bytes_per_rank": nbytes, "bytes_total": world * nbytes, "algbw_gbs": world * nbytes / ms / 1e6,
+            "busbw_gbs": (world - 1) * nbytes / ms / 1e6, "nvlink_measured_peer_gbs": 770.0, "result_ok": ok,
+            "call": "ember_gather_outputs (ncclAllGather of equal slabs), timed apart from the attention step"}
+
+
+def unit_checksum(torch, t):
+    """A position-weighted 64-bit checksum of a tensor's bits (wrapping integer arithmetic)."""
+    bits = t.contiguous().view(torch.int16 if t.element_size() == 2 else torch.int32).reshape(-1).to(torch.int64)
+    w = torch.arange(1, bits.numel() + 1, dtype=torch.int64, device=t.device)
+    return int((bits * w).sum().item())
+
+
+def check_identity(L, _lib, torch, dist, synth, dev, sptr, out, lse, rank, world, BH, S, D, scale):
+    """Outside any timed region: does the result of a unit depend on which rank computed it, or on
+    the shape of the launch it was part of? Every rank regenerates the FIRST unit of its right-hand
+    neighbour's slab from the global generator, runs it as a launch of one unit, and the checksum of
+    that output is compared with the checksum the owner took from its full launch (only the
+    checksums travel). With one rank the neighbour is the rank itself."""
+    nb = (rank + 1) % world
+    g = nb * BH
+    q1, k1, v1 = (synth.units_torch(torch, seed, g, g + 1, S, D, dev, 0.5, torch.bfloat16) for seed in (1001, 1002, 1003))
+    o1 = torch.empty_like(q1)
+    l1 = torch.empty((1, S), device=dev, dtype=torch.float32)
+    _lib.check(L.ember_attention_fwd(q1.data_ptr(), k1.data_ptr(), v1.data_ptr(), o1.data_ptr(), l1.data_ptr(), 1, S, S, D,
+                                     scale, 1, _lib.EMBER_BF16, sptr))
+    torch.cuda.synchronize()
+    mine = torch.tensor([unit_checksum(torch, out.view(BH, S, D)[0]), unit_checksum(torch, lse.view(BH, S)[0])],
+                        dtype=torch.int64, device=dev)
+    theirs = torch.tensor([unit_checksum(torch, o1[0]), unit_checksum(torch, l1[0])], dtype=torch.int64, device=dev)
+    if world > 1:
+        owners = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(owners, mine)
+        ok = bool(torch.equal(owners[nb], theirs))
+        flag = torch.tensor([1 if ok else 0], dtype=torch.int32, device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        ok = bool(flag.item())
+    else:
+        ok = bool(torch.equal(mine, theirs))
+    if not ok:
+        raise SystemExit("bench.py: a unit computed alone differs from the same unit inside its owner's launch")
+    return {"checked": True, "ok": ok, "how": "first unit of the next rank's slab recomputed as a one-unit launch; "
+                                              "output and log-sum-exp checksums equal the owner's, bit for bit"}
+
+
+def run_sustained(torch, fwd, stream, sampler, ms_step, flops_step, world, peaks, barrier, max_over_ranks):
+    """A second, seconds-long timed region of back-to-back launches of the headline workload: the SM
+    clock sinks under the power limit after the first tens of milliseconds, so this is the rate a
+    long job sees. Reported beside the short-burst headline with the clock sampled inside the region
+    (time x clock = cycles per step separates kernel changes from clock changes)."""
+    n = max(50, int(2000.0 / max(ms_step, 1e-3)))
+    barrier()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    a.record(stream)
+    for _ in range(n):
+        fwd()
+    b.record(stream)
+    barrier()
+    t1 = time.perf_counter()
+    ms = max_over_ranks(a.elapsed_time(b)) / n
+    clk = sampler.summary(t0 + 0.25 * (t1 - t0), t1)  # the settled part of the region
+    val = world * flops_step / (ms * 1e-3) / 1e12
+    mhz = clk.get("sm_mhz")
+    return {"value": val, "unit": "TFLOP/s", "steps": n, "ms_per_step": ms, "seconds": (t1 - t0),
+            "frac_of_sustained_peak": val / world / peaks["bf16_tflops_sustained"],
+            "peak_sustained": peaks["bf16_tflops_sustained"], "sm_mhz_median": mhz, "reasons": clk.get("reasons"),
+            "power_w_max": clk.get("power_w_max"),
+            "mcycles_per_step": (ms * 1e-3 * mhz) if mhz else None}
+
+
+def run_c5_sweep(L, _lib, torch, dist, dev, sptr, stream, rank, world, sampler):
     """The strong-scaling configuration: causal forward+backward, bf16, 128 (batch*head) units with D=128 split over
     the ranks (strong scaling: the total work is fixed), L in {2048, 8192, 16384}. Every rank owns
-    the contiguous slab shard_range(128, rank, world); no collective on the data path. Returns, per
-    L, the whole-job TFLOP/s from the slowest rank's device time."""
+    the contiguous slab shard_range(128, rank, world) of tensors generated from the global element
+    index; no collective on the data path. Returns, per L, the whole-job TFLOP/s from the slowest
+    rank's device time and the SM clock each rank saw. At L=2048 (cheap) every rank also computes ALL
+    128 units, the single-GPU job, and checks outside the timed region that its slab of that result
+    equals what it computed as a shard: bit for bit for O, LSE, dK and dV, and for dQ too when the
+    deterministic backward is selected (the default backward adds dQ contributions in no fixed
+    order; there dQ is compared to rounding)."""
+    from ember_b200 import synth
     from ember_b200.shard import shard_range
 
     out = {}
-    D = 128
-    b, e = shard_range(128, rank, world)
-    bh = e - b
-    for S in (2048, 8192, 16384):
-        scale = 1.0 / math.sqrt(D)
-        gen = torch.Generator(device=dev).manual_seed(500 + rank)
-        q, k, v = ((torch.randn((bh, S, D), generator=gen, device=dev) * 0.5).to(torch.bfloat16) for _ in range(3))
-        do = torch.randn((bh, S, D), generator=gen, device=dev).to(torch.bfloat16)
+    D, units = 128, 128
+    b, e = shard_range(units, rank, world)
+    scale = 1.0 / math.sqrt(D)
+
+    def make(u0, u1, S):
+        q, k, v = (synth.units_torch(torch, seed, u0, u1, S, D, dev, 0.5, torch.bfloat16) for seed in (501, 502, 503))
+        do = synth.units_torch(torch, 504, u0, u1, S, D, dev, 1.0, torch.bfloat16)
+        return q, k, v, do
+
+    def run(q, k, v, do, S):
+        bh = q.shape[0]
         o, dq, dk, dv = (torch.empty_like(q) for _ in range(4))
         lse = torch.empty((bh, S), device=dev, dtype=torch.float32)
         wsn = L.ember_attention_workspace_bytes(_lib.EMBER_OP_BWD, bh, S, S, D, 1, 0)
@@ -421,27 +559,68 @@ def run_c5_sweep(L, _lib, torch, dist, dev, sptr, stream, rank, world):
             _lib.check(L.ember_attention_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(),
                                              do.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), bh, S, S, D,
                                              scale, 1, 1, ws.data_ptr(), wsn, sptr))
+        return step, (o, lse, dq, dk, dv)
 
-        steps = 10 if S <= 8192 else 4
+    for S in (2048, 8192, 16384):
+        q, k, v, do = make(b, e, S)
+        step, res = run(q, k, v, do, S)
+        steps = {2048: 100, 8192: 20}.get(S, 6)  # each timed loop long enough for a few clock samples
         for _ in range(3):
             step()
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
         a, c = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
         a.record(stream)
         for _ in range(steps):
             step()
         c.record(stream)
         torch.cuda.synchronize()
+        t1 = time.perf_counter()
         ms = a.elapsed_time(c) / steps
+        mhz = sampler.summary(t0, t1).get("sm_mhz") or 0.0
+        mhz_all = [mhz]
         if world > 1:
             t = torch.tensor([ms], dtype=torch.float64, device=dev)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             ms = float(t.item())
-        total_flops = 3.5 * 4.0 * 128 * S * S * D / 2.0
-        out[f"L{S}"] = {"ms_fwd_bwd": ms, "tflops_total": total_flops / ms / 1e9, "bh_per_gpu": bh}
-        del q, k, v, do, o, dq, dk, dv, ws
+            g = [torch.empty(1, dtype=torch.float64, device=dev) for _ in range(world)]
+            dist.all_gather(g, torch.tensor([mhz], dtype=torch.float64, device=dev))
+            mhz_all = [float(x.item()) for x in g]
+        total_flops = 3.5 * 4.0 * units * S * S * D / 2.0
+        out[f"L{S}"] = {"ms_fwd_bwd": ms, "tflops_total": total_flops / ms / 1e9, "bh_per_gpu": e - b,
+                        "sm_mhz_per_rank": mhz_all}
+        if S == 2048:
+            fq, fk, fv, fdo = (q, k, v, do) if world == 1 else make(0, units, S)
+            if world == 1:
+                # one GPU: the same units as a launch of a different shape (the second half alone)
+                fq, fk, fv, fdo = (t[units // 2:] for t in (q, k, v, do))
+                lo, hi = units // 2, units
+            else:
+                lo, hi = 0, units
+            fstep, fres = run(fq, fk, fv, fdo, S)
+            fstep()
+            torch.cuda.synchronize()
+            det = bool(L.ember_get_deterministic())
+            ok = True
+            for name, mine, full in zip(("o", "lse", "dq", "dk", "dv"), res, fres):
+                ref = full[max(b, lo) - lo:min(e, hi) - lo]
+                got = mine[max(b, lo) - b:min(e, hi) - b]
+                if name == "dq" and not det:
+                    ok = ok and bool(((got.float() - ref.float()).abs().max() <= 1e-2 * ref.float().abs().max()).item())
+                else:
+                    ok = ok and bool(torch.equal(got, ref))
+            if world > 1:
+                flag = torch.tensor([1 if ok else 0], dtype=torch.int32, device=dev)
+                dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+                ok = bool(flag.item())
+            if not ok:
+                raise SystemExit("bench.py: a rank's slab differs from the same slab of the single-GPU job")
+            out["identity_1_vs_n"] = {"checked": True, "ok": ok, "L": S, "dq": "bit for bit" if det else "to rounding",
+                                      "o_lse_dk_dv": "bit for bit"}
+            del fq, fk, fv, fdo, fres
+        del q, k, v, do, res
     return out
 
 
