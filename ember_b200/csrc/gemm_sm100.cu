@@ -6,15 +6,22 @@
 // where x, dy and y may lie head-major (parts, batch, heads, seq, dim) instead of row-major, so that
 // no transpose kernel runs between a projection and attention.
 //
-// Persistent kernel, one CTA per SM, 128 x 256 output tiles, K in steps of 64:
+// Persistent kernel, one CTA per SM, CTAs in PAIRS (clusters of two, cta_group::2): a pair computes
+// 256 x 256 output tiles, K in steps of 64. Each CTA of a pair
+//   * loads its own 128 rows of A and its own 128 of the tile's 256 columns of B (its own TMA copies;
+//     the completion bytes of both CTAs are counted by rank 0's barrier),
+//   * receives its 128 rows x 256 columns of the result in its own tensor memory and writes them out.
+// Rank 0 issues tcgen05.mma M=256 N=256 K=16 for both. A single CTA working alone on 128 x 256
+// tiles reads 12 KB of operands per MMA and receives 48 KB per K step through the same 128 bytes
+// per clock of shared-memory bandwidth, about 190 bytes per clock of demand: that form measured
+// 0.70-0.76 of the library GEMM. In a pair each SM reads 8 KB per MMA and receives 32 KB per step.
 //   warps 0-3  epilogue: accumulator (TMEM) + bias -> bf16 -> shared memory -> coalesced rows
-//   warp  4    TMEM allocation, then MMA issue (warp-collective, one elected lane):
-//              tcgen05.mma M=128 N=256 K=16, four per K step
-//   warp  5    TMA producer (one lane): a ring of 4 stages of A (16 KB) and B (32 KB) tiles
+//   warp  4    TMEM allocation (both CTAs), then MMA issue (rank 0; warp-collective, one elected lane)
+//   warp  5    TMA producer (one lane): a ring of 6 stages of A (16 KB) and B (16 KB) tiles
 // Two accumulators of 256 columns (all 512 TMEM columns): the MMAs of the next tile run while the
 // epilogue drains the previous one.
 // Operand tiles in shared memory use the 128-byte swizzle. An operand whose contraction index runs
-// along its memory rows (K-major: A of NN/NT, B of NT) is one TMA box of 64 k x (128 | 256) rows;
+// along its memory rows (K-major: A of NN/NT, B of NT) is one TMA box of 64 k x 128 rows;
 // one whose contraction index runs across rows (MN-major: A of TN, B of NN/TN) is stored as
 // sub-tiles of 64 k-rows x 64 columns, 8 KB apart.
 #include "common.cuh"
@@ -27,8 +34,9 @@ namespace {
 
 using namespace ptx;
 
-constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
-constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int BM = 128, BN = 256, BK = 64, STAGES = 6;  // BM: rows per CTA; a pair covers 2 * BM
+constexpr int BNH = BN / 2;                             // B columns held by one CTA of a pair
+constexpr int A_BYTES = BM * BK * 2, B_BYTES = BNH * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int SUB_BYTES = 64 * 128;                   // 64 rows x 128 bytes
 constexpr int OFF_OUT = STAGES * STAGE_BYTES;         // 128 rows x 128 columns of bf16 for the epilogue
 constexpr int OFF_BIAS = OFF_OUT + BM * 128 * 2;      // 256 floats
@@ -93,7 +101,7 @@ struct BoxWalker {
     }
     __device__ __forceinline__ void load(uint32_t dst, const CUtensorMap *map, uint32_t bar) const
     {
-        tma_load_5d(dst, map, bar, c0, c1, c2, c3, c4);
+        tma_load_5d_pair(dst, map, bar, c0, c1, c2, c3, c4);
     }
 };
 
@@ -133,24 +141,26 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     float *bias_s = reinterpret_cast<float *>(smem_gen + OFF_BIAS);
 
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
-    const int num_tiles = p.tiles_m * p.tiles_n;
+    const int num_tiles = p.tiles_m * p.tiles_n;  // tiles of 2*BM x BN, one per CTA pair at a time
     const int kblocks = (p.k + BK - 1) / BK;
+    const uint32_t rank = cluster_ctarank();      // 0 issues the MMAs
+    const int pair = blockIdx.x / 2, npairs = gridDim.x / 2;
 
     if (threadIdx.x == 0) {
         *abort_flag = 0;
         for (int s = 0; s < STAGES; s++) {
-            mbar_init(BAR(B_FULL + s), 1);
-            mbar_init(BAR(B_EMPTY + s), 1);
+            mbar_init(BAR(B_FULL + s), 1);   // rank 0: its producer's arrive + the bytes of both CTAs
+            mbar_init(BAR(B_EMPTY + s), 1);  // one commit (delivered to both CTAs)
         }
         for (int b = 0; b < 2; b++) {
             mbar_init(BAR(B_ACCFULL + b), 1);
-            mbar_init(BAR(B_ACCEMPTY + b), 4);  // one arrival per epilogue warp
+            mbar_init(BAR(B_ACCEMPTY + b), 8);  // rank 0: one arrival per epilogue warp of both CTAs
         }
         fence_mbar_init();
     }
     if (warp == 4) {
-        tmem_alloc(smem_u32(tmem_slot), 512);
-        tmem_relinquish();
+        tmem_alloc_pair(smem_u32(tmem_slot), 512);
+        tmem_relinquish_pair();
     }
     if (warp == 5 && lane == 0) {
         prefetch_tensormap(&tm_a);
@@ -158,30 +168,32 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     }
     tc_fence_before();
     __syncthreads();
+    cluster_sync_all();  // both CTAs' barriers exist before either signals the other's
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
 
     if (warp == 5) {
         if (lane == 0) {
-            // ------------------------------------------------------------ TMA producer
+            // ------------------------------------------------------------ TMA producer (both CTAs)
             int it = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            for (int tile = pair; tile < num_tiles && ok; tile += npairs) {
                 int tm, tn;
                 tile_coords(p, tile, tm, tn);
-                constexpr int NA = MODE == GEMM_TN ? BM / 64 : 1, NB = MODE == GEMM_NT ? 1 : BN / 64;
+                const int m0 = tm * 2 * BM + (int)rank * BM, n0 = tn * BN + (int)rank * BNH;  // this CTA's A rows and B columns
+                constexpr int NA = MODE == GEMM_TN ? BM / 64 : 1, NB = MODE == GEMM_NT ? 1 : BNH / 64;
                 BoxWalker wa[NA], wb[NB];
 #pragma unroll
                 for (int sub = 0; sub < NA; sub++)  // TN: A view is (k x m), boxes of 64 k-rows x 64 m-columns
-                    wa[sub].init(p.a, MODE == GEMM_TN ? 0 : tm * BM, MODE == GEMM_TN ? tm * BM + sub * 64 : 0);
+                    wa[sub].init(p.a, MODE == GEMM_TN ? 0 : m0, MODE == GEMM_TN ? m0 + sub * 64 : 0);
 #pragma unroll
                 for (int sub = 0; sub < NB; sub++)  // NN, TN: B view is (k x n), boxes of 64 k-rows x 64 n-columns
-                    wb[sub].init(p.b, MODE == GEMM_NT ? tn * BN : 0, MODE == GEMM_NT ? 0 : tn * BN + sub * 64);
+                    wb[sub].init(p.b, MODE == GEMM_NT ? n0 : 0, MODE == GEMM_NT ? 0 : n0 + sub * 64);
                 for (int kb = 0; kb < kblocks; kb++, it++) {
                     const int s = it % STAGES;
                     if (!(ok = mbar_wait(BAR(B_EMPTY + s), ((it / STAGES) & 1) ^ 1, abort_flag, p.status, WG_EMPTY))) break;
                     const uint32_t a_dst = smem_base + s * STAGE_BYTES, b_dst = a_dst + A_BYTES;
-                    mbar_arrive_expect_tx(BAR(B_FULL + s), STAGE_BYTES);
+                    if (rank == 0) mbar_arrive_expect_tx(BAR(B_FULL + s), 2 * STAGE_BYTES);
 #pragma unroll
                     for (int sub = 0; sub < NA; sub++) {
                         wa[sub].load(a_dst + sub * SUB_BYTES, &tm_a, BAR(B_FULL + s));
@@ -194,48 +206,55 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                     }
                 }
             }
-            // Do not leave while a copy of this CTA is still landing in shared memory.
-            const long long t0 = clock64();
-            for (int j = max(0, it - STAGES); j < it; j++)
-                while (!mbar_try_wait(BAR(B_FULL + j % STAGES), (j / STAGES) & 1) && clock64() - t0 < kWaitLimitCycles) {}
+            // Do not leave while a copy of this pair is still landing in shared memory: rank 0's
+            // barriers count the bytes of both CTAs, and the cluster barrier below keeps rank 1 here
+            // until rank 0 has seen them.
+            if (rank == 0) {
+                const long long t0 = clock64();
+                for (int j = max(0, it - STAGES); j < it; j++)
+                    while (!mbar_try_wait(BAR(B_FULL + j % STAGES), (j / STAGES) & 1) && clock64() - t0 < kWaitLimitCycles) {}
+            }
         }
     } else if (warp == 4) {
-        // ---------------------------------------------------------------- MMA issue
-        constexpr uint32_t IDESC = idesc_bf16_f32(BM, BN, MODE == GEMM_TN ? 1 : 0, MODE == GEMM_NT ? 0 : 1);
-        constexpr uint32_t A_LBO = MODE == GEMM_TN ? SUB_BYTES : 16, A_STEP = (MODE == GEMM_TN ? 2048 : 32) >> 4;
-        constexpr uint32_t B_LBO = MODE == GEMM_NT ? 16 : SUB_BYTES, B_STEP = (MODE == GEMM_NT ? 32 : 2048) >> 4;
-        int it = 0, tcount = 0;
-        bool ok = true;
-        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, tcount++) {
-            const int buf = tcount & 1;
-            ok = ok && mbar_wait(BAR(B_ACCEMPTY + buf), ((tcount >> 1) & 1) ^ 1, abort_flag, p.status, WG_ACCEMPTY);
-            tc_fence_after();
-            for (int kb = 0; kb < kblocks; kb++, it++) {
-                const int s = it % STAGES;
-                ok = ok && mbar_wait(BAR(B_FULL + s), (it / STAGES) & 1, abort_flag, p.status, WG_FULL);
+        // ---------------------------------------------------------------- MMA issue (rank 0 for the pair)
+        if (rank == 0) {
+            constexpr uint32_t IDESC = idesc_bf16_f32(2 * BM, BN, MODE == GEMM_TN ? 1 : 0, MODE == GEMM_NT ? 0 : 1);
+            constexpr uint32_t A_LBO = MODE == GEMM_TN ? SUB_BYTES : 16, A_STEP = (MODE == GEMM_TN ? 2048 : 32) >> 4;
+            constexpr uint32_t B_LBO = MODE == GEMM_NT ? 16 : SUB_BYTES, B_STEP = (MODE == GEMM_NT ? 32 : 2048) >> 4;
+            int it = 0, tcount = 0;
+            bool ok = true;
+            for (int tile = pair; tile < num_tiles; tile += npairs, tcount++) {
+                const int buf = tcount & 1;
+                ok = ok && mbar_wait(BAR(B_ACCEMPTY + buf), ((tcount >> 1) & 1) ^ 1, abort_flag, p.status, WG_ACCEMPTY);
                 tc_fence_after();
-                const uint32_t a_lo = desc_lo(smem_base + s * STAGE_BYTES, A_LBO);
-                const uint32_t b_lo = desc_lo(smem_base + s * STAGE_BYTES + A_BYTES, B_LBO);
+                for (int kb = 0; kb < kblocks; kb++, it++) {
+                    const int s = it % STAGES;
+                    ok = ok && mbar_wait(BAR(B_FULL + s), (it / STAGES) & 1, abort_flag, p.status, WG_FULL);
+                    tc_fence_after();
+                    const uint32_t a_lo = desc_lo(smem_base + s * STAGE_BYTES, A_LBO);
+                    const uint32_t b_lo = desc_lo(smem_base + s * STAGE_BYTES + A_BYTES, B_LBO);
 #pragma unroll
-                for (int k16 = 0; k16 < BK / 16; k16++)
-                    mma_ss_lo(tmem + buf * BN, a_lo + k16 * A_STEP, b_lo + k16 * B_STEP, IDESC, (kb > 0 || k16 > 0) ? 1u : 0u);
-                tc_commit_elect(BAR(B_EMPTY + s));
+                    for (int k16 = 0; k16 < BK / 16; k16++)
+                        mma_ss_lo_pair(tmem + buf * BN, a_lo + k16 * A_STEP, b_lo + k16 * B_STEP, IDESC, (kb > 0 || k16 > 0) ? 1u : 0u);
+                    tc_commit_pair(BAR(B_EMPTY + s), 3);  // the stage is free in both CTAs
+                }
+                tc_commit_pair(BAR(B_ACCFULL + buf), 3);
             }
-            tc_commit_elect(BAR(B_ACCFULL + buf));
         }
     } else {
-        // -------------------------------------------------------------------- epilogue (warps 0-3)
-        const int r = threadIdx.x;  // row inside the tile == TMEM lane
+        // -------------------------------------------------------------------- epilogue (warps 0-3, both CTAs)
+        const int r = threadIdx.x;  // row inside this CTA's half of the tile == TMEM lane
         const uint32_t lane_sel = (uint32_t)(warp * 32) << 16;
         uint8_t *stage = smem_gen + OFF_OUT;
         __nv_bfloat16 *cptr = (__nv_bfloat16 *)p.c.ptr;
+        const uint32_t accempty0 = map_to_cta(BAR(B_ACCEMPTY), 0);  // rank 0's barriers, as cluster addresses
         int tcount = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, tcount++) {
+        for (int tile = pair; tile < num_tiles; tile += npairs, tcount++) {
             int tm, tn;
             tile_coords(p, tile, tm, tn);
             const int buf = tcount & 1;
-            const long long m0 = (long long)tm * BM;
+            const long long m0 = (long long)tm * 2 * BM + (long long)rank * BM;
             const int n0 = tn * BN;
             named_bar_sync(1, 128);  // the previous tile's bias has been read by every thread
             for (int j = r; j < BN; j += 128)
@@ -254,7 +273,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                     if (half == 1 && ch == 3) {  // the accumulator is in registers: the next tile may use it
                         tc_fence_before();
                         __syncwarp();
-                        if (lane == 0) mbar_arrive(BAR(B_ACCEMPTY + buf));
+                        if (lane == 0) mbar_arrive_cluster(accempty0 + 8u * (uint32_t)buf);
                     }
                     const float *bs = bias_s + half * 128 + ch * 32;
 #pragma unroll
@@ -288,7 +307,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
 
     tc_fence_before();
     __syncthreads();
-    if (warp == 4) tmem_dealloc(tmem, 512);
+    cluster_sync_all();  // neither CTA leaves while the other may still signal its barriers or use the shared allocation
+    if (warp == 4) tmem_dealloc_pair(tmem, 512);
 }
 
 bool view_ok(const MatView &v, int row_box)
@@ -305,12 +325,12 @@ int launch(const GemmArgs &g, DeviceState *st, cudaStream_t s)
     CUtensorMap ta, tb;
     int rc;
     if ((rc = make_tensor_map_bf16_view(&ta, g.a, 64, MODE == GEMM_TN ? 64 : BM)) != EMBER_OK) return rc;
-    if ((rc = make_tensor_map_bf16_view(&tb, g.b, 64, MODE == GEMM_NT ? BN : 64)) != EMBER_OK) return rc;
+    if ((rc = make_tensor_map_bf16_view(&tb, g.b, 64, MODE == GEMM_NT ? BNH : 64)) != EMBER_OK) return rc;
     GemmParams p;
     p.m = g.m;
     p.n = g.n;
     p.k = g.k;
-    p.tiles_m = (int)((g.m + BM - 1) / BM);
+    p.tiles_m = (int)((g.m + 2 * BM - 1) / (2 * BM));
     p.tiles_n = (g.n + BN - 1) / BN;
     p.a = {g.a.heads, g.a.seq, g.a.dim};
     p.b = {g.b.heads, g.b.seq, g.b.dim};
@@ -321,9 +341,20 @@ int launch(const GemmArgs &g, DeviceState *st, cudaStream_t s)
     EMBER_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
     const long long tiles = (long long)p.tiles_m * p.tiles_n;
     const int sms = st->sm_count > 0 ? st->sm_count : 148;
-    const int grid = (int)(tiles < sms ? tiles : sms);
-    kern<<<grid, GEMM_THREADS, SMEM_BYTES, s>>>(ta, tb, p);
-    EMBER_CUDA_TRY(cudaGetLastError());
+    const int pairs = (int)(tiles < sms / 2 ? tiles : sms / 2);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * pairs);
+    cfg.blockDim = dim3(GEMM_THREADS);
+    cfg.dynamicSmemBytes = SMEM_BYTES;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;  // consecutive CTAs 2i, 2i+1 form a pair
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    EMBER_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, ta, tb, p));
     return EMBER_OK;
 }
 
@@ -333,10 +364,10 @@ bool sm100_gemm_supported(const GemmArgs &g)
 {
     if (g.dtype != EMBER_BF16 || g.m <= 0 || g.n <= 0 || g.k <= 0) return false;
     if (g.m > 0x7fffff00LL || g.a.rows > 0x7fffff00LL || g.b.rows > 0x7fffff00LL) return false;  // 32-bit box coordinates
-    if ((g.m + BM - 1) / BM * (long long)((g.n + BN - 1) / BN) > 0x7fffffffLL) return false;
+    if ((g.m + 2 * BM - 1) / (2 * BM) * (long long)((g.n + BN - 1) / BN) > 0x7fffffffLL) return false;
     if (g.n % 8 != 0 || ((uintptr_t)g.c.ptr & 15) != 0) return false;       // 16-byte output chunks
     if (g.c.heads > 0 && g.c.dim % 8 != 0) return false;
-    const int a_rows = g.mode == GEMM_TN ? 64 : BM, b_rows = g.mode == GEMM_NT ? BN : 64;
+    const int a_rows = g.mode == GEMM_TN ? 64 : BM, b_rows = g.mode == GEMM_NT ? BNH : 64;
     return view_ok(g.a, a_rows) && view_ok(g.b, b_rows);
 }
 

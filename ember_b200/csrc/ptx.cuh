@@ -312,6 +312,90 @@ __device__ __forceinline__ void mma_ts_lo(uint32_t d_tmem, uint32_t a_tmem, uint
         : "memory");
 }
 
+// ---------------------------------------------------------------- CTA pairs (cta_group::2)
+// Two CTAs of a cluster (ranks 0 and 1, on the two SMs of one TPC) act as one 256-row MMA: rank 0
+// issues, each CTA supplies its own 128 rows of A and its own half of B's N columns from its own
+// shared memory, and each CTA's tensor memory receives its 128 rows of the result. Every CTA loads
+// its own operands with its own TMA copies (no multicast); the completion bytes of both CTAs are
+// counted by rank 0's barrier.
+__device__ __forceinline__ uint32_t cluster_ctarank()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Address of the same shared-memory location in the CTA of the given rank of this cluster.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank)
+{
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr)
+{
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// In the shared::cluster window the rank of the owning CTA is bit 24 of an address; clearing it
+// turns the address of a barrier in this CTA into the address of the same barrier in rank 0.
+constexpr uint32_t kPeerBitMask = 0xFEFFFFFFu;
+// 5-D tile load of one CTA of a pair into its OWN shared memory; the bytes are reported to rank 0's
+// barrier at the same offset.
+__device__ __forceinline__ void tma_load_5d_pair(uint32_t dst_smem, const CUtensorMap *m, uint32_t bar, int c0, int c1,
+                                                 int c2, int c3, int c4)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.5d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+        ::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar & kPeerBitMask), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
+        : "memory");
+}
+// Tensor-memory allocation of a CTA pair: one warp of EACH CTA (the same warp index) executes it,
+// with the same destination offset.
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t dst_smem, uint32_t ncols)
+{
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair()
+{
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols)
+{
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// Warp-collective (rank 0 only): D[tmem of both CTAs] (+)= A[smem of both] * B[smem of both].
+__device__ __forceinline__ void mma_ss_lo_pair(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n"
+        ".reg .pred p, q;\n"
+        ".reg .b64 da, db;\n"
+        "elect.sync _|q, 0xffffffff;\n"
+        "mov.b64 da, {%1, %5};\n"
+        "mov.b64 db, {%2, %5};\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "@q tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %3, p;\n"
+        "}\n"
+        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(kDescHiSw128)
+        : "memory");
+}
+// Warp-collective (rank 0 only): when every MMA issued before has finished, the barrier at this
+// offset receives one arrival in each CTA named in cta_mask (bit r = rank r).
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar, uint16_t cta_mask)
+{
+    asm volatile(
+        "{\n"
+        ".reg .pred q;\n"
+        "elect.sync _|q, 0xffffffff;\n"
+        "@q tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n"
+        "}\n" ::"r"(bar), "h"(cta_mask)
+        : "memory");
+}
+
 // Named barrier (ids 1..15; 0 is __syncthreads) over `count` threads, a multiple of 32.
 __device__ __forceinline__ void named_bar_sync(int id, int count)
 {
