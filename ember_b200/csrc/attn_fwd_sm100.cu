@@ -48,19 +48,31 @@ constexpr float LOG2E_F = 1.4426950408889634f;
 constexpr float LN2_F = 0.6931471805599453f;
 constexpr float RESCALE_THRESHOLD = 8.0f;  // log2 units
 
-template <int HD>
+// PAIR: two CTAs of a cluster work as one (cta_group::2). Each 256-row MMA covers one 128-row query
+// tile of each CTA; a CTA holds only HALF of every K tile (64 of its 128 keys) and half of every V
+// tile (64 of its HD columns) in shared memory and loads that half with its own TMA copies, so per
+// key tile an SM receives 32 KB instead of 64 KB and the score MMAs read 48 KB of operands per
+// 128x128x128 product instead of 64 KB. Shared memory moves 128 bytes per clock; the single-CTA
+// form needs about 125 of them at the full MMA rate, which is what held it near 2850 clocks per key
+// tile where the tensor core needs 2048.
+template <int HD, bool PAIR = false>
 struct FwdCfg {
     static constexpr int NSUB = HD / 64;                 // 64-column (128-byte) sub-tiles per tile
     static constexpr int SUB_BYTES = 128 * 128;          // 128 rows x 128 bytes
     static constexpr int TILE_BYTES = NSUB * SUB_BYTES;  // one 128 x HD bf16 tile
+    // what one CTA holds of a K tile (PAIR: 64 keys x HD as NSUB sub-tiles of 64 rows) and of a V
+    // tile (PAIR: 128 keys x 64 columns, one sub-tile)
+    static constexpr int K_SUB_BYTES = PAIR ? 64 * 128 : SUB_BYTES;
+    static constexpr int K_BYTES = NSUB * K_SUB_BYTES;
+    static constexpr int V_BYTES = PAIR ? SUB_BYTES : TILE_BYTES;
     // K(j) is released as soon as both score MMAs of step j are issued; V(j) stays in use until the
     // second tile's PV MMA one step later, so V gets the deeper ring.
-    static constexpr int KSTAGES = 2, VSTAGES = 3;
+    static constexpr int KSTAGES = PAIR ? 3 : 2, VSTAGES = PAIR ? 4 : 3;
     static constexpr int OFF_Q = 0;
     static constexpr int OFF_K = OFF_Q + 2 * TILE_BYTES;
-    static constexpr int OFF_V = OFF_K + KSTAGES * TILE_BYTES;
-    static constexpr int OFF_BAR = OFF_V + VSTAGES * TILE_BYTES;
-    static constexpr int USED_BYTES = OFF_BAR + 256;     // barriers + TMEM slot + abort flag
+    static constexpr int OFF_V = OFF_K + KSTAGES * K_BYTES;
+    static constexpr int OFF_BAR = OFF_V + VSTAGES * V_BYTES;
+    static constexpr int USED_BYTES = OFF_BAR + 320;     // barriers + TMEM slot + abort flag
     static constexpr int SMEM_BYTES = USED_BYTES + 1024; // + room to round the base up to 1024
     static constexpr int TMEM_P = 0, TMEM_S = 128, TMEM_O = 256;
     // barrier indices
@@ -96,12 +108,58 @@ struct FwdParams {
 
 // EMU: of every 4 pairs of exponentials, how many are evaluated as a polynomial on the FMA pipe
 // instead of the MUFU (0..4).
-template <int HD, int EMU>
+// MMA, commit, allocation and arrival forms of a single CTA or of a CTA pair.
+template <bool PAIR>
+__device__ __forceinline__ void f_mma_ss(uint32_t d, uint32_t a, uint32_t b, uint32_t idesc, uint32_t acc)
+{
+    if constexpr (PAIR) mma_ss_lo_pair(d, a, b, idesc, acc); else mma_ss_lo(d, a, b, idesc, acc);
+}
+__device__ __forceinline__ void mma_ts_lo_pair(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n"
+        ".reg .pred p, q;\n"
+        ".reg .b64 db;\n"
+        "elect.sync _|q, 0xffffffff;\n"
+        "mov.b64 db, {%2, %5};\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "@q tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], db, %3, p;\n"
+        "}\n"
+        ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(kDescHiSw128)
+        : "memory");
+}
+template <bool PAIR>
+__device__ __forceinline__ void f_mma_ts(uint32_t d, uint32_t a, uint32_t b, uint32_t idesc, uint32_t acc)
+{
+    if constexpr (PAIR) mma_ts_lo_pair(d, a, b, idesc, acc); else mma_ts_lo(d, a, b, idesc, acc);
+}
+template <bool PAIR>
+__device__ __forceinline__ void f_commit(uint32_t bar)  // PAIR: the barrier of BOTH CTAs gets the arrival
+{
+    if constexpr (PAIR) tc_commit_pair(bar, 3); else tc_commit_elect(bar);
+}
+// 3-D tile load of one CTA of a pair into its own shared memory, bytes reported to rank 0's barrier.
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst_smem, const CUtensorMap *m, uint32_t bar, int c0, int c1, int c2)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar & kPeerBitMask), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+template <bool PAIR>
+__device__ __forceinline__ void f_tma_3d(uint32_t dst, const CUtensorMap *m, uint32_t bar, int c0, int c1, int c2)
+{
+    if constexpr (PAIR) tma_load_3d_pair(dst, m, bar, c0, c1, c2); else tma_load_3d(dst, m, bar, c0, c1, c2);
+}
+
+template <int HD, int EMU, bool PAIR>
 __global__ void __launch_bounds__(FWD_THREADS, 1)
     sm100_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                      const __grid_constant__ CUtensorMap tm_v, const FwdParams p)
 {
-    using C = FwdCfg<HD>;
+    using C = FwdCfg<HD, PAIR>;
+    static_assert(!PAIR || HD == 128, "the pair form halves V along its 128 columns");
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -114,16 +172,21 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const uint32_t crank = PAIR ? cluster_ctarank() : 0u;  // rank 0 of a pair issues the MMAs
     int bh, rank;
-    work_item(p.order, blockIdx.x, bh, rank);
+    work_item(p.order, PAIR ? blockIdx.x / 2 : blockIdx.x, bh, rank);
     const int qblock = p.order.blocks - 1 - rank;  // heaviest (latest) causal rows first
-    const int q_base = qblock * 256;
+    // A CTA has two 128-row query tiles. Alone they are consecutive rows. In a pair the four tiles of
+    // a 512-row block alternate between the CTAs (rank r has tiles r and 2 + r), so that the two tiles
+    // multiplied by one 256-row MMA are neighbours and see the same key tiles but one under a mask.
+    const int q_base = PAIR ? qblock * 512 + (int)crank * 128 : qblock * 256;
+    constexpr int TSTEP = PAIR ? 256 : 128;        // rows from this CTA's tile 0 to its tile 1
     // which tensor slab the unit reads, where its keys start and how many it sees
     const int unit = p.splits > 1 ? bh / p.splits : bh;
     const int k_row0 = p.splits > 1 ? (bh - unit * p.splits) * p.chunk : 0;
     int lk = p.seq_lens ? min(p.lk, p.seq_lens[unit / p.lens_div]) : p.lk;
     lk = p.splits > 1 ? min(p.chunk, lk - k_row0) : lk;
-    if (lk <= 0) {
+    if (!PAIR && lk <= 0) {
         // An empty split (a sequence shorter than the others): its partial is "no weight". Every
         // thread leaves here, before any barrier or tensor-memory allocation exists. Without splits
         // the (empty) sequence's result is defined as zeros with lse = -inf.
@@ -140,11 +203,14 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
     int n_t[2];
 #pragma unroll
     for (int t = 0; t < 2; t++) {
-        const int qs = q_base + t * 128;
-        if (qs >= p.lq) {
+        // PAIR: both CTAs walk the key tiles of the later of the two paired tiles (the earlier one sees
+        // its last key tile fully masked), and a pair of tiles exists if its first tile does
+        const int qs_first = PAIR ? qblock * 512 + t * 256 : q_base + t * 128;
+        const int qs_last = PAIR ? qs_first + 128 : qs_first;
+        if (qs_first >= p.lq) {
             n_t[t] = 0;
         } else {
-            const int visible = p.causal ? min(lk, qs + 128 + off) : lk;
+            const int visible = p.causal ? min(lk, qs_last + 128 + off) : lk;
             n_t[t] = (visible + 127) / 128;
         }
     }
@@ -163,16 +229,21 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
         }
         for (int t = 0; t < 2; t++) {
             mbar_init(BAR(B_S + t), 1);
-            mbar_init(BAR(B_R + t), 4);          // one arrival per softmax warp
-            mbar_init(BAR(B_P + 2 * t), 4);      // first 64 keys of P written (one arrival per warp)
-            mbar_init(BAR(B_P + 2 * t + 1), 4);  // last 64 keys of P written
+            mbar_init(BAR(B_R + t), PAIR ? 8 : 4);          // one arrival per softmax warp (of both CTAs of a pair)
+            mbar_init(BAR(B_P + 2 * t), PAIR ? 8 : 4);      // first 64 keys of P written (one arrival per warp)
+            mbar_init(BAR(B_P + 2 * t + 1), PAIR ? 8 : 4);  // last 64 keys of P written
             mbar_init(BAR(B_O + t), 1);
         }
         fence_mbar_init();
     }
     if (warp == 11) {
-        tmem_alloc(smem_u32(tmem_slot), 512);
-        tmem_relinquish();
+        if constexpr (PAIR) {
+            tmem_alloc_pair(smem_u32(tmem_slot), 512);
+            tmem_relinquish_pair();
+        } else {
+            tmem_alloc(smem_u32(tmem_slot), 512);
+            tmem_relinquish();
+        }
     }
     if (warp == 10 && lane == 0) {
         prefetch_tensormap(&tm_q);
@@ -181,6 +252,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
     }
     tc_fence_before();
     __syncthreads();
+    if constexpr (PAIR) cluster_sync_all();  // both CTAs' barriers exist before either signals the other's
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
 
@@ -188,44 +260,56 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
         reg_dealloc_40();
         if (warp == 10 && lane == 0) {
             // ------------------------------------------------------------ TMA producer
+            // In a pair every CTA loads its own tiles; the bytes of both are counted by rank 0's
+            // barriers, whose expected total rank 0 announces.
+            constexpr int NCTA = PAIR ? 2 : 1;
             const int ntiles_q = (n_t[1] > 0) ? 2 : 1;
-            mbar_arrive_expect_tx(BAR(B_Q), ntiles_q * C::TILE_BYTES);
+            if (crank == 0) mbar_arrive_expect_tx(BAR(B_Q), NCTA * ntiles_q * C::TILE_BYTES);
             for (int t = 0; t < ntiles_q; t++)
                 for (int s = 0; s < C::NSUB; s++)
-                    tma_load_3d(smem_base + C::OFF_Q + t * C::TILE_BYTES + s * C::SUB_BYTES, &tm_q,
-                                BAR(B_Q), s * 64, q_base + t * 128, p.splits > 1 ? unit : bh);
+                    f_tma_3d<PAIR>(smem_base + C::OFF_Q + t * C::TILE_BYTES + s * C::SUB_BYTES, &tm_q,
+                                   BAR(B_Q), s * 64, q_base + t * TSTEP, p.splits > 1 ? unit : bh);
             int k_issued = 0, v_issued = 0;
             for (int j = 0; j < n; j++) {
                 const int ks = j % C::KSTAGES, vs = j % C::VSTAGES;
                 if (!mbar_wait(BAR(B_KEMPTY + ks), ((j / C::KSTAGES) & 1) ^ 1, abort_flag, p.status, W_TMA_KEMPTY)) break;
-                mbar_arrive_expect_tx(BAR(B_KFULL + ks), C::TILE_BYTES);
-                for (int s = 0; s < C::NSUB; s++)
-                    tma_load_3d(smem_base + C::OFF_K + ks * C::TILE_BYTES + s * C::SUB_BYTES, &tm_k,
-                                BAR(B_KFULL + ks), s * 64, k_row0 + j * 128, unit);
+                if (crank == 0) mbar_arrive_expect_tx(BAR(B_KFULL + ks), NCTA * C::K_BYTES);
+                for (int s = 0; s < C::NSUB; s++)  // PAIR: this CTA's 64 of the tile's 128 keys
+                    f_tma_3d<PAIR>(smem_base + C::OFF_K + ks * C::K_BYTES + s * C::K_SUB_BYTES, &tm_k,
+                                   BAR(B_KFULL + ks), s * 64, k_row0 + j * 128 + (PAIR ? (int)crank * 64 : 0), unit);
                 k_issued = j + 1;
                 if (!mbar_wait(BAR(B_VEMPTY + vs), ((j / C::VSTAGES) & 1) ^ 1, abort_flag, p.status, W_TMA_VEMPTY)) break;
-                mbar_arrive_expect_tx(BAR(B_VFULL + vs), C::TILE_BYTES);
-                for (int s = 0; s < C::NSUB; s++)
-                    tma_load_3d(smem_base + C::OFF_V + vs * C::TILE_BYTES + s * C::SUB_BYTES, &tm_v,
-                                BAR(B_VFULL + vs), s * 64, k_row0 + j * 128, unit);
+                if (crank == 0) mbar_arrive_expect_tx(BAR(B_VFULL + vs), NCTA * C::V_BYTES);
+                if constexpr (PAIR) {              // this CTA's 64 of the tile's 128 columns
+                    f_tma_3d<PAIR>(smem_base + C::OFF_V + vs * C::V_BYTES, &tm_v, BAR(B_VFULL + vs), (int)crank * 64,
+                                   k_row0 + j * 128, unit);
+                } else {
+                    for (int s = 0; s < C::NSUB; s++)
+                        tma_load_3d(smem_base + C::OFF_V + vs * C::V_BYTES + s * C::SUB_BYTES, &tm_v,
+                                    BAR(B_VFULL + vs), s * 64, k_row0 + j * 128, unit);
+                }
                 v_issued = j + 1;
             }
             // Do not leave the CTA while one of its own copies is still landing in shared memory:
             // a bounded poll (ignoring the abort flag; a copy that was issued always completes) on
             // the full-barrier of every stage still in flight.
-            const long long t0 = clock64();
-            for (int j = max(0, k_issued - C::KSTAGES); j < k_issued; j++)
-                while (!mbar_try_wait(BAR(B_KFULL + j % C::KSTAGES), (j / C::KSTAGES) & 1) &&
-                       clock64() - t0 < kWaitLimitCycles) {}
-            for (int j = max(0, v_issued - C::VSTAGES); j < v_issued; j++)
-                while (!mbar_try_wait(BAR(B_VFULL + j % C::VSTAGES), (j / C::VSTAGES) & 1) &&
-                       clock64() - t0 < kWaitLimitCycles) {}
-            while (!mbar_try_wait(BAR(B_Q), 0) && clock64() - t0 < kWaitLimitCycles) {}
-        } else if (warp == 8 || warp == 9) {  // all 32 lanes, converged; one elected lane issues
-            // ------------------------------------------------------------ MMA issue for tile t
+            // (In a pair rank 0's barriers count the copies of both CTAs, and the cluster barrier at the
+            // end keeps rank 1 resident until rank 0 has passed this point.)
+            if (crank == 0) {
+                const long long t0 = clock64();
+                for (int j = max(0, k_issued - C::KSTAGES); j < k_issued; j++)
+                    while (!mbar_try_wait(BAR(B_KFULL + j % C::KSTAGES), (j / C::KSTAGES) & 1) &&
+                           clock64() - t0 < kWaitLimitCycles) {}
+                for (int j = max(0, v_issued - C::VSTAGES); j < v_issued; j++)
+                    while (!mbar_try_wait(BAR(B_VFULL + j % C::VSTAGES), (j / C::VSTAGES) & 1) &&
+                           clock64() - t0 < kWaitLimitCycles) {}
+                while (!mbar_try_wait(BAR(B_Q), 0) && clock64() - t0 < kWaitLimitCycles) {}
+            }
+        } else if ((warp == 8 || warp == 9) && crank == 0) {  // all 32 lanes, converged; one elected lane issues
+            // ------------------------------------------------------------ MMA issue for tile t (of both CTAs of a pair)
             const int t = warp - 8;
-            constexpr uint32_t IDESC_S = idesc_bf16_f32(128, 128, 0, 0);
-            constexpr uint32_t IDESC_O = idesc_bf16_f32(128, HD, 0, 1);
+            constexpr uint32_t IDESC_S = idesc_bf16_f32(PAIR ? 256 : 128, 128, 0, 0);
+            constexpr uint32_t IDESC_O = idesc_bf16_f32(PAIR ? 256 : 128, HD, 0, 1);
             const int nt = n_t[t], no = n_t[1 - t];  // key tiles of this tile / of the other tile
             const uint32_t q_lo = desc_lo(smem_base + C::OFF_Q + t * C::TILE_BYTES, 16);
             bool ok = mbar_wait(BAR(B_Q), 0, abort_flag, p.status, W_MMA_Q);
@@ -244,33 +328,34 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
                         ok = ok && mbar_wait(BAR(B_R + 1), (j - 1) & 1, abort_flag, p.status, W_MMA_R);
                 }
                 tc_fence_after();
-                const uint32_t k_lo = desc_lo(smem_base + C::OFF_K + (j % C::KSTAGES) * C::TILE_BYTES, 16);
+                const uint32_t k_lo = desc_lo(smem_base + C::OFF_K + (j % C::KSTAGES) * C::K_BYTES, 16);
 #pragma unroll
                 for (int ks = 0; ks < HD / 16; ks++) {
                     const uint32_t o16 = ((ks / 4) * C::SUB_BYTES + (ks % 4) * 32) >> 4;
-                    mma_ss_lo(tmem + C::TMEM_S, q_lo + o16, k_lo + o16, IDESC_S, ks > 0);
+                    const uint32_t k16 = ((ks / 4) * C::K_SUB_BYTES + (ks % 4) * 32) >> 4;
+                    f_mma_ss<PAIR>(tmem + C::TMEM_S, q_lo + o16, k_lo + k16, IDESC_S, ks > 0);
                 }
-                tc_commit_elect(BAR(B_S + t));
+                f_commit<PAIR>(BAR(B_S + t));
             };
             // O_t += P_t(j) V_j for keys [64*half, 64*half + 64) of the tile
             auto issue_pv_half = [&](int j, int half) {
                 ok = ok && mbar_wait(BAR(B_P + 2 * t + half), j & 1, abort_flag, p.status, W_MMA_P);
                 tc_fence_after();
-                const uint32_t v_lo = desc_lo(smem_base + C::OFF_V + (j % C::VSTAGES) * C::TILE_BYTES, C::SUB_BYTES);
+                const uint32_t v_lo = desc_lo(smem_base + C::OFF_V + (j % C::VSTAGES) * C::V_BYTES, C::SUB_BYTES);
 #pragma unroll
                 for (int k4 = 0; k4 < 4; k4++) {
                     const int ks = half * 4 + k4;
-                    mma_ts_lo(tmem + C::TMEM_O + t * HD, tmem + C::TMEM_P + t * 64 + ks * 8, v_lo + ks * (2048 >> 4),
-                              IDESC_O, (j > 0 || ks > 0) ? 1u : 0u);
+                    f_mma_ts<PAIR>(tmem + C::TMEM_O + t * HD, tmem + C::TMEM_P + t * 64 + ks * 8, v_lo + ks * (2048 >> 4),
+                                   IDESC_O, (j > 0 || ks > 0) ? 1u : 0u);
                 }
-                if (half == 1) tc_commit_elect(BAR(B_O + t));
+                if (half == 1) f_commit<PAIR>(BAR(B_O + t));
             };
             // Both MMA warps release every K and V stage (the "empty" barriers count two commits), also
             // for key tiles this query tile does not visit; a warp waits for the stage to be full
             // before it commits, so that its arrival can never land in an earlier phase of the barrier.
             ok = ok && mbar_wait(BAR(B_KFULL + 0), 0, abort_flag, p.status, W_MMA_K);
             if (nt > 0) issue_s(0);
-            tc_commit_elect(BAR(B_KEMPTY + 0));
+            f_commit<PAIR>(BAR(B_KEMPTY + 0));
             // Step j of this tile: S_t(j+1), then the two halves of PV_t(j). The score MMA comes
             // first: its buffer is free (the other tile copied out) about half a period before this
             // tile's probabilities are ready.
@@ -279,16 +364,16 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
                     ok = ok && mbar_wait(BAR(B_KFULL + (j + 1) % C::KSTAGES), ((j + 1) / C::KSTAGES) & 1, abort_flag,
                                          p.status, W_MMA_K);
                     if (j + 1 < nt) issue_s(j + 1);
-                    tc_commit_elect(BAR(B_KEMPTY + (j + 1) % C::KSTAGES));  // our reads of K(j+1) are issued
+                    f_commit<PAIR>(BAR(B_KEMPTY + (j + 1) % C::KSTAGES));  // our reads of K(j+1) are issued
                 }
                 ok = ok && mbar_wait(BAR(B_VFULL + j % C::VSTAGES), (j / C::VSTAGES) & 1, abort_flag, p.status, W_MMA_V);
-                if (p.seq_lens && j < nt && j * 128 + 128 > lk) {
+                if (!PAIR && p.seq_lens && j < nt && j * 128 + 128 > lk) {
                     // Cache decode with a per-sequence length below the tensor map's extent: TMA only
                     // zero-fills rows past the MAP's end, so V rows [lk, ...) of this tile hold whatever
                     // the cache holds there, and 0 * Inf (or NaN) would poison the product although
                     // their probabilities are exactly zero. Zero those rows in shared memory (a row is
                     // 128 bytes of each 64-column sub-tile; the swizzle only permutes inside a row).
-                    uint8_t *vt = smem_gen + C::OFF_V + (j % C::VSTAGES) * C::TILE_BYTES;
+                    uint8_t *vt = smem_gen + C::OFF_V + (j % C::VSTAGES) * C::V_BYTES;
                     const int r0 = lk - j * 128;
                     for (int i = lane; i < (128 - r0) * C::NSUB * 8; i += 32) {
                         const int rr = r0 + i / (C::NSUB * 8), sub = (i / 8) % C::NSUB, ch = i % 8;
@@ -301,7 +386,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
                     issue_pv_half(j, 0);
                     issue_pv_half(j, 1);
                 }
-                tc_commit_elect(BAR(B_VEMPTY + j % C::VSTAGES));  // our reads of V(j) are issued
+                f_commit<PAIR>(BAR(B_VEMPTY + j % C::VSTAGES));  // our reads of V(j) are issued
             }
         }
     } else {
@@ -309,7 +394,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
         reg_alloc_232();
         const int t = warp / 4;                   // which query tile
         const int r = threadIdx.x % 128;          // row inside the tile == TMEM lane
-        const int row = q_base + t * 128 + r;     // query row
+        const int row = q_base + t * TSTEP + r;   // query row
         const uint32_t lane_sel = (uint32_t)((warp % 4) * 32) << 16;
         const uint32_t ts = tmem + lane_sel + C::TMEM_S;           // the shared score buffer
         const uint32_t tp = tmem + lane_sel + C::TMEM_P + t * 64;  // this tile's probabilities
@@ -317,7 +402,13 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
         const int nk = n_t[t];
         const float c = p.scale_log2;
         const int limit_row = p.causal ? min(lk - 1, row + off) : lk - 1;
-        const int limit_tile = p.causal ? min(lk - 1, q_base + t * 128 + off) : lk - 1;
+        const int limit_tile = p.causal ? min(lk - 1, q_base + t * TSTEP + off) : lk - 1;
+        // where this warp reports "scores read" and "P written": the issuing CTA's barriers
+        const uint32_t bar_r = PAIR ? map_to_cta(BAR(B_R + t), 0) : BAR(B_R + t);
+        const uint32_t bar_p = PAIR ? map_to_cta(BAR(B_P + 2 * t), 0) : BAR(B_P + 2 * t);
+        auto arrive = [&](uint32_t bar) {
+            if constexpr (PAIR) mbar_arrive_cluster(bar); else mbar_arrive(bar);
+        };
 
         float m_ref = -INFINITY, l = 0.f;
         bool ok = true;
@@ -336,7 +427,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
             // The scores are in registers: hand the buffer to the other tile.
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(BAR(B_R + t));
+            if (lane == 0) arrive(bar_r);
 
             if (j * 128 + 127 > limit_tile) {
 #pragma unroll
@@ -425,7 +516,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
                 tmem_wait_st();
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(BAR(B_P + 2 * t + half));
+                if (lane == 0) arrive(bar_p + 8u * (uint32_t)half);
             }
             {
                 float a0, a1;
@@ -474,7 +565,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
                     const int rr = wrow0 + it * ROWS_PER_ST + lane / CHUNKS;
                     const int sw = (chunk & ~7) | ((chunk ^ rr) & 7);
                     const uint4 wv = *reinterpret_cast<const uint4 *>(stage + rr * ROWB + sw * 16);
-                    const int grow = q_base + t * 128 + rr;
+                    const int grow = q_base + t * TSTEP + rr;
                     if (ok && grow < p.lq)
                         *reinterpret_cast<uint4 *>(p.out + ((size_t)bh * p.lq + grow) * HD + chunk * 8) = wv;
                 }
@@ -485,7 +576,53 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
 
     tc_fence_before();
     __syncthreads();
-    if (warp == 11) tmem_dealloc(tmem, 512);
+    if constexpr (PAIR) {
+        cluster_sync_all();  // neither CTA leaves while the other may still signal its barriers
+        if (warp == 11) tmem_dealloc_pair(tmem, 512);
+    } else {
+        if (warp == 11) tmem_dealloc(tmem, 512);
+    }
+}
+
+template <int HD, int EMU>
+int launch_pair(const AttnArgs &a, DeviceState *st, cudaStream_t s)
+{
+    using C = FwdCfg<HD, true>;
+    CUtensorMap tq, tk, tv;
+    int rc;
+    if ((rc = make_tensor_map_bf16_3d(&tq, a.q, HD, a.lq, a.bh, 64, 128)) != EMBER_OK) return rc;
+    if ((rc = make_tensor_map_bf16_3d(&tk, a.k, HD, a.lk, a.bh, 64, 64)) != EMBER_OK) return rc;   // half a key tile per CTA
+    if ((rc = make_tensor_map_bf16_3d(&tv, a.v, HD, a.lk, a.bh, 64, 128)) != EMBER_OK) return rc;  // half the columns per CTA
+    FwdParams p;
+    p.out = (__nv_bfloat16 *)a.out;
+    p.lse = a.lse;
+    p.lq = a.lq;
+    p.lk = a.lk;
+    p.causal = a.causal;
+    p.scale_log2 = a.scale * LOG2E_F;
+    p.status = st->status;
+    p.splits = 1;
+    p.chunk = a.lk;
+    p.lens_div = 1;
+    p.seq_lens = nullptr;
+    auto kern = sm100_fwd_kernel<HD, EMU, true>;
+    EMBER_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+    // a work item is a 512-row block of one unit, taken by one pair of CTAs
+    p.order = make_work_order(a.bh, (a.lq + 511) / 512, st->sm_count / 2, ((size_t)a.lq + a.lk) * HD * 2 * 2, a.causal != 0);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2u * (unsigned)(p.order.units * p.order.blocks));
+    cfg.blockDim = dim3(FWD_THREADS);
+    cfg.dynamicSmemBytes = C::SMEM_BYTES;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;  // consecutive CTAs 2i, 2i+1 form a pair
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    EMBER_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, tq, tk, tv, p));
+    return EMBER_OK;
 }
 
 template <int HD, int EMU>
@@ -509,7 +646,7 @@ int launch(const AttnArgs &a, DeviceState *st, cudaStream_t s)
     p.chunk = a.lk;
     p.lens_div = 1;
     p.seq_lens = nullptr;
-    auto kern = sm100_fwd_kernel<HD, EMU>;
+    auto kern = sm100_fwd_kernel<HD, EMU, false>;
     EMBER_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
     p.order = make_work_order(a.bh, (a.lq + 255) / 256, st->sm_count, ((size_t)a.lq + a.lk) * HD * 2 * 2,  // Q, O, K, V
                               a.causal != 0);
@@ -573,7 +710,7 @@ int launch_cache_decode(const CacheDecodeArgs &a, DeviceState *st, cudaStream_t 
     p.lens_div = a.kv_heads;
     p.seq_lens = a.seq_lens;
     p.order = make_work_order(units * a.splits, 1, st->sm_count, 1, false);
-    auto kern = sm100_fwd_kernel<HD, 1>;
+    auto kern = sm100_fwd_kernel<HD, 1, false>;
     EMBER_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
     kern<<<(unsigned)(units * a.splits), FWD_THREADS, C::SMEM_BYTES, s>>>(tq, tk, tv, p);
     EMBER_CUDA_TRY(cudaGetLastError());
@@ -609,10 +746,32 @@ static int fwd_emu_setting()
     return v;
 }
 
+// EMBER_FWD_PAIR=1 sends D = 128 shapes with more than 256 query rows to the CTA-pair form of the
+// kernel (read once). It is off by default: the pair form halves the shared-memory traffic per SM, but
+// one thread issues the MMAs of both CTAs, so every hand-over between the second CTA's softmax warps
+// and the issuing warp (scores read, P written, scores ready, PV done) crosses SMs, and with ONE score
+// buffer ping-ponged between the tiles those latencies sit on the critical path: it measured 0.75x
+// (no mask) and 0.67x (causal) of the single-CTA kernel at B4 H32 L4096 D128.
+static bool fwd_pair_enabled()
+{
+    static int v = -1;
+    if (v < 0) {
+        const char *e = getenv("EMBER_FWD_PAIR");
+        v = (e && e[0] == '1') ? 1 : 0;
+    }
+    return v != 0;
+}
+
 int sm100_attention_fwd(const AttnArgs &a, DeviceState *st, cudaStream_t s)
 {
     const int emu = fwd_emu_setting();
     if (a.d == 128) {
+        // CTA pairs take 512-row blocks; below three query tiles a pair would mostly idle
+        if (a.lq > 256 && fwd_pair_enabled()) {
+            if (emu == 0) return launch_pair<128, 0>(a, st, s);
+            if (emu == 2) return launch_pair<128, 2>(a, st, s);
+            return launch_pair<128, 1>(a, st, s);
+        }
         if (emu == 0) return launch<128, 0>(a, st, s);
         if (emu == 2) return launch<128, 2>(a, st, s);
         return launch<128, 1>(a, st, s);

@@ -77,6 +77,9 @@ TC_SHAPES = [
     (1, 1, 128, 128, 128), (1, 2, 256, 256, 128), (2, 2, 512, 512, 128), (1, 1, 384, 384, 64),
     (1, 3, 100, 100, 128), (1, 2, 129, 300, 128), (1, 1, 1, 257, 128), (1, 2, 300, 1000, 64),
     (1, 1, 257, 257, 128), (1, 2, 1024, 1024, 128),
+    # more than 256 query rows at D = 128 (the shapes the optional CTA-pair kernel takes: 512-row
+    # blocks that are full, partly filled and missing a whole tile)
+    (1, 2, 700, 700, 128), (1, 1, 513, 900, 128), (2, 2, 1100, 1100, 128), (1, 3, 384, 640, 128), (1, 1, 2048, 2048, 128),
 ]
 
 
@@ -277,3 +280,30 @@ def test_forward_over_host_tensors_equals_device_path():
     with pytest.raises(ValueError):
         _lib.check(L.ember_attention_fwd_host(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), None, 0, 1, 1, 8, 1.0, 0,
                                               _lib.EMBER_F32))
+
+
+def test_bf16_forward_cta_pair_kernel_in_a_subprocess():
+    """The optional CTA-pair form of the forward kernel (EMBER_FWD_PAIR=1, read once per process, hence
+    the child process) against the oracle on full, partly filled and ragged 512-row blocks."""
+    import os
+    import subprocess
+    import sys
+
+    code = r"""
+import sys, numpy as np
+sys.path.insert(0, sys.argv[1]); sys.path.insert(0, sys.argv[1] + "/tests")
+import ember_b200 as em
+from conftest import bf16_round, seeded
+from oracle import cpu_oracle
+for (B, H, Lq, Lk, D) in [(1, 2, 700, 700, 128), (1, 1, 513, 900, 128), (1, 3, 384, 640, 128), (1, 1, 2048, 2048, 128)]:
+    for causal in (False, True):
+        q, k, v = (bf16_round(seeded((B, H, L, D), s, 0.5)) for L, s in ((Lq, 1), (Lk, 2), (Lk, 3)))
+        ro, rl = cpu_oracle.attention_fwd(q, k, v, None, causal)
+        o, lse = em.attention_forward(*(em.Tensor(x, "bfloat16") for x in (q, k, v)), None, causal)
+        assert np.abs(o.to_np() - ro).max() <= 2e-2 and np.abs(lse.to_np() - rl).max() <= 2e-2, (Lq, Lk, causal)
+print("pair ok")
+"""
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, EMBER_FWD_PAIR="1")
+    r = subprocess.run([sys.executable, "-c", code, root], env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "pair ok" in r.stdout, r.stdout + r.stderr
