@@ -824,14 +824,6 @@ struct SpParams {
     WorkOrder order;
 };
 
-// Adds four float32 values to four consecutive accumulator words (16-byte aligned) in global memory.
-__device__ __forceinline__ void red_add_f32x4(float *gdst, uint32_t a, uint32_t b, uint32_t c, uint32_t d)
-{
-    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(gdst), "f"(__uint_as_float(a)), "f"(__uint_as_float(b)),
-                 "f"(__uint_as_float(c)), "f"(__uint_as_float(d))
-                 : "memory");
-}
-
 __device__ __forceinline__ void bulk_reduce_add_f32(float *gdst, uint32_t smem_src, uint32_t bytes)
 {
     asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;" ::"l"(gdst), "r"(smem_src),
@@ -841,10 +833,6 @@ __device__ __forceinline__ void bulk_reduce_add_f32(float *gdst, uint32_t smem_s
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_read_1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-
-#ifndef BWD_RED_CHUNKS
-#define BWD_RED_CHUNKS 0  // of the HD/32 column chunks of a dQ row, how many are added straight from registers
-#endif
 
 #ifdef EMBER_BWD_TRACE
 // Development aid (not compiled into the library): one CTA records clock64() at the hand-over points
@@ -924,7 +912,7 @@ __global__ void __launch_bounds__(SP_THREADS, 1)
 
     if (warp >= W_DRAIN0) {
         // -------------------------------------------------------------------- drain dQ(i)
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 136;");  // holds a whole 128-column row of dQ(i)
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 88;");  // holds half a row (64 columns) of dQ(i) at a time
         const int w = warp - W_DRAIN0;  // == warp % 4: the tensor-memory lane quarter this warp may read
         const uint32_t t_dq = tmem + ((uint32_t)(w * 32) << 16) + C::T_DP;
         uint8_t *stage = smem_gen + C::OFF_STAGE + w * C::STAGE_WARP_BYTES;
@@ -936,41 +924,37 @@ __global__ void __launch_bounds__(SP_THREADS, 1)
             tc_fence_after();
             if (w == 0 && lane == 0) TR(16, i);
             float *gdst = p.dq_acc + ((((size_t)bh * nqt + (i_begin + i)) * 4 + w) * (HD / 32)) * 1024;
-            // The whole row leaves tensor memory at once, so that dP^T(i+1) can overwrite it while the
-            // chunks go through the staging buffers.
-            uint32_t u[HD / 32][32];
+            // The row leaves tensor memory in two halves of 64 columns (the registers of these warps are
+            // what the compute warps do not get); dP^T(i+1) may overwrite it once the second half is read.
 #pragma unroll
-            for (int c = 0; c < HD / 32; c++) tmem_ld_32x32b_x32(t_dq + c * 32, u[c]);
-            tmem_wait_ld();
-            warp_arrive(BAR(C::B_DQFREE), lane);
-            if (w == 0 && lane == 0) TR(17, i);
+            for (int hf = 0; hf < HD / 64; hf++) {
+                uint32_t u[2][32];
+                tmem_ld_32x32b_x32(t_dq + hf * 64, u[0]);
+                tmem_ld_32x32b_x32(t_dq + hf * 64 + 32, u[1]);
+                tmem_wait_ld();
+                if (hf == HD / 64 - 1) {
+                    warp_arrive(BAR(C::B_DQFREE), lane);
+                    if (w == 0 && lane == 0) TR(17, i);
+                }
 #pragma unroll
-            for (int c = 0; c < HD / 32; c++) {
-                if (c < BWD_RED_CHUNKS) {
-                    // one instruction adds 32 lanes x 16 bytes = 512 consecutive bytes of the accumulator
-                    if (ok) {
+                for (int c2 = 0; c2 < 2; c2++) {
+                    const int c = hf * 2 + c2;
+                    // the bulk operation that read this buffer two chunks ago must be done with it
+                    if (lane == 0) bulk_wait_read_1();
+                    __syncwarp();
+                    uint8_t *buf = stage + (cnt & 1) * 4096;
 #pragma unroll
-                        for (int cg = 0; cg < 8; cg++)
-                            red_add_f32x4(gdst + c * 1024 + cg * 128 + lane * 4, u[c][4 * cg], u[c][4 * cg + 1], u[c][4 * cg + 2],
-                                          u[c][4 * cg + 3]);
+                    for (int cg = 0; cg < 8; cg++)
+                        *reinterpret_cast<uint4 *>(buf + (cg * 32 + lane) * 16) =
+                            make_uint4(u[c2][4 * cg], u[c2][4 * cg + 1], u[c2][4 * cg + 2], u[c2][4 * cg + 3]);
+                    fence_proxy_async();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (ok) bulk_reduce_add_f32(gdst + c * 1024, stage_u32 + (cnt & 1) * 4096, 4096);
+                        bulk_commit();
                     }
-                    continue;
+                    cnt++;
                 }
-                // the bulk operation that read this buffer two chunks ago must be done with it
-                if (lane == 0) bulk_wait_read_1();
-                __syncwarp();
-                uint8_t *buf = stage + (cnt & 1) * 4096;
-#pragma unroll
-                for (int cg = 0; cg < 8; cg++)
-                    *reinterpret_cast<uint4 *>(buf + (cg * 32 + lane) * 16) =
-                        make_uint4(u[c][4 * cg], u[c][4 * cg + 1], u[c][4 * cg + 2], u[c][4 * cg + 3]);
-                fence_proxy_async();
-                __syncwarp();
-                if (lane == 0) {
-                    if (ok) bulk_reduce_add_f32(gdst + c * 1024, stage_u32 + (cnt & 1) * 4096, 4096);
-                    bulk_commit();
-                }
-                cnt++;
             }
         }
         if (lane == 0) bulk_wait_all();
@@ -1097,7 +1081,7 @@ __global__ void __launch_bounds__(SP_THREADS, 1)
         }
     } else {
         // -------------------------------------------------------------------- compute
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 168;");  // 8 x 32 x 168 + 4 x 32 x 40 + 4 x 32 x 136 == 65536
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 192;");  // 8 x 32 x 192 + 4 x 32 x 40 + 4 x 32 x 88 == 65536
         const int h = warp / 4;                // which 64-column half of the 128 score columns (queries)
         const int r = threadIdx.x % 128;       // TMEM lane == key row inside the tile
         const int key = k0 + r;
