@@ -1193,33 +1193,72 @@ __global__ void __launch_bounds__(SP_THREADS, 1)
     if (warp == W_ALLOC) tmem_dealloc(tmem, 512);
 }
 
-// dq = bf16(scale * accumulator): one block per (unit, query tile), thread t owns row t of the tile
-// (lane quarter t / 32, lane t % 32 of the accumulator's block layout).
+// dq = bf16(scale * accumulator): one block per (unit, query tile, 32-column chunk), thread t owns row t of
+// the tile (lane quarter t / 32, lane t % 32 of the accumulator's block layout) and writes 64 bytes of it.
 template <int HD>
 __global__ void __launch_bounds__(128) dq_finish_kernel(const float *__restrict__ acc, __nv_bfloat16 *__restrict__ dq, int lq,
                                                         int nqt, float scale)
 {
     const size_t tile = blockIdx.x;  // unit * nqt + query tile
+    const int c = blockIdx.y;        // 32-column chunk
     const int qt = (int)(tile % nqt);
     const size_t unit = tile / nqt;
     const int w = threadIdx.x / 32, lane = threadIdx.x % 32;
     const int row = qt * 128 + threadIdx.x;
     if (row >= lq) return;
-    const float4 *src = reinterpret_cast<const float4 *>(acc + ((tile * 4 + w) * (HD / 32)) * 1024);
-    __nv_bfloat16 *dst = dq + (unit * lq + row) * HD;
+    const float4 *src = reinterpret_cast<const float4 *>(acc + ((tile * 4 + w) * (HD / 32) + c) * 1024);
+    float4 v[8];
 #pragma unroll
-    for (int c = 0; c < HD / 32; c++) {
+    for (int cg = 0; cg < 8; cg++) v[cg] = src[cg * 32 + lane];  // all eight loads in flight
+    __nv_bfloat16 *dst = dq + (unit * lq + row) * HD + c * 32;
 #pragma unroll
-        for (int cg = 0; cg < 8; cg += 2) {
-            const float4 a = src[c * 256 + cg * 32 + lane], b = src[c * 256 + (cg + 1) * 32 + lane];
-            uint4 o;
-            o.x = pack_bf16(a.x * scale, a.y * scale);
-            o.y = pack_bf16(a.z * scale, a.w * scale);
-            o.z = pack_bf16(b.x * scale, b.y * scale);
-            o.w = pack_bf16(b.z * scale, b.w * scale);
-            *reinterpret_cast<uint4 *>(dst + c * 32 + cg * 4) = o;
+    for (int cg = 0; cg < 8; cg += 2) {
+        uint4 o;
+        o.x = pack_bf16(v[cg].x * scale, v[cg].y * scale);
+        o.y = pack_bf16(v[cg].z * scale, v[cg].w * scale);
+        o.z = pack_bf16(v[cg + 1].x * scale, v[cg + 1].y * scale);
+        o.w = pack_bf16(v[cg + 1].z * scale, v[cg + 1].w * scale);
+        *reinterpret_cast<uint4 *>(dst + cg * 4) = o;
+    }
+}
+
+// delta[row] = sum_c dO[row][c] * O[row][c] for bf16 rows of HD elements: HD / 16 lanes per row, two
+// 16-byte loads per tensor and lane, 32 / (HD / 16) rows per warp.
+template <int HD>
+__global__ void __launch_bounds__(256) delta_bf16_kernel(const uint4 *__restrict__ out, const uint4 *__restrict__ dout,
+                                                         float *__restrict__ delta, size_t rows)
+{
+    constexpr int LPR = HD / 16, RPW = 32 / LPR;
+    const int lane = threadIdx.x % 32;
+    const size_t row = ((size_t)blockIdx.x * 8 + threadIdx.x / 32) * RPW + lane / LPR;
+    float s = 0.f;
+    if (row < rows) {
+        const size_t base = row * (HD / 8) + (lane % LPR) * 2;
+        const uint4 a[2] = {out[base], out[base + 1]}, b[2] = {dout[base], dout[base + 1]};
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const uint32_t x[4] = {a[h].x, a[h].y, a[h].z, a[h].w}, y[4] = {b[h].x, b[h].y, b[h].z, b[h].w};
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                s = fmaf(__uint_as_float(x[i] << 16), __uint_as_float(y[i] << 16), s);
+                s = fmaf(__uint_as_float(x[i] & 0xffff0000u), __uint_as_float(y[i] & 0xffff0000u), s);
+            }
         }
     }
+#pragma unroll
+    for (int o = LPR / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (row < rows && lane % LPR == 0) delta[row] = s;
+}
+
+template <int HD>
+int launch_delta_bf16(const AttnArgs &a, float *delta, cudaStream_t s)
+{
+    const size_t rows = (size_t)a.bh * a.lq;
+    constexpr int ROWS_PER_BLOCK = 8 * (32 / (HD / 16));
+    delta_bf16_kernel<HD><<<(unsigned)((rows + ROWS_PER_BLOCK - 1) / ROWS_PER_BLOCK), 256, 0, s>>>(
+        (const uint4 *)a.out, (const uint4 *)a.dout, delta, rows);
+    EMBER_CUDA_TRY(cudaGetLastError());
+    return EMBER_OK;
 }
 
 template <int HD>
@@ -1227,7 +1266,7 @@ int launch_fused(const AttnArgs &a, float *delta, float *dq_acc, DeviceState *st
 {
     using C = SpCfg<HD>;
     static_assert(NCW == 8, "the single-pass kernel is written for eight compute warps");
-    int rc = launch_delta(a, delta, s);
+    int rc = launch_delta_bf16<HD>(a, delta, s);
     if (rc) return rc;
     const int nqt = (a.lq + 127) / 128;
     EMBER_CUDA_TRY(cudaMemsetAsync(dq_acc, 0, (size_t)a.bh * nqt * 128 * HD * sizeof(float), s));
@@ -1254,7 +1293,7 @@ int launch_fused(const AttnArgs &a, float *delta, float *dq_acc, DeviceState *st
     p.order = make_work_order(a.bh, (a.lk + 127) / 128, st->sm_count, touched, a.causal != 0);
     k1<<<dim3((unsigned)(p.order.units * p.order.blocks)), SP_THREADS, C::SMEM_BYTES, s>>>(tq, tk, tv, tdo, p);
     EMBER_CUDA_TRY(cudaGetLastError());
-    dq_finish_kernel<HD><<<(unsigned)((size_t)a.bh * nqt), 128, 0, s>>>(dq_acc, (__nv_bfloat16 *)a.dq, a.lq, nqt, a.scale);
+    dq_finish_kernel<HD><<<dim3((unsigned)((size_t)a.bh * nqt), HD / 32), 128, 0, s>>>(dq_acc, (__nv_bfloat16 *)a.dq, a.lq, nqt, a.scale);
     EMBER_CUDA_TRY(cudaGetLastError());
     return EMBER_OK;
 }
@@ -1263,7 +1302,7 @@ template <int HD>
 int launch(const AttnArgs &a, float *delta, DeviceState *st, cudaStream_t s)
 {
     using C = BwdCfg<HD>;
-    int rc = launch_delta(a, delta, s);
+    int rc = launch_delta_bf16<HD>(a, delta, s);
     if (rc) return rc;
     CUtensorMap tq, tk, tv, tdo;
     if ((rc = make_tensor_map_bf16_3d(&tq, a.q, HD, a.lq, a.bh, 64, 128)) != EMBER_OK) return rc;
@@ -1306,7 +1345,7 @@ bool sm100_bwd_supported(const AttnArgs &a)
     if ((long long)a.bh * ((a.lq + 127) / 128) > 0x7fffffffLL || (long long)a.bh * ((a.lk + 127) / 128) > 0x7fffffffLL)
         return false;
     // TMA needs 16-byte aligned bases; the epilogues store 16-byte vectors.
-    const uintptr_t bits = (uintptr_t)a.q | (uintptr_t)a.k | (uintptr_t)a.v | (uintptr_t)a.dout |
+    const uintptr_t bits = (uintptr_t)a.q | (uintptr_t)a.k | (uintptr_t)a.v | (uintptr_t)a.dout | (uintptr_t)a.out |
                            (uintptr_t)a.dq | (uintptr_t)a.dk | (uintptr_t)a.dv;
     return (bits & 15) == 0;
 }
