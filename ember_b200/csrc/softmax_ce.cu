@@ -213,6 +213,106 @@ __global__ void __launch_bounds__(W < 256 ? 256 : W) row_softmax_kernel(const T 
     }
 }
 
+// The same three passes with the row held in REGISTERS: a thread loads its (at most 16) 16-byte pieces
+// of the row up front, all of them in flight at once, and maximum, sum and results are computed from
+// the registers. For rows of up to W x 256 bytes (W = 32: 8 KB, one warp per row and no block barrier;
+// W = 256: 64 KB) this replaces the shared-memory cache of row_softmax_kernel: there a thread has four
+// loads in flight during the first pass only, and nothing while it reduces and writes, which left the
+// kernels latency-bound at 0.5-0.75 of the copy bandwidth. Two blocks per SM (128 registers per thread)
+// so that one block's loads run under the other's arithmetic. 16-byte aligned rows only. MAXV: pieces
+// per thread (a power of two up to 16, the smallest that covers the row: loops over pieces that do not
+// exist would still cost their issue slots).
+template <typename T, int W, int MODE, int MAXV>
+__global__ void __launch_bounds__(256, 2) row_softmax_regs_kernel(const T *__restrict__ x, const T *__restrict__ target,
+                                                                   T *__restrict__ y, float *__restrict__ row_loss,
+                                                                   long long rows, int cols)
+{
+    __shared__ float red[32];
+    constexpr int GROUPS = 256 / W, NV = Vec16<T>::NV;
+    constexpr float kLog2e = 1.4426950408889634f;
+    const int group = threadIdx.x / W, t = threadIdx.x % W;
+    const int nvec = cols / NV;
+    for (long long row0 = (long long)blockIdx.x * GROUPS; row0 < rows; row0 += (long long)gridDim.x * GROUPS) {
+        const long long row = row0 + group;
+        const bool active = row < rows;  // W == 256: always true; W == 32: the whole warp agrees
+        const uint4 *xv = reinterpret_cast<const uint4 *>(x + (size_t)(active ? row : 0) * cols);
+        uint4 raw[MAXV];
+#pragma unroll
+        for (int i = 0; i < MAXV; i++) {
+            const int j = t + i * W;
+            if (active && j < nvec) raw[i] = xv[j];
+        }
+        // ---- maximum
+        float m = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < MAXV; i++) {
+            if (active && t + i * W < nvec) {
+                float v[NV];
+                Vec16<T>::unpack(raw[i], v);
+#pragma unroll
+                for (int k = 0; k < NV; k++) m = fmaxf(m, v[k]);
+            }
+        }
+        m = group_reduce<W, true>(m, red);
+        const float m2 = m * kLog2e;
+        // ---- sum of exp(x - max)
+        float s = 0.f;
+#pragma unroll
+        for (int i = 0; i < MAXV; i++) {
+            if (active && t + i * W < nvec) {
+                float v[NV];
+                Vec16<T>::unpack(raw[i], v);
+#pragma unroll
+                for (int k = 0; k < NV; k++) s += fast_exp2(fmaf(v[k], kLog2e, -m2));
+            }
+        }
+        s = group_reduce<W, false>(s, red);
+        // ---- results
+        const float inv = 1.f / s, lg = logf(s);
+        const float mlg2 = (m + lg) * kLog2e;  // exp(x - m - lg) = exp2(x * log2(e) - mlg2)
+        float loss = 0.f;
+        if (active) {
+            uint4 *yv = reinterpret_cast<uint4 *>(y + (size_t)row * cols);
+            const uint4 *tv4 = MODE == MODE_CROSS_ENTROPY ? reinterpret_cast<const uint4 *>(target + (size_t)row * cols) : nullptr;
+            // cross-entropy: the targets are fetched four pieces at a time (the registers hold the row)
+            constexpr int TB = MAXV < 4 ? MAXV : 4;
+#pragma unroll
+            for (int i0 = 0; i0 < MAXV; i0 += TB) {
+                uint4 traw[TB];
+                if (MODE == MODE_CROSS_ENTROPY) {
+#pragma unroll
+                    for (int i = 0; i < TB; i++)
+                        if (t + (i0 + i) * W < nvec) traw[i] = tv4[t + (i0 + i) * W];
+                }
+#pragma unroll
+                for (int i = 0; i < TB; i++) {
+                    const int j = t + (i0 + i) * W;
+                    if (j < nvec) {
+                        float v[NV], o[NV], tv[NV];
+                        Vec16<T>::unpack(raw[i0 + i], v);
+                        if (MODE == MODE_CROSS_ENTROPY) Vec16<T>::unpack(traw[i], tv);
+#pragma unroll
+                        for (int k = 0; k < NV; k++) {
+                            if (MODE == MODE_SOFTMAX) {
+                                o[k] = fast_exp2(fmaf(v[k], kLog2e, -m2)) * inv;
+                            } else {
+                                const float lp = (v[k] - m) - lg;
+                                o[k] = MODE == MODE_LOG_SOFTMAX ? lp : fast_exp2(fmaf(v[k], kLog2e, -mlg2));
+                                if (MODE == MODE_CROSS_ENTROPY) loss = fmaf(tv[k], lp, loss);
+                            }
+                        }
+                        yv[j] = Vec16<T>::pack(o);
+                    }
+                }
+            }
+        }
+        if (MODE == MODE_CROSS_ENTROPY) {
+            loss = group_reduce<W, false>(loss, red);
+            if (active && t == 0) row_loss[row] = loss;
+        }
+    }
+}
+
 // loss = -(sum of the row losses) / rows, added in a fixed order.
 __global__ void __launch_bounds__(BLOCK) loss_finalize_kernel(const float *row_loss, long long rows, float *loss)
 {
@@ -261,6 +361,27 @@ int launch_rows(const T *x, const T *target, T *y, float *row_loss, long long ro
     const bool vec = cols % NV == 0 && aligned16(x) && aligned16(y) && (MODE != MODE_CROSS_ENTROPY || aligned16(target));
     const size_t row_bytes = (size_t)cols * sizeof(T);
     const int width = row_bytes <= WARP_ROW_MAX_BYTES ? 32 : (row_bytes <= BLOCK_ROW_MAX_BYTES ? 256 : 1024);
+    if (vec && width <= 256) {  // the row fits the registers of the threads that own it
+        const int groups_r = 256 / width;
+        const long long need_r = (rows + groups_r - 1) / groups_r;
+        const long long cap_r = (long long)(sm_count > 0 ? sm_count : 148) * 16;
+        const int grid_r = (int)(need_r < cap_r ? need_r : cap_r);
+        const int pieces = (cols / NV + width - 1) / width;  // per thread, at most 16 here
+#define EMBER_LAUNCH_REGS(W, NP) row_softmax_regs_kernel<T, W, MODE, NP><<<grid_r, 256, 0, s>>>(x, target, y, row_loss, rows, cols)
+#define EMBER_LAUNCH_REGS_W(W)                    \
+    do {                                          \
+        if (pieces <= 1) EMBER_LAUNCH_REGS(W, 1); \
+        else if (pieces <= 2) EMBER_LAUNCH_REGS(W, 2); \
+        else if (pieces <= 4) EMBER_LAUNCH_REGS(W, 4); \
+        else if (pieces <= 8) EMBER_LAUNCH_REGS(W, 8); \
+        else EMBER_LAUNCH_REGS(W, 16);            \
+    } while (0)
+        if (width == 32) EMBER_LAUNCH_REGS_W(32); else EMBER_LAUNCH_REGS_W(256);
+#undef EMBER_LAUNCH_REGS_W
+#undef EMBER_LAUNCH_REGS
+        EMBER_CUDA_TRY(cudaGetLastError());
+        return EMBER_OK;
+    }
     const int block = width < 256 ? 256 : width, groups = block / width;
     // per-row cache, rounded up to 16 bytes so that every group's cache stays vector-aligned
     const int cache_elems = row_bytes <= CACHE_BYTES ? (int)(align_up(row_bytes, 16) / sizeof(T)) : 0;
