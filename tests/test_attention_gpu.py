@@ -80,6 +80,8 @@ TC_SHAPES = [
     # more than 256 query rows at D = 128 (the shapes the optional CTA-pair kernel takes: 512-row
     # blocks that are full, partly filled and missing a whole tile)
     (1, 2, 700, 700, 128), (1, 1, 513, 900, 128), (2, 2, 1100, 1100, 128), (1, 3, 384, 640, 128), (1, 1, 2048, 2048, 128),
+    # longer causal self-attention in a launch of less than one wave of CTAs
+    (1, 2, 1280, 1280, 64), (1, 3, 1536, 1536, 128),
 ]
 
 
