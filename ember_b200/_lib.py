@@ -11,7 +11,8 @@ import ctypes
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libember_b200.so")
+# EMBER_B200_LIB selects another build of the same library (the bounds-checked debug build, for one)
+LIB_PATH = os.environ.get("EMBER_B200_LIB") or os.path.join(_HERE, "libember_b200.so")
 
 EMBER_OK, EMBER_ERR_INVALID, EMBER_ERR_UNSUPPORTED, EMBER_ERR_CUDA = 0, 1, 2, 3
 EMBER_ERR_TIMEOUT, EMBER_ERR_NOMEM, EMBER_ERR_WORKSPACE = 4, 5, 6

@@ -84,5 +84,33 @@ def build_binding(force: bool = False) -> str:
     return out
 
 
+def build_bounds_checked() -> str:
+    """``libember_b200_dbg.so``: the same library with -DEMBER_BOUNDS_CHECK (every global store of the
+    tensor-core attention kernels checked against its tensor's extent; see csrc/common.cuh). Objects
+    go to build/dbg/. Select it at run time with EMBER_B200_LIB=<path>."""
+    obj = os.path.join(OBJ, "dbg")
+    os.makedirs(obj, exist_ok=True)
+    lib = os.path.join(HERE, "libember_b200_dbg.so")
+    hdr_t = _deps_mtime()
+    jobs, objs = [], []
+    for src in SOURCES:
+        s = os.path.join(CSRC, src)
+        o = os.path.join(obj, src.replace(".cu", ".o"))
+        objs.append(o)
+        if not os.path.exists(o) or os.path.getmtime(o) < max(os.path.getmtime(s), hdr_t):
+            jobs.append([_nvcc(), *NVCC_FLAGS, "-DEMBER_BOUNDS_CHECK", "-c", s, "-o", o])
+    for cmd in jobs:
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError("nvcc failed: %s\n%s" % (" ".join(cmd), r.stderr))
+    if jobs or not os.path.exists(lib):
+        r = subprocess.run([_nvcc(), "-shared", "-o", lib, *objs, "-cudart", "shared", "-ldl"], capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError("link failed: %s" % r.stderr)
+    return lib
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    if "--bounds" in sys.argv:
+        print(build_bounds_checked())

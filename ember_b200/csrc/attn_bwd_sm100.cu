@@ -243,9 +243,10 @@ __device__ __forceinline__ void stage_acc(uint32_t tacc, uint8_t *stage, int r, 
 // store_staged: after all compute threads have staged (caller synchronises), compute warp w8 copies
 // its 128/NCW rows of the tile to global memory, whole rows per instruction.
 // gtile points at row 0 of the tile in the (rows x HD) global matrix; rows >= rows_valid are skipped.
+// (tensor, tensor_bytes, status: the whole destination tensor, for the bounds-checked debug build)
 template <int HD>
 __device__ __forceinline__ void store_staged(const uint8_t *stage, __nv_bfloat16 *gtile, int rows_valid, int w8,
-                                             int lane)
+                                             int lane, const void *tensor, size_t tensor_bytes, DeviceStatus *status)
 {
     constexpr int ROWB = HD * 2, CHUNKS = ROWB / 16, ROWS_PER_ST = 32 / CHUNKS, ROWS_PER_WARP = 128 / NCW;
     const int chunk = lane % CHUNKS;
@@ -254,7 +255,8 @@ __device__ __forceinline__ void store_staged(const uint8_t *stage, __nv_bfloat16
         const int rr = w8 * ROWS_PER_WARP + it * ROWS_PER_ST + lane / CHUNKS;
         const int sw = (chunk & ~7) | ((chunk ^ rr) & 7);
         const uint4 wv = *reinterpret_cast<const uint4 *>(stage + rr * ROWB + sw * 16);
-        if (rr < rows_valid) *reinterpret_cast<uint4 *>(gtile + (size_t)rr * HD + chunk * 8) = wv;
+        __nv_bfloat16 *dst = gtile + (size_t)rr * HD + chunk * 8;
+        if (rr < rows_valid && EMBER_STORE_OK(dst, tensor, tensor_bytes, 16, status)) *reinterpret_cast<uint4 *>(dst) = wv;
     }
 }
 
@@ -524,8 +526,8 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
         named_bar_sync(3, NCT);
         const int rows_valid = ok ? min(128, p.lk - k0) : 0;
         const size_t gtile = ((size_t)bh * p.lk + k0) * HD;
-        store_staged<HD>(smem_gen + C::OFF_RES1, p.dv + gtile, rows_valid, warp, lane);
-        store_staged<HD>(smem_gen + C::OFF_RES0, p.dk + gtile, rows_valid, warp, lane);
+        store_staged<HD>(smem_gen + C::OFF_RES1, p.dv + gtile, rows_valid, warp, lane, p.dv, (size_t)p.order.units * p.lk * HD * 2, p.status);
+        store_staged<HD>(smem_gen + C::OFF_RES0, p.dk + gtile, rows_valid, warp, lane, p.dk, (size_t)p.order.units * p.lk * HD * 2, p.status);
     }
 
     tc_fence_before();
@@ -735,7 +737,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
         stage_acc<HD>(tmem + lane_sel + C::T_ACC0, smem_gen + C::OFF_RES0, r, h, p.scale);
         named_bar_sync(3, NCT);
         store_staged<HD>(smem_gen + C::OFF_RES0, p.dq + ((size_t)bh * p.lq + q0) * HD, ok ? min(128, p.lq - q0) : 0, warp,
-                         lane);
+                         lane, p.dq, (size_t)p.order.units * p.lq * HD * 2, p.status);
     }
 
     tc_fence_before();
@@ -1184,8 +1186,8 @@ __global__ void __launch_bounds__(SP_THREADS, 1)
         named_bar_sync(3, NCT);
         const int rows_valid = ok ? min(128, p.lk - k0) : 0;
         const size_t gtile = ((size_t)bh * p.lk + k0) * HD;
-        store_staged<HD>(smem_gen + C::OFF_RES1, p.dv + gtile, rows_valid, warp, lane);
-        store_staged<HD>(smem_gen + C::OFF_RES0, p.dk + gtile, rows_valid, warp, lane);
+        store_staged<HD>(smem_gen + C::OFF_RES1, p.dv + gtile, rows_valid, warp, lane, p.dv, (size_t)p.order.units * p.lk * HD * 2, p.status);
+        store_staged<HD>(smem_gen + C::OFF_RES0, p.dk + gtile, rows_valid, warp, lane, p.dk, (size_t)p.order.units * p.lk * HD * 2, p.status);
     }
 
     tc_fence_before();

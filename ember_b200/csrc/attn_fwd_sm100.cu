@@ -566,11 +566,13 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
                     const int sw = (chunk & ~7) | ((chunk ^ rr) & 7);
                     const uint4 wv = *reinterpret_cast<const uint4 *>(stage + rr * ROWB + sw * 16);
                     const int grow = q_base + t * TSTEP + rr;
-                    if (ok && grow < p.lq)
-                        *reinterpret_cast<uint4 *>(p.out + ((size_t)bh * p.lq + grow) * HD + chunk * 8) = wv;
+                    __nv_bfloat16 *dst = p.out + ((size_t)bh * p.lq + grow) * HD + chunk * 8;
+                    if (ok && grow < p.lq && EMBER_STORE_OK(dst, p.out, (size_t)p.order.units * p.lq * HD * 2, 16, p.status))
+                        *reinterpret_cast<uint4 *>(dst) = wv;
                 }
             }
-            if (store && p.lse) p.lse[(size_t)bh * p.lq + row] = (m_ref + log2f(l)) * LN2_F;
+            if (store && p.lse && EMBER_STORE_OK(p.lse + (size_t)bh * p.lq + row, p.lse, (size_t)p.order.units * p.lq * 4, 4, p.status))
+                p.lse[(size_t)bh * p.lq + row] = (m_ref + log2f(l)) * LN2_F;
         }
     }
 

@@ -107,6 +107,30 @@ EMBER_HD void work_item(const WorkOrder &w, int idx, int &unit, int &rank)
     unit = g * w.group + (rem - rank * units_here);
 }
 
+// Bounds-checked debug build (-DEMBER_BOUNDS_CHECK, `python -m ember_b200.build --bounds`): every
+// global store of the tensor-core attention kernels first checks that [ptr, ptr + len) lies inside the
+// tensor it belongs to; a store that does not is skipped and reported through the device status word
+// (EMBER_ERR_INVALID, wait code 9100, extra = the byte offset) instead of being made. It stands in for a
+// memory checker where none can be run. In the normal build the check is a constant `true`.
+#ifdef __CUDACC__
+#ifdef EMBER_BOUNDS_CHECK
+__device__ __forceinline__ bool store_in_bounds(const void *ptr, const void *base, size_t bytes, size_t len, DeviceStatus *status)
+{
+    const size_t off = (size_t)((const char *)ptr - (const char *)base);
+    if ((const char *)ptr >= (const char *)base && off + len <= bytes) return true;
+    if (atomicCAS(&status->code, 0, EMBER_ERR_INVALID) == 0) {
+        status->where = 9100;
+        status->block = blockIdx.x;
+        status->extra = (int)(off > 0x7fffffffu ? 0x7fffffffu : off);
+    }
+    return false;
+}
+#define EMBER_STORE_OK(ptr, base, bytes, len, status) ::ember::store_in_bounds(ptr, base, bytes, len, status)
+#else
+#define EMBER_STORE_OK(ptr, base, bytes, len, status) true
+#endif
+#endif
+
 inline size_t dtype_size(int dtype) { return dtype == EMBER_BF16 ? 2 : 4; }
 
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
