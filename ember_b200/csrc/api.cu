@@ -187,13 +187,16 @@ int ember_attention_fwd_host(const void *q_host, const void *k_host, const void 
     }
     const size_t es = dtype_size(dtype);
     const size_t q_unit = (size_t)lq * d * es, k_unit = (size_t)lk * d * es, l_unit = (size_t)lq * sizeof(float);
-    // chunks of about 32 MB of inputs, at least 2 so that copies and compute overlap, at most 16
-    int chunks = (int)(((q_unit + 2 * k_unit) * batch_heads + (32u << 20) - 1) / (32u << 20));
-    if (chunks < 2) chunks = 2;
-    if (chunks > 16) chunks = 16;
-    if (chunks > batch_heads) chunks = batch_heads;
-    const int per = (batch_heads + chunks - 1) / chunks;
-    chunks = (batch_heads + per - 1) / per;
+    // Chunks of about 64 MB of inputs (fewer, larger copies measured faster than many small ones: 8.24 ms
+    // against 8.42 at 32 MB and 8.92 at 16 MB for 403 MB in / 134 MB out), tapering towards the end: what
+    // is left after the last copy-in is that chunk's kernel and copy-out, so the last chunks halve down
+    // to a single unit.
+    const size_t unit_in = q_unit + 2 * k_unit;
+    const size_t chunk_target = (size_t)64 << 20;
+    int per = (int)(chunk_target / (unit_in ? unit_in : 1));
+    if (per < 1) per = 1;
+    if (per > (batch_heads + 1) / 2) per = (batch_heads + 1) / 2;  // at least two chunks, so that copies and compute overlap
+    if (per < 1) per = 1;
     // two sets of staging buffers: q, k, v, out, lse for `per` units each
     const size_t set_bytes = align_up(per * q_unit, 256) * 2 + align_up(per * k_unit, 256) * 2 + align_up(per * l_unit, 256);
     char *stage = (char *)alloc_memory(2 * set_bytes);
@@ -215,8 +218,10 @@ int ember_attention_fwd_host(const void *q_host, const void *k_host, const void 
     HOST_TRY(cudaEventRecord(st->compute_done[1], st->stream));
     HOST_TRY(cudaEventRecord(st->out_done[0], st->copy_out));
     HOST_TRY(cudaEventRecord(st->out_done[1], st->copy_out));
-    for (int c = 0; c < chunks; c++) {
-        const int b = c & 1, u0 = c * per, n = (u0 + per <= batch_heads) ? per : batch_heads - u0;
+    for (int c = 0, u0 = 0, n = 0; u0 < batch_heads; c++, u0 += n) {
+        const int b = c & 1, left = batch_heads - u0;
+        n = left > 2 * per ? per : (left + 1) / 2;  // full chunks, then halves of what is left
+        if (n > per) n = per;
         char *dq = stage + b * set_bytes, *dk = dq + align_up(per * q_unit, 256), *dv = dk + align_up(per * k_unit, 256);
         char *dout = dv + align_up(per * k_unit, 256), *dl = dout + align_up(per * q_unit, 256);
         // inputs of this set may be overwritten once the kernel that last read them is done
