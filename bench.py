@@ -659,6 +659,10 @@ def run_extras(L, _lib, torch, dev, sptr, stream, peaks):
     extra = {}
 
     def timed(fn, steps, warm=3):
+        # every extra is a short burst timed on its own: idle first, so that it does not inherit the
+        # power state (a clock near 1.6 GHz) of the kernel measured before it
+        torch.cuda.synchronize()
+        time.sleep(1.0)
         for _ in range(warm):
             fn()
         torch.cuda.synchronize()
