@@ -289,16 +289,22 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                     }
                 }
                 __syncwarp();
-                // Each warp copies its own 32 rows: two rows of 16 chunks per instruction.
+                // Each warp copies its own 32 rows: two rows of 16 chunks per instruction. The destination
+                // of a chunk is found without divisions in the loop: this thread's column is fixed, and
+                // the 128 rows of a CTA's tile are consecutive in memory rows (row-major: `cols` apart;
+                // head-major: the tile lies inside one batch entry because seq is a multiple of 128, so
+                // consecutive rows are `dim` apart).
                 const int chunk = lane % 16;
                 const int col = n0 + half * 128 + chunk * 8;
+                const size_t row_stride = p.c.heads == 0 ? (size_t)p.c.cols : (size_t)p.c.dim;
+                const size_t base = (m0 < p.m && col < p.n) ? view_offset(p.c, m0, col) : 0;
 #pragma unroll 4
                 for (int it2 = 0; it2 < 16; it2++) {
                     const int rr = warp * 32 + it2 * 2 + lane / 16;
                     const int sw = (chunk & ~7) | ((chunk ^ rr) & 7);
                     const uint4 wv = *reinterpret_cast<const uint4 *>(stage + rr * 256 + sw * 16);
                     const long long grow = m0 + rr;
-                    if (ok && grow < p.m && col < p.n) *reinterpret_cast<uint4 *>(cptr + view_offset(p.c, grow, col)) = wv;
+                    if (ok && grow < p.m && col < p.n) *reinterpret_cast<uint4 *>(cptr + base + (size_t)rr * row_stride) = wv;
                 }
                 __syncwarp();
             }
@@ -366,7 +372,7 @@ bool sm100_gemm_supported(const GemmArgs &g)
     if (g.m > 0x7fffff00LL || g.a.rows > 0x7fffff00LL || g.b.rows > 0x7fffff00LL) return false;  // 32-bit box coordinates
     if ((g.m + 2 * BM - 1) / (2 * BM) * (long long)((g.n + BN - 1) / BN) > 0x7fffffffLL) return false;
     if (g.n % 8 != 0 || ((uintptr_t)g.c.ptr & 15) != 0) return false;       // 16-byte output chunks
-    if (g.c.heads > 0 && g.c.dim % 8 != 0) return false;
+    if (g.c.heads > 0 && (g.c.dim % 8 != 0 || g.c.seq % BM != 0)) return false;  // a CTA's 128 result rows lie in one batch entry
     const int a_rows = g.mode == GEMM_TN ? 64 : BM, b_rows = g.mode == GEMM_NT ? BNH : 64;
     return view_ok(g.a, a_rows) && view_ok(g.b, b_rows);
 }
