@@ -274,15 +274,26 @@ __global__ void __launch_bounds__(256, 2) row_softmax_regs_kernel(const T *__res
         if (active) {
             uint4 *yv = reinterpret_cast<uint4 *>(y + (size_t)row * cols);
             const uint4 *tv4 = MODE == MODE_CROSS_ENTROPY ? reinterpret_cast<const uint4 *>(target + (size_t)row * cols) : nullptr;
-            // cross-entropy: the targets are fetched four pieces at a time (the registers hold the row)
+            // cross-entropy: the targets are fetched four pieces at a time (the registers hold the row),
+            // one group ahead of the group being computed
             constexpr int TB = MAXV < 4 ? MAXV : 4;
+            uint4 tnext[TB];
+            if (MODE == MODE_CROSS_ENTROPY) {
+#pragma unroll
+                for (int i = 0; i < TB; i++)
+                    if (t + i * W < nvec) tnext[i] = tv4[t + i * W];
+            }
 #pragma unroll
             for (int i0 = 0; i0 < MAXV; i0 += TB) {
                 uint4 traw[TB];
                 if (MODE == MODE_CROSS_ENTROPY) {
 #pragma unroll
-                    for (int i = 0; i < TB; i++)
-                        if (t + (i0 + i) * W < nvec) traw[i] = tv4[t + (i0 + i) * W];
+                    for (int i = 0; i < TB; i++) traw[i] = tnext[i];
+                    if (i0 + TB < MAXV) {
+#pragma unroll
+                        for (int i = 0; i < TB; i++)
+                            if (t + (i0 + TB + i) * W < nvec) tnext[i] = tv4[t + (i0 + TB + i) * W];
+                    }
                 }
 #pragma unroll
                 for (int i = 0; i < TB; i++) {
