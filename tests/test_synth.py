@@ -36,3 +36,25 @@ def test_a_slab_does_not_depend_on_the_sharding():
         for r in range(world):
             slab = synth.units_torch(torch, 9, r * per, (r + 1) * per, rows, dim, "cpu", 0.5, torch.bfloat16)
             assert torch.equal(slab, whole[r * per:(r + 1) * per])
+
+
+def test_bench_checksum_sees_single_bit_changes_and_positions():
+    """The 64-bit checksum bench.py uses for its one-GPU-vs-N identity checks: equal tensors agree, one
+    flipped bit or two swapped elements do not."""
+    import importlib.util
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location("bench_module", os.path.join(root, "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    a = synth.units_torch(torch, 3, 0, 2, 16, 32, "cpu", 0.5, torch.bfloat16)
+    b = a.clone()
+    assert bench.unit_checksum(torch, a) == bench.unit_checksum(torch, b)
+    b.view(torch.int16)[1, 3, 5] ^= 1
+    assert bench.unit_checksum(torch, a) != bench.unit_checksum(torch, b)
+    c = a.clone()
+    c[0, 0, 0], c[0, 0, 1] = a[0, 0, 1].clone(), a[0, 0, 0].clone()
+    if not torch.equal(c, a):
+        assert bench.unit_checksum(torch, a) != bench.unit_checksum(torch, c)
+    f = torch.arange(10, dtype=torch.float32)
+    assert bench.unit_checksum(torch, f) == bench.unit_checksum(torch, f.clone())
