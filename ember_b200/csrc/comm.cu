@@ -27,6 +27,7 @@ struct NcclApi {
     ncclResult_t (*CommGetAsyncError)(ncclComm_t, ncclResult_t *) = nullptr;
     ncclResult_t (*CommAbort)(ncclComm_t) = nullptr;
     ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+    ncclResult_t (*CommFinalize)(ncclComm_t) = nullptr;  // optional (NCCL >= 2.14)
     ncclResult_t (*AllGather)(const void *, void *, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
     const char *(*GetErrorString)(ncclResult_t) = nullptr;
     bool ok = false;
@@ -63,6 +64,7 @@ int load_nccl()
         !bind(g_nccl.CommDestroy, "ncclCommDestroy") || !bind(g_nccl.AllGather, "ncclAllGather") ||
         !bind(g_nccl.GetErrorString, "ncclGetErrorString"))
         return EMBER_ERR_UNSUPPORTED;
+    g_nccl.CommFinalize = reinterpret_cast<decltype(g_nccl.CommFinalize)>(dlsym(g_nccl.handle, "ncclCommFinalize"));
     g_nccl.ok = true;
     return EMBER_OK;
 }
@@ -139,8 +141,19 @@ int ember_comm_destroy(void *comm)
     if (!comm) return EMBER_OK;
     int rc = load_nccl();
     if (rc) return rc;
-    ncclResult_t r = g_nccl.CommDestroy((ncclComm_t)comm);
-    return r == ncclSuccess ? EMBER_OK : nccl_fail(r, "ncclCommDestroy");
+    // The communicator is non-blocking: finish what is still queued on it first (polled), then destroy.
+    ncclComm_t c = (ncclComm_t)comm;
+    if (g_nccl.CommFinalize) {
+        ncclResult_t f = g_nccl.CommFinalize(c);
+        const double t0 = now_ms();
+        while (f == ncclInProgress && now_ms() - t0 < 60000.0) {
+            timespec nap = {0, 1000000};
+            nanosleep(&nap, nullptr);
+            if (g_nccl.CommGetAsyncError(c, &f) != ncclSuccess) break;
+        }
+    }
+    ncclResult_t r = g_nccl.CommDestroy(c);
+    return (r == ncclSuccess || r == ncclInProgress) ? EMBER_OK : nccl_fail(r, "ncclCommDestroy");
 }
 
 int ember_gather_outputs(void *out_full, const void *out_slab, size_t slab_bytes, void *comm, void *stream)
