@@ -149,9 +149,82 @@ int simt_gemm(const GemmArgs &g, cudaStream_t s)
     return g.dtype == EMBER_BF16 ? launch_gemm<__nv_bfloat16>(g, s) : launch_gemm<float>(g, s);
 }
 
+// Column sums of a large bf16 matrix in two passes, both coalesced: the rows are cut into chunks; a block
+// of 8 warps takes 256 columns of one chunk (a warp reads 512 contiguous bytes of a row, lane t its
+// columns 8t..8t+7; the offset of a view element splits into a column part, computed once per lane,
+// and a row part that is walked without divisions), adds its rows in float32 and writes one partial
+// per column; a second kernel adds the partials of a column in a fixed order. The one-pass kernel
+// above gives a block only 32 columns, i.e. 64-byte pieces of every row.
+__global__ void __launch_bounds__(256) column_partial_kernel(MatView a, float *__restrict__ partial, int rows_per_chunk)
+{
+    __shared__ float red[8][256];
+    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const int col = blockIdx.x * 256 + lane * 8;
+    const long long r0 = (long long)blockIdx.y * rows_per_chunk, r1 = min(a.rows, r0 + rows_per_chunk);
+    float s[8] = {};
+    if (col < a.cols) {
+        const __nv_bfloat16 *ap = (const __nv_bfloat16 *)a.ptr;
+        const size_t col_off = view_offset(a, 0, col);  // rows and columns of a view address independently
+        // row part of the offset: row-major r * cols; head-major (b * heads * seq + l) * dim with r = b * seq + l
+        long long r = r0 + warp;
+        long long b = a.heads ? r / a.seq : 0;
+        int l = a.heads ? (int)(r - b * a.seq) : 0;
+#pragma unroll 4
+        for (; r < r1; r += 8) {
+            const size_t row_off = a.heads ? ((size_t)b * a.heads * a.seq + l) * a.dim : (size_t)r * a.cols;
+            const uint4 v = *reinterpret_cast<const uint4 *>(ap + col_off + row_off);
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                s[2 * i] += __uint_as_float(w[i] << 16);
+                s[2 * i + 1] += __uint_as_float(w[i] & 0xffff0000u);
+            }
+            if (a.heads) {
+                l += 8;
+                if (l >= a.seq) { l -= a.seq; b++; }
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 8; i++) red[warp][lane * 8 + i] = s[i];
+    __syncthreads();
+    const int c = blockIdx.x * 256 + threadIdx.x;
+    if (c < a.cols) {
+        float t = 0.f;
+#pragma unroll
+        for (int w8 = 0; w8 < 8; w8++) t += red[w8][threadIdx.x];
+        partial[(size_t)blockIdx.y * a.cols + c] = t;
+    }
+}
+
+__global__ void __launch_bounds__(256) column_final_kernel(const float *__restrict__ partial, __nv_bfloat16 *__restrict__ out, int cols,
+                                                           int chunks)
+{
+    const int c = blockIdx.x * 256 + threadIdx.x;
+    if (c >= cols) return;
+    float t = 0.f;
+    for (int k = 0; k < chunks; k++) t += partial[(size_t)k * cols + c];
+    out[c] = __float2bfloat16_rn(t);
+}
+
 int column_sums(const MatView &a, void *out, int dtype, cudaStream_t s)
 {
     const bool vec = ((uintptr_t)a.ptr & 15) == 0 && (a.heads ? a.dim % 8 == 0 : a.cols % 8 == 0);
+    if (vec && dtype == EMBER_BF16 && a.rows >= 4096 && (a.heads == 0 || a.seq % 8 == 0)) {
+        const int chunks = 64;
+        const int rows_per_chunk = (int)((a.rows + chunks - 1) / chunks + 7) / 8 * 8;
+        float *partial = nullptr;
+        EMBER_CUDA_TRY(cudaMallocAsync((void **)&partial, (size_t)chunks * a.cols * sizeof(float), s));
+        column_partial_kernel<<<dim3((a.cols + 255) / 256, chunks), 256, 0, s>>>(a, partial, rows_per_chunk);
+        cudaError_t e = cudaGetLastError();
+        if (e == cudaSuccess) {
+            column_final_kernel<<<(a.cols + 255) / 256, 256, 0, s>>>(partial, (__nv_bfloat16 *)out, a.cols, chunks);
+            e = cudaGetLastError();
+        }
+        cudaFreeAsync(partial, s);
+        EMBER_CUDA_TRY(e);
+        return EMBER_OK;
+    }
     if (vec) {
         const int grid = (a.cols + 31) / 32;
         if (dtype == EMBER_BF16)
