@@ -35,7 +35,7 @@ bool deterministic_mode()
     return g_deterministic != 0;
 }
 
-bool tensor_core_shape(int d, int dtype) { return dtype == EMBER_BF16 && (d == 64 || d == 128); }
+bool tensor_core_shape(int d, int dtype) { return dtype == EMBER_BF16 && d >= 8 && d <= 128 && d % 8 == 0; }
 
 // delta vector, then (single-pass tensor-core backward only) the float32 dQ accumulator
 size_t bwd_workspace_bytes(int bh, int lq, int d, int dtype)

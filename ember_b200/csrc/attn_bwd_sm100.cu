@@ -93,6 +93,8 @@ struct BwdParams {
     __nv_bfloat16 *dq, *dk, *dv;
     const float *lse, *delta;
     int lq, lk, causal;
+    int d;  // elements per row in memory (a multiple of 8, <= HD): the TMA copies read the columns past d
+            // as zero, so the accumulators' columns past d are zero too and the epilogues skip them
     float scale, scale_log2;
     DeviceStatus *status;
     WorkOrder order;  // set per launch
@@ -242,10 +244,11 @@ __device__ __forceinline__ void stage_acc(uint32_t tacc, uint8_t *stage, int r, 
 
 // store_staged: after all compute threads have staged (caller synchronises), compute warp w8 copies
 // its 128/NCW rows of the tile to global memory, whole rows per instruction.
-// gtile points at row 0 of the tile in the (rows x HD) global matrix; rows >= rows_valid are skipped.
+// gtile points at row 0 of the tile in the (rows x d) global matrix, d <= HD elements per row; rows >=
+// rows_valid and the 16-byte chunks past column d are skipped.
 // (tensor, tensor_bytes, status: the whole destination tensor, for the bounds-checked debug build)
 template <int HD>
-__device__ __forceinline__ void store_staged(const uint8_t *stage, __nv_bfloat16 *gtile, int rows_valid, int w8,
+__device__ __forceinline__ void store_staged(const uint8_t *stage, __nv_bfloat16 *gtile, int d, int rows_valid, int w8,
                                              int lane, const void *tensor, size_t tensor_bytes, DeviceStatus *status)
 {
     constexpr int ROWB = HD * 2, CHUNKS = ROWB / 16, ROWS_PER_ST = 32 / CHUNKS, ROWS_PER_WARP = 128 / NCW;
@@ -255,8 +258,9 @@ __device__ __forceinline__ void store_staged(const uint8_t *stage, __nv_bfloat16
         const int rr = w8 * ROWS_PER_WARP + it * ROWS_PER_ST + lane / CHUNKS;
         const int sw = (chunk & ~7) | ((chunk ^ rr) & 7);
         const uint4 wv = *reinterpret_cast<const uint4 *>(stage + rr * ROWB + sw * 16);
-        __nv_bfloat16 *dst = gtile + (size_t)rr * HD + chunk * 8;
-        if (rr < rows_valid && EMBER_STORE_OK(dst, tensor, tensor_bytes, 16, status)) *reinterpret_cast<uint4 *>(dst) = wv;
+        __nv_bfloat16 *dst = gtile + (size_t)rr * d + chunk * 8;
+        if (rr < rows_valid && chunk * 8 < d && EMBER_STORE_OK(dst, tensor, tensor_bytes, 16, status))
+            *reinterpret_cast<uint4 *>(dst) = wv;
     }
 }
 
@@ -525,9 +529,9 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
         stage_acc<HD>(tmem + lane_sel + C::T_ACC1, smem_gen + C::OFF_RES0, r, h, p.scale);
         named_bar_sync(3, NCT);
         const int rows_valid = ok ? min(128, p.lk - k0) : 0;
-        const size_t gtile = ((size_t)bh * p.lk + k0) * HD;
-        store_staged<HD>(smem_gen + C::OFF_RES1, p.dv + gtile, rows_valid, warp, lane, p.dv, (size_t)p.order.units * p.lk * HD * 2, p.status);
-        store_staged<HD>(smem_gen + C::OFF_RES0, p.dk + gtile, rows_valid, warp, lane, p.dk, (size_t)p.order.units * p.lk * HD * 2, p.status);
+        const size_t gtile = ((size_t)bh * p.lk + k0) * p.d;
+        store_staged<HD>(smem_gen + C::OFF_RES1, p.dv + gtile, p.d, rows_valid, warp, lane, p.dv, (size_t)p.order.units * p.lk * p.d * 2, p.status);
+        store_staged<HD>(smem_gen + C::OFF_RES0, p.dk + gtile, p.d, rows_valid, warp, lane, p.dk, (size_t)p.order.units * p.lk * p.d * 2, p.status);
     }
 
     tc_fence_before();
@@ -736,8 +740,8 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
         // dQ (times the softmax scale) through the Q tile's buffer, which is dead by now.
         stage_acc<HD>(tmem + lane_sel + C::T_ACC0, smem_gen + C::OFF_RES0, r, h, p.scale);
         named_bar_sync(3, NCT);
-        store_staged<HD>(smem_gen + C::OFF_RES0, p.dq + ((size_t)bh * p.lq + q0) * HD, ok ? min(128, p.lq - q0) : 0, warp,
-                         lane, p.dq, (size_t)p.order.units * p.lq * HD * 2, p.status);
+        store_staged<HD>(smem_gen + C::OFF_RES0, p.dq + ((size_t)bh * p.lq + q0) * p.d, p.d, ok ? min(128, p.lq - q0) : 0, warp,
+                         lane, p.dq, (size_t)p.order.units * p.lq * p.d * 2, p.status);
     }
 
     tc_fence_before();
@@ -821,6 +825,7 @@ struct SpParams {
     float *dq_acc;  // [unit][query tile][lane quarter][HD/32 chunks][1024] float32, zero on entry
     const float *lse, *delta;
     int lq, lk, causal;
+    int d;  // elements per row in memory (a multiple of 8, <= HD), as in BwdParams
     float scale, scale_log2;
     DeviceStatus *status;
     WorkOrder order;
@@ -1185,9 +1190,9 @@ __global__ void __launch_bounds__(SP_THREADS, 1)
         stage_acc<HD>(tmem + lane_sel + C::T_ACC1, smem_gen + C::OFF_RES0, r, h, p.scale);
         named_bar_sync(3, NCT);
         const int rows_valid = ok ? min(128, p.lk - k0) : 0;
-        const size_t gtile = ((size_t)bh * p.lk + k0) * HD;
-        store_staged<HD>(smem_gen + C::OFF_RES1, p.dv + gtile, rows_valid, warp, lane, p.dv, (size_t)p.order.units * p.lk * HD * 2, p.status);
-        store_staged<HD>(smem_gen + C::OFF_RES0, p.dk + gtile, rows_valid, warp, lane, p.dk, (size_t)p.order.units * p.lk * HD * 2, p.status);
+        const size_t gtile = ((size_t)bh * p.lk + k0) * p.d;
+        store_staged<HD>(smem_gen + C::OFF_RES1, p.dv + gtile, p.d, rows_valid, warp, lane, p.dv, (size_t)p.order.units * p.lk * p.d * 2, p.status);
+        store_staged<HD>(smem_gen + C::OFF_RES0, p.dk + gtile, p.d, rows_valid, warp, lane, p.dk, (size_t)p.order.units * p.lk * p.d * 2, p.status);
     }
 
     tc_fence_before();
@@ -1199,7 +1204,7 @@ __global__ void __launch_bounds__(SP_THREADS, 1)
 // the tile (lane quarter t / 32, lane t % 32 of the accumulator's block layout) and writes 64 bytes of it.
 template <int HD>
 __global__ void __launch_bounds__(128) dq_finish_kernel(const float *__restrict__ acc, __nv_bfloat16 *__restrict__ dq, int lq,
-                                                        int nqt, float scale)
+                                                        int nqt, float scale, int d)
 {
     const size_t tile = blockIdx.x;  // unit * nqt + query tile
     const int c = blockIdx.y;        // 32-column chunk
@@ -1207,14 +1212,15 @@ __global__ void __launch_bounds__(128) dq_finish_kernel(const float *__restrict_
     const size_t unit = tile / nqt;
     const int w = threadIdx.x / 32, lane = threadIdx.x % 32;
     const int row = qt * 128 + threadIdx.x;
-    if (row >= lq) return;
+    if (row >= lq || c * 32 >= d) return;  // d: elements per dq row in memory (<= HD, a multiple of 8)
     const float4 *src = reinterpret_cast<const float4 *>(acc + ((tile * 4 + w) * (HD / 32) + c) * 1024);
     float4 v[8];
 #pragma unroll
     for (int cg = 0; cg < 8; cg++) v[cg] = src[cg * 32 + lane];  // all eight loads in flight
-    __nv_bfloat16 *dst = dq + (unit * lq + row) * HD + c * 32;
+    __nv_bfloat16 *dst = dq + (unit * lq + row) * d + c * 32;
 #pragma unroll
     for (int cg = 0; cg < 8; cg += 2) {
+        if (c * 32 + cg * 4 >= d) break;
         uint4 o;
         o.x = pack_bf16(v[cg].x * scale, v[cg].y * scale);
         o.y = pack_bf16(v[cg].z * scale, v[cg].w * scale);
@@ -1252,10 +1258,38 @@ __global__ void __launch_bounds__(256) delta_bf16_kernel(const uint4 *__restrict
     if (row < rows && lane % LPR == 0) delta[row] = s;
 }
 
+// The same for rows of any multiple of 8 elements up to 128: 16 lanes per row, one 16-byte load per
+// tensor and lane where the row has that chunk.
+__global__ void __launch_bounds__(256) delta_bf16_rows_kernel(const uint4 *__restrict__ out, const uint4 *__restrict__ dout,
+                                                              float *__restrict__ delta, size_t rows, int chunks)
+{
+    const int lane = threadIdx.x % 32, c = lane % 16;
+    const size_t row = ((size_t)blockIdx.x * 8 + threadIdx.x / 32) * 2 + lane / 16;
+    float s = 0.f;
+    if (row < rows && c < chunks) {
+        const uint4 a = out[row * chunks + c], b = dout[row * chunks + c];
+        const uint32_t x[4] = {a.x, a.y, a.z, a.w}, y[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            s = fmaf(__uint_as_float(x[i] << 16), __uint_as_float(y[i] << 16), s);
+            s = fmaf(__uint_as_float(x[i] & 0xffff0000u), __uint_as_float(y[i] & 0xffff0000u), s);
+        }
+    }
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (row < rows && c == 0) delta[row] = s;
+}
+
 template <int HD>
 int launch_delta_bf16(const AttnArgs &a, float *delta, cudaStream_t s)
 {
     const size_t rows = (size_t)a.bh * a.lq;
+    if (a.d != HD) {
+        delta_bf16_rows_kernel<<<(unsigned)((rows + 15) / 16), 256, 0, s>>>((const uint4 *)a.out, (const uint4 *)a.dout, delta,
+                                                                             rows, a.d / 8);
+        EMBER_CUDA_TRY(cudaGetLastError());
+        return EMBER_OK;
+    }
     constexpr int ROWS_PER_BLOCK = 8 * (32 / (HD / 16));
     delta_bf16_kernel<HD><<<(unsigned)((rows + ROWS_PER_BLOCK - 1) / ROWS_PER_BLOCK), 256, 0, s>>>(
         (const uint4 *)a.out, (const uint4 *)a.dout, delta, rows);
@@ -1273,10 +1307,10 @@ int launch_fused(const AttnArgs &a, float *delta, float *dq_acc, DeviceState *st
     const int nqt = (a.lq + 127) / 128;
     EMBER_CUDA_TRY(cudaMemsetAsync(dq_acc, 0, (size_t)a.bh * nqt * 128 * HD * sizeof(float), s));
     CUtensorMap tq, tk, tv, tdo;
-    if ((rc = make_tensor_map_bf16_3d(&tq, a.q, HD, a.lq, a.bh, 64, 128)) != EMBER_OK) return rc;
-    if ((rc = make_tensor_map_bf16_3d(&tk, a.k, HD, a.lk, a.bh, 64, 128)) != EMBER_OK) return rc;
-    if ((rc = make_tensor_map_bf16_3d(&tv, a.v, HD, a.lk, a.bh, 64, 128)) != EMBER_OK) return rc;
-    if ((rc = make_tensor_map_bf16_3d(&tdo, a.dout, HD, a.lq, a.bh, 64, 128)) != EMBER_OK) return rc;
+    if ((rc = make_tensor_map_bf16_3d(&tq, a.q, a.d, a.lq, a.bh, 64, 128)) != EMBER_OK) return rc;
+    if ((rc = make_tensor_map_bf16_3d(&tk, a.k, a.d, a.lk, a.bh, 64, 128)) != EMBER_OK) return rc;
+    if ((rc = make_tensor_map_bf16_3d(&tv, a.v, a.d, a.lk, a.bh, 64, 128)) != EMBER_OK) return rc;
+    if ((rc = make_tensor_map_bf16_3d(&tdo, a.dout, a.d, a.lq, a.bh, 64, 128)) != EMBER_OK) return rc;
     SpParams p;
     p.dk = (__nv_bfloat16 *)a.dk;
     p.dv = (__nv_bfloat16 *)a.dv;
@@ -1285,6 +1319,7 @@ int launch_fused(const AttnArgs &a, float *delta, float *dq_acc, DeviceState *st
     p.delta = delta;
     p.lq = a.lq;
     p.lk = a.lk;
+    p.d = a.d;
     p.causal = a.causal;
     p.scale = a.scale;
     p.scale_log2 = a.scale * LOG2E_B;
@@ -1295,7 +1330,7 @@ int launch_fused(const AttnArgs &a, float *delta, float *dq_acc, DeviceState *st
     p.order = make_work_order(a.bh, (a.lk + 127) / 128, st->sm_count, touched, a.causal != 0);
     k1<<<dim3((unsigned)(p.order.units * p.order.blocks)), SP_THREADS, C::SMEM_BYTES, s>>>(tq, tk, tv, tdo, p);
     EMBER_CUDA_TRY(cudaGetLastError());
-    dq_finish_kernel<HD><<<dim3((unsigned)((size_t)a.bh * nqt), HD / 32), 128, 0, s>>>(dq_acc, (__nv_bfloat16 *)a.dq, a.lq, nqt, a.scale);
+    dq_finish_kernel<HD><<<dim3((unsigned)((size_t)a.bh * nqt), HD / 32), 128, 0, s>>>(dq_acc, (__nv_bfloat16 *)a.dq, a.lq, nqt, a.scale, a.d);
     EMBER_CUDA_TRY(cudaGetLastError());
     return EMBER_OK;
 }
@@ -1307,10 +1342,10 @@ int launch(const AttnArgs &a, float *delta, DeviceState *st, cudaStream_t s)
     int rc = launch_delta_bf16<HD>(a, delta, s);
     if (rc) return rc;
     CUtensorMap tq, tk, tv, tdo;
-    if ((rc = make_tensor_map_bf16_3d(&tq, a.q, HD, a.lq, a.bh, 64, 128)) != EMBER_OK) return rc;
-    if ((rc = make_tensor_map_bf16_3d(&tk, a.k, HD, a.lk, a.bh, 64, 128)) != EMBER_OK) return rc;
-    if ((rc = make_tensor_map_bf16_3d(&tv, a.v, HD, a.lk, a.bh, 64, 128)) != EMBER_OK) return rc;
-    if ((rc = make_tensor_map_bf16_3d(&tdo, a.dout, HD, a.lq, a.bh, 64, 128)) != EMBER_OK) return rc;
+    if ((rc = make_tensor_map_bf16_3d(&tq, a.q, a.d, a.lq, a.bh, 64, 128)) != EMBER_OK) return rc;
+    if ((rc = make_tensor_map_bf16_3d(&tk, a.k, a.d, a.lk, a.bh, 64, 128)) != EMBER_OK) return rc;
+    if ((rc = make_tensor_map_bf16_3d(&tv, a.v, a.d, a.lk, a.bh, 64, 128)) != EMBER_OK) return rc;
+    if ((rc = make_tensor_map_bf16_3d(&tdo, a.dout, a.d, a.lq, a.bh, 64, 128)) != EMBER_OK) return rc;
     BwdParams p;
     p.dq = (__nv_bfloat16 *)a.dq;
     p.dk = (__nv_bfloat16 *)a.dk;
@@ -1319,6 +1354,7 @@ int launch(const AttnArgs &a, float *delta, DeviceState *st, cudaStream_t s)
     p.delta = delta;
     p.lq = a.lq;
     p.lk = a.lk;
+    p.d = a.d;
     p.causal = a.causal;
     p.scale = a.scale;
     p.scale_log2 = a.scale * LOG2E_B;
@@ -1342,7 +1378,7 @@ int launch(const AttnArgs &a, float *delta, DeviceState *st, cudaStream_t s)
 bool sm100_bwd_supported(const AttnArgs &a)
 {
     if (a.dtype != EMBER_BF16) return false;
-    if (a.d != 64 && a.d != 128) return false;
+    if (a.d < 8 || a.d > 128 || a.d % 8 != 0) return false;  // zero-padded to 64 or 128 columns by the TMA copies
     if (!isfinite(a.scale)) return false;
     if ((long long)a.bh * ((a.lq + 127) / 128) > 0x7fffffffLL || (long long)a.bh * ((a.lk + 127) / 128) > 0x7fffffffLL)
         return false;
@@ -1362,13 +1398,14 @@ extern "C" EMBER_API int ember_debug_bwd_trace(long long *host)
 // Bytes of float32 dQ accumulator the single-pass kernel needs after the delta vector.
 size_t sm100_bwd_accumulator_bytes(int bh, int lq, int d)
 {
-    return (size_t)bh * ((lq + 127) / 128) * 128 * d * sizeof(float);
+    const int hd = d <= 64 ? 64 : 128;  // the kernel's column count
+    return (size_t)bh * ((lq + 127) / 128) * 128 * hd * sizeof(float);
 }
 
 int sm100_attention_bwd(const AttnArgs &a, float *delta, float *dq_acc, bool deterministic, DeviceState *st, cudaStream_t s)
 {
-    if (deterministic || !dq_acc) return a.d == 128 ? launch<128>(a, delta, st, s) : launch<64>(a, delta, st, s);
-    return a.d == 128 ? launch_fused<128>(a, delta, dq_acc, st, s) : launch_fused<64>(a, delta, dq_acc, st, s);
+    if (deterministic || !dq_acc) return a.d > 64 ? launch<128>(a, delta, st, s) : launch<64>(a, delta, st, s);
+    return a.d > 64 ? launch_fused<128>(a, delta, dq_acc, st, s) : launch_fused<64>(a, delta, dq_acc, st, s);
 }
 
 }  // namespace ember

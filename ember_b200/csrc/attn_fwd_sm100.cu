@@ -94,6 +94,8 @@ struct FwdParams {
     __nv_bfloat16 *out;
     float *lse;
     int lq, lk;
+    int d;  // elements per row of q, k, v and out in memory (a multiple of 8, <= HD): the kernel works on
+            // HD columns, the TMA copies read the columns past d as zero and the epilogue skips them
     int causal;
     float scale_log2;  // scale * log2(e)
     DeviceStatus *status;
@@ -193,8 +195,8 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
         if (p.lse && threadIdx.x < 256 && q_base + (int)threadIdx.x < p.lq)
             p.lse[(size_t)bh * p.lq + q_base + threadIdx.x] = -INFINITY;
         if (p.splits == 1)
-            for (int i = threadIdx.x; i < 256 * HD; i += FWD_THREADS)
-                if (q_base + i / HD < p.lq) p.out[((size_t)bh * p.lq + q_base) * HD + i] = __float2bfloat16_rn(0.f);
+            for (int i = threadIdx.x; i < 256 * p.d; i += FWD_THREADS)
+                if (q_base + i / p.d < p.lq) p.out[((size_t)bh * p.lq + q_base) * p.d + i] = __float2bfloat16_rn(0.f);
         return;
     }
     const int off = lk - p.lq;
@@ -566,8 +568,9 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
                     const int sw = (chunk & ~7) | ((chunk ^ rr) & 7);
                     const uint4 wv = *reinterpret_cast<const uint4 *>(stage + rr * ROWB + sw * 16);
                     const int grow = q_base + t * TSTEP + rr;
-                    __nv_bfloat16 *dst = p.out + ((size_t)bh * p.lq + grow) * HD + chunk * 8;
-                    if (ok && grow < p.lq && EMBER_STORE_OK(dst, p.out, (size_t)p.order.units * p.lq * HD * 2, 16, p.status))
+                    __nv_bfloat16 *dst = p.out + ((size_t)bh * p.lq + grow) * p.d + chunk * 8;
+                    if (ok && grow < p.lq && chunk * 8 < p.d &&
+                        EMBER_STORE_OK(dst, p.out, (size_t)p.order.units * p.lq * p.d * 2, 16, p.status))
                         *reinterpret_cast<uint4 *>(dst) = wv;
                 }
             }
@@ -600,6 +603,7 @@ int launch_pair(const AttnArgs &a, DeviceState *st, cudaStream_t s)
     p.lse = a.lse;
     p.lq = a.lq;
     p.lk = a.lk;
+    p.d = HD;
     p.causal = a.causal;
     p.scale_log2 = a.scale * LOG2E_F;
     p.status = st->status;
@@ -633,14 +637,16 @@ int launch(const AttnArgs &a, DeviceState *st, cudaStream_t s)
     using C = FwdCfg<HD>;
     CUtensorMap tq, tk, tv;
     int rc;
-    if ((rc = make_tensor_map_bf16_3d(&tq, a.q, HD, a.lq, a.bh, 64, 128)) != EMBER_OK) return rc;
-    if ((rc = make_tensor_map_bf16_3d(&tk, a.k, HD, a.lk, a.bh, 64, 128)) != EMBER_OK) return rc;
-    if ((rc = make_tensor_map_bf16_3d(&tv, a.v, HD, a.lk, a.bh, 64, 128)) != EMBER_OK) return rc;
+    // a.d < HD: the maps describe rows of a.d elements; a box reaches to column HD and reads zeros there
+    if ((rc = make_tensor_map_bf16_3d(&tq, a.q, a.d, a.lq, a.bh, 64, 128)) != EMBER_OK) return rc;
+    if ((rc = make_tensor_map_bf16_3d(&tk, a.k, a.d, a.lk, a.bh, 64, 128)) != EMBER_OK) return rc;
+    if ((rc = make_tensor_map_bf16_3d(&tv, a.v, a.d, a.lk, a.bh, 64, 128)) != EMBER_OK) return rc;
     FwdParams p;
     p.out = (__nv_bfloat16 *)a.out;
     p.lse = a.lse;
     p.lq = a.lq;
     p.lk = a.lk;
+    p.d = a.d;
     p.causal = a.causal;
     p.scale_log2 = a.scale * LOG2E_F;
     p.status = st->status;
@@ -704,6 +710,7 @@ int launch_cache_decode(const CacheDecodeArgs &a, DeviceState *st, cudaStream_t 
     p.lse = split ? lse_part : a.lse;
     p.lq = rows;
     p.lk = a.lk;
+    p.d = HD;
     p.causal = 0;
     p.scale_log2 = a.scale * LOG2E_F;
     p.status = st->status;
@@ -728,7 +735,10 @@ int launch_cache_decode(const CacheDecodeArgs &a, DeviceState *st, cudaStream_t 
 bool sm100_fwd_supported(const AttnArgs &a)
 {
     if (a.dtype != EMBER_BF16) return false;
-    if (a.d != 64 && a.d != 128) return false;
+    // Rows of any multiple of 8 elements up to 128 (16-byte rows for the TMA copies and the epilogue's
+    // stores): the kernel runs at 64 or 128 columns and the copies pad with zeros, which changes neither
+    // the scores (zero products) nor the valid output columns.
+    if (a.d < 8 || a.d > 128 || a.d % 8 != 0) return false;
     if (!(a.scale != 0.f) || !isfinite(a.scale)) return false;
     if ((long long)a.bh * ((a.lq + 255) / 256) > 0x7fffffffLL) return false;
     // TMA needs 16-byte aligned bases; the epilogue stores 16-byte vectors.
@@ -769,9 +779,9 @@ static bool fwd_pair_enabled()
 int sm100_attention_fwd(const AttnArgs &a, DeviceState *st, cudaStream_t s)
 {
     const int emu = fwd_emu_setting();
-    if (a.d == 128) {
+    if (a.d > 64) {
         // CTA pairs take 512-row blocks; below three query tiles a pair would mostly idle
-        if (a.lq > 256 && fwd_pair_enabled()) {
+        if (a.d == 128 && a.lq > 256 && fwd_pair_enabled()) {
             if (emu == 0) return launch_pair<128, 0>(a, st, s);
             if (emu == 2) return launch_pair<128, 2>(a, st, s);
             return launch_pair<128, 1>(a, st, s);

@@ -55,7 +55,10 @@ def test_kernel_dispatch_names():
     L = _lib.lib()
     assert L.ember_attention_kernel_name(_lib.EMBER_OP_FWD, 4096, 4096, 128, _lib.EMBER_BF16) == b"sm100_tcgen05"
     assert L.ember_attention_kernel_name(_lib.EMBER_OP_FWD, 128, 128, 64, _lib.EMBER_F32) == b"simt_f32"
-    assert L.ember_attention_kernel_name(_lib.EMBER_OP_FWD, 128, 128, 80, _lib.EMBER_BF16) == b"simt_f32"
+    # any multiple of 8 up to 128 runs on the tensor cores (zero-padded to 64 or 128 columns)
+    assert L.ember_attention_kernel_name(_lib.EMBER_OP_FWD, 128, 128, 80, _lib.EMBER_BF16) == b"sm100_tcgen05"
+    assert L.ember_attention_kernel_name(_lib.EMBER_OP_BWD, 128, 128, 24, _lib.EMBER_BF16) == b"sm100_tcgen05"
+    assert L.ember_attention_kernel_name(_lib.EMBER_OP_FWD, 128, 128, 100, _lib.EMBER_BF16) == b"simt_f32"
 
 
 def _fake(shape, dtype="float32"):

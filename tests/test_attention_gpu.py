@@ -99,6 +99,60 @@ def test_bf16_forward_tcgen05(shape, causal):
     assert np.abs(lse - rl).max() <= BF16_TOL, f"LSE max err {np.abs(lse - rl).max()}"
 
 
+# Head dimensions between the kernels' 64 and 128 columns (any multiple of 8): the TMA copies pad
+# the rows with zeros, the epilogues skip the padding. Checked forward and backward, in both backward
+# modes, with guard bands around every output (a store into the padding would land in the next row
+# or, for the last row, in the band).
+PADDED_SHAPES = [
+    (1, 2, 200, 200, 8), (1, 1, 130, 257, 24), (1, 2, 300, 300, 40), (2, 1, 129, 129, 56), (1, 2, 257, 300, 72),
+    (1, 2, 384, 384, 80), (2, 2, 640, 640, 96), (1, 1, 100, 517, 104), (1, 2, 256, 256, 112), (1, 1, 1, 300, 120),
+]
+
+
+@pytest.mark.parametrize("shape", PADDED_SHAPES)
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("deterministic", [0, 1])
+def test_bf16_padded_head_dims(shape, causal, deterministic):
+    import ctypes
+
+    torch = pytest.importorskip("torch")
+    from conftest import Guarded
+
+    B, H, Lq, Lk, D = shape
+    L = _lib.lib()
+    assert L.ember_attention_kernel_name(_lib.EMBER_OP_FWD, Lq, Lk, D, 1) == b"sm100_tcgen05"
+    assert L.ember_attention_kernel_name(_lib.EMBER_OP_BWD, Lq, Lk, D, 1) == b"sm100_tcgen05"
+    host = [bf16_round(seeded((B, H, n, D), s, sc)) for n, s, sc in ((Lq, 1, 0.5), (Lk, 2, 0.5), (Lk, 3, 0.5), (Lq, 4, 1.0))]
+    dev = torch.device("cuda", 0)
+    q, k, v, do = (torch.from_numpy(x).to(dev).to(torch.bfloat16) for x in host)
+    bh, scale = B * H, 1.0 / math.sqrt(D)
+    before = L.ember_set_deterministic(deterministic)
+    try:
+        o, dq = (Guarded(torch, (bh, Lq, D), torch.bfloat16, dev) for _ in range(2))
+        dk, dv = (Guarded(torch, (bh, Lk, D), torch.bfloat16, dev) for _ in range(2))
+        lse = Guarded(torch, (bh, Lq), torch.float32, dev)
+        wsn = L.ember_attention_workspace_bytes(_lib.EMBER_OP_BWD, bh, Lq, Lk, D, 1, 0)
+        ws = Guarded(torch, (wsn,), torch.uint8, dev)
+        sp = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        _lib.check(L.ember_attention_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.t.data_ptr(), lse.t.data_ptr(), bh, Lq,
+                                         Lk, D, scale, int(causal), 1, sp))
+        _lib.check(L.ember_attention_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.t.data_ptr(), lse.t.data_ptr(),
+                                         do.data_ptr(), dq.t.data_ptr(), dk.t.data_ptr(), dv.t.data_ptr(), bh, Lq, Lk, D, scale,
+                                         int(causal), 1, ws.t.data_ptr(), wsn, sp))
+        torch.cuda.synchronize()
+    finally:
+        L.ember_set_deterministic(before)
+    no_device_fault()
+    for name, g in (("o", o), ("lse", lse), ("dq", dq), ("dk", dk), ("dv", dv), ("workspace", ws)):
+        g.check(f"{name} at {shape}")
+    ro, rl = cpu_oracle.attention_fwd(*host[:3], None, causal)
+    assert np.abs(o.t.float().cpu().numpy().reshape(ro.shape) - ro).max() <= BF16_TOL
+    assert np.abs(lse.t.cpu().numpy().reshape(rl.shape) - rl).max() <= BF16_TOL
+    for name, got, ref in zip(("dq", "dk", "dv"), (dq, dk, dv), cpu_oracle.attention_bwd(*host, None, causal)):
+        err = np.abs(got.t.float().cpu().numpy().reshape(ref.shape) - ref).max()
+        assert err <= BF16_TOL * np.abs(ref).max(), (name, err)
+
+
 def test_bf16_forward_large_values_trigger_rescale():
     # Scores grow along the key axis so the running maximum keeps moving past the lazy-rescale
     # threshold; exercises the O rescale path.
@@ -154,15 +208,16 @@ def test_bf16_forward_is_deterministic():
 
 
 @pytest.mark.parametrize("shape", [
-    (1, 2, 96, 160, 64), (1, 1, 200, 200, 128), (1, 2, 64, 64, 80),       # last one: CUDA-core path
+    (1, 2, 96, 160, 64), (1, 1, 200, 200, 128), (1, 2, 64, 64, 80),       # 80: zero-padded to 128 columns
+    (1, 2, 64, 64, 20), (1, 1, 70, 90, 100),                               # CUDA-core path (not a multiple of 8)
     (1, 1, 128, 128, 128), (1, 2, 256, 256, 128), (1, 2, 300, 300, 128), (1, 1, 200, 520, 128),
     (2, 2, 512, 512, 128), (1, 2, 300, 300, 64), (1, 1, 1, 257, 128), (1, 2, 640, 1024, 64),
 ])
 @pytest.mark.parametrize("causal", [False, True])
 def test_bf16_backward(shape, causal):
     B, H, Lq, Lk, D = shape
-    if D in (64, 128):
-        assert _lib.lib().ember_attention_kernel_name(1, Lq, Lk, D, 1) == b"sm100_tcgen05"
+    want = b"sm100_tcgen05" if D % 8 == 0 and D <= 128 else b"simt_f32"
+    assert _lib.lib().ember_attention_kernel_name(1, Lq, Lk, D, 1) == want
     q, k, v = (bf16_round(seeded((B, H, L, D), s, 0.5)) for L, s in ((Lq, 1), (Lk, 2), (Lk, 3)))
     g = bf16_round(seeded((B, H, Lq, D), 4))
     ref = cpu_oracle.attention_bwd(q, k, v, g, None, causal)
