@@ -44,6 +44,7 @@ SIGNATURES = {
     "ember_attention_bwd": (_i, [_vp] * 9 + [_i] * 4 + [_f, _i, _i, _vp, _sz, _vp]),
     "ember_set_deterministic": (_i, [_i]),
     "ember_get_deterministic": (_i, []),
+    "ember_set_forward_block_rows": (_i, [_i]),
     "ember_attention_decode": (_i, [_vp] * 5 + [_i] * 3 + [_f, _i, _i, _vp, _sz, _vp]),
     "ember_attention_decode_static": (_i, [_vp] * 5 + [_i] * 3 + [_f, _i, _i, _vp]),
     "ember_attention_decode_static_capacity": (_sz, []),

@@ -112,6 +112,15 @@ int ember_set_deterministic(int on)
 
 int ember_get_deterministic(void) { return deterministic_mode() ? 1 : 0; }
 
+int ember_set_forward_block_rows(int rows)
+{
+    if (rows != 0 && rows != 128 && rows != 256) {
+        set_error("ember_set_forward_block_rows: %d is not 0, 128 or 256", rows);
+        return -EMBER_ERR_INVALID;
+    }
+    return sm100_fwd_set_block_rows(rows);
+}
+
 int ember_attention_decode_splits(int batch_heads, int lk, int d, int dtype)
 {
     DeviceState *st = device_state();

@@ -26,6 +26,7 @@ int launch_delta(const AttnArgs &a, float *delta, cudaStream_t s);
 
 // tcgen05 kernels (attn_fwd_sm100.cu / attn_bwd_sm100.cu): bf16 storage, d in {64, 128}.
 bool sm100_fwd_supported(const AttnArgs &a);
+int sm100_fwd_set_block_rows(int rows);  // 0 = choose per call, 128, 256; returns the previous setting
 int sm100_attention_fwd(const AttnArgs &a, DeviceState *st, cudaStream_t s);
 bool sm100_bwd_supported(const AttnArgs &a);
 // deterministic: two kernels (dK/dV, then dQ), bit-reproducible; otherwise one pass that adds its dQ

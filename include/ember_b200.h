@@ -142,6 +142,14 @@ EMBER_API int ember_attention_bwd(const void *q, const void *k, const void *v, c
 EMBER_API int ember_set_deterministic(int on);
 EMBER_API int ember_get_deterministic(void);
 
+/* ---- query rows per CTA of the bf16 tensor-core forward (a tuning and test switch; no counterpart
+ *      in the reference). 0 (the default) lets the library choose per call: 256 rows (two 128-row
+ *      tiles sharing the key/value stream), or 128 rows for launches too small to keep every SM
+ *      busy. 128 or 256 forces one form for every later call; both give the same bits. The initial
+ *      value comes from the environment variable EMBER_FWD_ROWS when it is 128 or 256.
+ *      Returns the previous setting; other values are EMBER_ERR_INVALID (negative). ---- */
+EMBER_API int ember_set_forward_block_rows(int rows);
+
 /* ---- single-query decode against a long key/value cache (lq == 1, no mask),
  *      split over the key axis with a log-sum-exp combine. Same reference path as
  *      the forward with n = 1 rows per batch (src/tensor/operators_gpu.cu:126-136).

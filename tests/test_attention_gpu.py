@@ -364,3 +364,31 @@ print("pair ok")
     env = dict(os.environ, EMBER_FWD_PAIR="1")
     r = subprocess.run([sys.executable, "-c", code, root], env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0 and "pair ok" in r.stdout, r.stdout + r.stderr
+
+
+def test_bf16_forward_one_and_two_tile_ctas_give_the_same_bits():
+    """The forward kernel runs 256 query rows per CTA (two tiles) or, for launches too small to fill
+    the SMs, 128 (one tile); ember_set_forward_block_rows forces either form. Both must meet the
+    oracle, and they must agree bit for bit, since a row's arithmetic does not depend on which other
+    rows share its CTA."""
+    L = _lib.lib()
+    assert L.ember_set_forward_block_rows(77) < 0
+    shapes = [(1, 2, 700, 700, 128), (1, 1, 513, 900, 128), (1, 3, 384, 640, 64), (1, 1, 2048, 2048, 128),
+              (1, 2, 129, 300, 128), (2, 2, 256, 256, 128), (1, 2, 300, 300, 80), (1, 1, 100, 100, 128)]
+    before = L.ember_set_forward_block_rows(0)
+    try:
+        for B, H, Lq, Lk, D in shapes:
+            for causal in (False, True):
+                q, k, v = (bf16_round(seeded((B, H, n, D), s, 0.5)) for n, s in ((Lq, 1), (Lk, 2), (Lk, 3)))
+                ro, rl = cpu_oracle.attention_fwd(q, k, v, None, causal)
+                got = {}
+                for rows in (128, 256, 0):
+                    assert L.ember_set_forward_block_rows(rows) >= 0
+                    got[rows] = run_fwd(q, k, v, None, causal, "bfloat16")
+                    no_device_fault()
+                o, lse = got[256]
+                assert np.abs(o - ro).max() <= BF16_TOL and np.abs(lse - rl).max() <= BF16_TOL, (Lq, Lk, D, causal)
+                for rows in (128, 0):
+                    assert np.array_equal(got[rows][0], o) and np.array_equal(got[rows][1], lse), (rows, Lq, Lk, D, causal)
+    finally:
+        L.ember_set_forward_block_rows(before)

@@ -32,6 +32,8 @@ for D in (64, 128):
     q, k, v, do = (torch.from_numpy(x).to(dev).to(torch.bfloat16) for x in host)
     for n in (1, 17, 100, 127, 128, 129, 255, 256, 257, 260, 384, 513, 700):
         for causal in (0, 1):
+            # both forms of the forward kernel: one query tile per CTA (odd passes) and two (even)
+            assert L.ember_set_forward_block_rows(128 if (n + causal) % 2 else 256) >= 0
             o, dq, dk, dv = (torch.empty((n, D), device=dev, dtype=torch.bfloat16) for _ in range(4))
             lse = torch.empty((n,), device=dev, dtype=torch.float32)
             wsn = L.ember_attention_workspace_bytes(_lib.EMBER_OP_BWD, 1, n, n, D, 1, 0)

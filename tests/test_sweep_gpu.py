@@ -36,9 +36,20 @@ def env():
     return L, dev, ctypes.c_void_p(s.cuda_stream)
 
 
+@pytest.fixture(params=[128, 256])
+def block_rows(request):
+    """Both forms of the forward kernel (one or two query tiles per CTA); left to itself the library
+    would take the one-tile form for every launch this small."""
+    L = _lib.lib()
+    before = L.ember_set_forward_block_rows(request.param)
+    assert before >= 0
+    yield request.param
+    L.ember_set_forward_block_rows(before)
+
+
 @pytest.mark.parametrize("D", [64, 128])
 @pytest.mark.parametrize("causal", [False, True])
-def test_every_length_up_to_260(env, D, causal):
+def test_every_length_up_to_260(env, D, causal, block_rows):
     L, dev, sp = env
     host = [bf16_round(seeded((LMAX, D), s, sc)) for s, sc in ((31, 0.5), (32, 0.5), (33, 0.5), (34, 1.0))]
     q, k, v, do = (torch.from_numpy(x).to(dev).to(torch.bfloat16) for x in host)
