@@ -1200,8 +1200,12 @@ __global__ void __launch_bounds__(SP_THREADS, 1)
     if (warp == W_ALLOC) tmem_dealloc(tmem, 512);
 }
 
-// dq = bf16(scale * accumulator): one block per (unit, query tile, 32-column chunk), thread t owns row t of
-// the tile (lane quarter t / 32, lane t % 32 of the accumulator's block layout) and writes 64 bytes of it.
+// dq = bf16(scale * accumulator): one block per (unit, query tile, 32-column chunk), warp w takes lane
+// quarter w of the accumulator's block layout ([4-column group][row][4 floats], 4 KB). A lane owns one
+// 16-byte piece of dq (8 columns = two column groups) of one row per pass, four lanes side by side on a
+// row: a warp-wide load reads four whole 128-byte runs of the block, a warp-wide store writes 64
+// contiguous bytes (two full sectors) of each of 8 rows. (One row per lane, as the accumulator is laid
+// out, made every store touch 32 lines with 16 bytes each and ran at half the memory bandwidth.)
 template <int HD>
 __global__ void __launch_bounds__(128) dq_finish_kernel(const float *__restrict__ acc, __nv_bfloat16 *__restrict__ dq, int lq,
                                                         int nqt, float scale, int d)
@@ -1211,22 +1215,27 @@ __global__ void __launch_bounds__(128) dq_finish_kernel(const float *__restrict_
     const int qt = (int)(tile % nqt);
     const size_t unit = tile / nqt;
     const int w = threadIdx.x / 32, lane = threadIdx.x % 32;
-    const int row = qt * 128 + threadIdx.x;
-    if (row >= lq || c * 32 >= d) return;  // d: elements per dq row in memory (<= HD, a multiple of 8)
+    const int q = lane % 4;          // which 8 columns of the chunk
+    const int col = c * 32 + q * 8;
+    if (col >= d) return;            // d: elements per dq row in memory (<= HD, a multiple of 8)
+    const int row0 = qt * 128 + w * 32 + lane / 4;
     const float4 *src = reinterpret_cast<const float4 *>(acc + ((tile * 4 + w) * (HD / 32) + c) * 1024);
-    float4 v[8];
+    float4 v[4][2];
 #pragma unroll
-    for (int cg = 0; cg < 8; cg++) v[cg] = src[cg * 32 + lane];  // all eight loads in flight
-    __nv_bfloat16 *dst = dq + (unit * lq + row) * d + c * 32;
+    for (int it = 0; it < 4; it++) {  // all eight loads in flight
+        v[it][0] = src[(2 * q) * 32 + it * 8 + lane / 4];
+        v[it][1] = src[(2 * q + 1) * 32 + it * 8 + lane / 4];
+    }
 #pragma unroll
-    for (int cg = 0; cg < 8; cg += 2) {
-        if (c * 32 + cg * 4 >= d) break;
+    for (int it = 0; it < 4; it++) {
+        const int row = row0 + it * 8;
+        if (row >= lq) continue;
         uint4 o;
-        o.x = pack_bf16(v[cg].x * scale, v[cg].y * scale);
-        o.y = pack_bf16(v[cg].z * scale, v[cg].w * scale);
-        o.z = pack_bf16(v[cg + 1].x * scale, v[cg + 1].y * scale);
-        o.w = pack_bf16(v[cg + 1].z * scale, v[cg + 1].w * scale);
-        *reinterpret_cast<uint4 *>(dst + cg * 4) = o;
+        o.x = pack_bf16(v[it][0].x * scale, v[it][0].y * scale);
+        o.y = pack_bf16(v[it][0].z * scale, v[it][0].w * scale);
+        o.z = pack_bf16(v[it][1].x * scale, v[it][1].y * scale);
+        o.w = pack_bf16(v[it][1].z * scale, v[it][1].w * scale);
+        *reinterpret_cast<uint4 *>(dq + (unit * lq + row) * d + col) = o;
     }
 }
 
