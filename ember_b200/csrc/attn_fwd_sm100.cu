@@ -783,18 +783,21 @@ bool sm100_fwd_supported(const AttnArgs &a)
     return (bits & 15) == 0 && ((uintptr_t)a.out & 15) == 0;
 }
 
-// EMBER_FWD_EMU=0..2 sets the share of polynomial exponentials (read once). Default 0: with the softmax
-// warps no longer bound by the MUFU, every exponential there measured 1.3 % faster at B4 H32 L4096 than
-// a quarter of them on the FMA pipe (0.487 against 0.494 ms), and half of them 5 % slower.
-static int fwd_emu_setting()
+// EMBER_FWD_EMU=0..2 sets the share of polynomial exponentials (read once). Default at 128 columns 0:
+// with the softmax warps no longer bound by the MUFU, every exponential there measured 1.3 % faster at
+// B4 H32 L4096 than a quarter of them on the FMA pipe (0.487 against 0.494 ms), and half of them 5 %
+// slower. Default at 64 columns 1: a key tile then needs half the tensor time for the same 16384
+// exponentials, the MUFU is the limit, and a quarter on the FMA pipe measured 2.7 % faster (0.421 against
+// 0.432 ms at 128 units x L4096 causal; half of them 2 % slower).
+static int fwd_emu_setting(int hd)
 {
-    static int v = -1;
-    if (v < 0) {
+    static int v = -2;
+    if (v == -2) {
         const char *e = getenv("EMBER_FWD_EMU");
-        v = e ? atoi(e) : 0;
-        if (v < 0 || v > 2) v = 0;
+        v = e ? atoi(e) : -1;
+        if (v < 0 || v > 2) v = -1;
     }
-    return v;
+    return v >= 0 ? v : (hd <= 64 ? 1 : 0);
 }
 
 // EMBER_FWD_PAIR=1 sends D = 128 shapes with more than 256 query rows to the CTA-pair form of the
@@ -822,7 +825,7 @@ int sm100_fwd_set_block_rows(int rows)
 
 int sm100_attention_fwd(const AttnArgs &a, DeviceState *st, cudaStream_t s)
 {
-    const int emu = fwd_emu_setting();
+    const int emu = fwd_emu_setting(a.d > 64 ? 128 : 64);
     if (a.d > 64) {
         // CTA pairs take 512-row blocks; below three query tiles a pair would mostly idle
         if (a.d == 128 && a.lq > 256 && fwd_pair_enabled()) {
