@@ -265,13 +265,22 @@ __device__ __forceinline__ void store_staged(const uint8_t *stage, __nv_bfloat16
 }
 
 #ifndef BWD_EMU_PAIRS_OF_4
-#define BWD_EMU_PAIRS_OF_4 2  // pairs per group of 4 whose exponentials avoid the MUFU
+#define BWD_EMU_PAIRS_OF_4 2  // pairs per group of 4 whose exponentials avoid the MUFU (128 columns)
 #endif
+// At 64 columns every exponential goes through the MUFU: a tile pair has half the tensor and
+// shared-memory work there, the compute warps' instruction issue is the limit, and the polynomial costs
+// more instructions than it frees MUFU slots (measured at 128 units x L4096: 1.57 against 1.70 ms without
+// a mask, 0.906 against 0.913 ms causal).
+template <int HD>
+struct BwdEmu {
+    static constexpr int PAIRS_OF_4 = HD >= 128 ? BWD_EMU_PAIRS_OF_4 : 0;
+};
 
 // p = 2^x for a pair, through the MUFU or the FMA-pipe polynomial depending on the pair's position
+template <int EMU_OF_4>
 __device__ __forceinline__ void exp2_pair(f32x2 x2, int pair_index, float &p0, float &p1)
 {
-    if (pair_index % 4 < BWD_EMU_PAIRS_OF_4) {
+    if (pair_index % 4 < EMU_OF_4) {
         exp2_poly2(x2, p0, p1);
     } else {
         float x0, x1;
@@ -488,7 +497,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
                     const int qq = h * CPT + cc;
                     const f32x2 x2 = fma2(pack2(pv[cc], pv[cc + 1]), c2, *reinterpret_cast<const f32x2 *>(&rv[qq]));
                     float p0, p1;
-                    exp2_pair(x2, x, p0, p1);
+                    exp2_pair<BwdEmu<HD>::PAIRS_OF_4>(x2, x, p0, p1);
                     pv[cc] = p0;
                     pv[cc + 1] = p1;
                     pk[x] = pack_bf16(p0, p1);
@@ -707,7 +716,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
             for (int x = 0; x < CPT / 2; x++) {
                 const f32x2 x2 = fma2(pack2(pv[2 * x], pv[2 * x + 1]), c2, nl2);
                 float p0, p1;
-                exp2_pair(x2, x, p0, p1);
+                exp2_pair<BwdEmu<HD>::PAIRS_OF_4>(x2, x, p0, p1);
                 pv[2 * x] = p0;
                 pv[2 * x + 1] = p1;
             }
@@ -1142,7 +1151,7 @@ __global__ void __launch_bounds__(SP_THREADS, 1)
                     const int cc = ch * 16 + 2 * x;
                     const f32x2 x2 = fma2(pack2(pv[cc], pv[cc + 1]), c2, *reinterpret_cast<const f32x2 *>(&rv[h * 64 + cc]));
                     float p0, p1;
-                    exp2_pair(x2, x, p0, p1);
+                    exp2_pair<BwdEmu<HD>::PAIRS_OF_4>(x2, x, p0, p1);
                     pv[cc] = p0;
                     pv[cc + 1] = p1;
                     pk[x] = pack_bf16(p0, p1);
