@@ -1250,13 +1250,25 @@ __global__ void __launch_bounds__(128) dq_finish_kernel(const float *__restrict_
 
 // delta[row] = sum_c dO[row][c] * O[row][c] for bf16 rows of HD elements: HD / 16 lanes per row, two
 // 16-byte loads per tensor and lane, 32 / (HD / 16) rows per warp.
+// The same launch clears the float32 dQ accumulator of the single-pass kernel (zero_vecs 16-byte
+// vectors at `zero`, an equal slice per block): one launch less than a memset of its own. zero_vecs == 0: nothing to clear.
+__device__ __forceinline__ void zero_slice(uint4 *__restrict__ zero, size_t zero_vecs)
+{
+    const size_t per = (zero_vecs + gridDim.x - 1) / gridDim.x;
+    const size_t begin = (size_t)blockIdx.x * per;
+    const size_t end = begin + per < zero_vecs ? begin + per : zero_vecs;
+    for (size_t i = begin + threadIdx.x; i < end; i += blockDim.x) zero[i] = make_uint4(0u, 0u, 0u, 0u);
+}
+
 template <int HD>
 __global__ void __launch_bounds__(256) delta_bf16_kernel(const uint4 *__restrict__ out, const uint4 *__restrict__ dout,
-                                                         float *__restrict__ delta, size_t rows)
+                                                         float *__restrict__ delta, size_t rows, uint4 *__restrict__ zero,
+                                                         size_t zero_vecs)
 {
     constexpr int LPR = HD / 16, RPW = 32 / LPR;
     const int lane = threadIdx.x % 32;
     const size_t row = ((size_t)blockIdx.x * 8 + threadIdx.x / 32) * RPW + lane / LPR;
+    zero_slice(zero, zero_vecs);  // every thread of every block, also those past the last row
     float s = 0.f;
     if (row < rows) {
         const size_t base = row * (HD / 8) + (lane % LPR) * 2;
@@ -1279,10 +1291,12 @@ __global__ void __launch_bounds__(256) delta_bf16_kernel(const uint4 *__restrict
 // The same for rows of any multiple of 8 elements up to 128: 16 lanes per row, one 16-byte load per
 // tensor and lane where the row has that chunk.
 __global__ void __launch_bounds__(256) delta_bf16_rows_kernel(const uint4 *__restrict__ out, const uint4 *__restrict__ dout,
-                                                              float *__restrict__ delta, size_t rows, int chunks)
+                                                              float *__restrict__ delta, size_t rows, int chunks,
+                                                              uint4 *__restrict__ zero, size_t zero_vecs)
 {
     const int lane = threadIdx.x % 32, c = lane % 16;
     const size_t row = ((size_t)blockIdx.x * 8 + threadIdx.x / 32) * 2 + lane / 16;
+    zero_slice(zero, zero_vecs);
     float s = 0.f;
     if (row < rows && c < chunks) {
         const uint4 a = out[row * chunks + c], b = dout[row * chunks + c];
@@ -1298,19 +1312,20 @@ __global__ void __launch_bounds__(256) delta_bf16_rows_kernel(const uint4 *__res
     if (row < rows && c == 0) delta[row] = s;
 }
 
+// zero / zero_bytes: the accumulator to clear in the same launch (16-byte aligned, a multiple of 16 bytes), or NULL / 0
 template <int HD>
-int launch_delta_bf16(const AttnArgs &a, float *delta, cudaStream_t s)
+int launch_delta_bf16(const AttnArgs &a, float *delta, cudaStream_t s, void *zero = nullptr, size_t zero_bytes = 0)
 {
     const size_t rows = (size_t)a.bh * a.lq;
     if (a.d != HD) {
         delta_bf16_rows_kernel<<<(unsigned)((rows + 15) / 16), 256, 0, s>>>((const uint4 *)a.out, (const uint4 *)a.dout, delta,
-                                                                             rows, a.d / 8);
+                                                                             rows, a.d / 8, (uint4 *)zero, zero_bytes / 16);
         EMBER_CUDA_TRY(cudaGetLastError());
         return EMBER_OK;
     }
     constexpr int ROWS_PER_BLOCK = 8 * (32 / (HD / 16));
     delta_bf16_kernel<HD><<<(unsigned)((rows + ROWS_PER_BLOCK - 1) / ROWS_PER_BLOCK), 256, 0, s>>>(
-        (const uint4 *)a.out, (const uint4 *)a.dout, delta, rows);
+        (const uint4 *)a.out, (const uint4 *)a.dout, delta, rows, (uint4 *)zero, zero_bytes / 16);
     EMBER_CUDA_TRY(cudaGetLastError());
     return EMBER_OK;
 }
@@ -1320,10 +1335,10 @@ int launch_fused(const AttnArgs &a, float *delta, float *dq_acc, DeviceState *st
 {
     using C = SpCfg<HD>;
     static_assert(NCW == 8, "the single-pass kernel is written for eight compute warps");
-    int rc = launch_delta_bf16<HD>(a, delta, s);
-    if (rc) return rc;
     const int nqt = (a.lq + 127) / 128;
-    EMBER_CUDA_TRY(cudaMemsetAsync(dq_acc, 0, (size_t)a.bh * nqt * 128 * HD * sizeof(float), s));
+    // delta, and the accumulator cleared by the same launch
+    int rc = launch_delta_bf16<HD>(a, delta, s, dq_acc, (size_t)a.bh * nqt * 128 * HD * sizeof(float));
+    if (rc) return rc;
     CUtensorMap tq, tk, tv, tdo;
     if ((rc = make_tensor_map_bf16_3d(&tq, a.q, a.d, a.lq, a.bh, 64, 128)) != EMBER_OK) return rc;
     if ((rc = make_tensor_map_bf16_3d(&tk, a.k, a.d, a.lk, a.bh, 64, 128)) != EMBER_OK) return rc;
