@@ -926,9 +926,11 @@ __global__ void __launch_bounds__(SP_THREADS, 1)
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
 
+    pdl_launch_dependents();  // the dQ finish kernel may be placed on SMs as they fall idle; it waits for this grid's end
     if (warp >= W_DRAIN0) {
         // -------------------------------------------------------------------- drain dQ(i)
         asm volatile("setmaxnreg.dec.sync.aligned.u32 88;");  // holds half a row (64 columns) of dQ(i) at a time
+        pdl_wait();  // the accumulator is cleared by the delta launch before this one
         const int w = warp - W_DRAIN0;  // == warp % 4: the tensor-memory lane quarter this warp may read
         const uint32_t t_dq = tmem + ((uint32_t)(w * 32) << 16) + C::T_DP;
         uint8_t *stage = smem_gen + C::OFF_STAGE + w * C::STAGE_WARP_BYTES;
@@ -1117,6 +1119,9 @@ __global__ void __launch_bounds__(SP_THREADS, 1)
             if (i < n && qrow < p.lq) asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v) : "l"(rowvec_src + qrow));
             return v;
         };
+        // Everything up to here (and the producer's copies and the first two products) needs nothing
+        // from the delta launch before this one; the delta vector does.
+        pdl_wait();
         float raw_next = fetch_raw(0);
         for (int i = 0; i < n; i++) {
             const int q0 = (i_begin + i) * 128;
@@ -1224,6 +1229,7 @@ __global__ void __launch_bounds__(128) dq_finish_kernel(const float *__restrict_
     const int qt = (int)(tile % nqt);
     const size_t unit = tile / nqt;
     const int w = threadIdx.x / 32, lane = threadIdx.x % 32;
+    pdl_wait();                      // the accumulator is complete when the single-pass kernel has ended
     const int q = lane % 4;          // which 8 columns of the chunk
     const int col = c * 32 + q * 8;
     if (col >= d) return;            // d: elements per dq row in memory (<= HD, a multiple of 8)
@@ -1268,6 +1274,8 @@ __global__ void __launch_bounds__(256) delta_bf16_kernel(const uint4 *__restrict
     constexpr int LPR = HD / 16, RPW = 32 / LPR;
     const int lane = threadIdx.x % 32;
     const size_t row = ((size_t)blockIdx.x * 8 + threadIdx.x / 32) * RPW + lane / LPR;
+    pdl_wait();                   // O comes from the kernel before (the forward, when it directly precedes)
+    pdl_launch_dependents();      // the single-pass kernel may start its loads and first products under this kernel's tail
     zero_slice(zero, zero_vecs);  // every thread of every block, also those past the last row
     float s = 0.f;
     if (row < rows) {
@@ -1296,6 +1304,8 @@ __global__ void __launch_bounds__(256) delta_bf16_rows_kernel(const uint4 *__res
 {
     const int lane = threadIdx.x % 32, c = lane % 16;
     const size_t row = ((size_t)blockIdx.x * 8 + threadIdx.x / 32) * 2 + lane / 16;
+    pdl_wait();
+    pdl_launch_dependents();
     zero_slice(zero, zero_vecs);
     float s = 0.f;
     if (row < rows && c < chunks) {
@@ -1317,16 +1327,24 @@ template <int HD>
 int launch_delta_bf16(const AttnArgs &a, float *delta, cudaStream_t s, void *zero = nullptr, size_t zero_bytes = 0)
 {
     const size_t rows = (size_t)a.bh * a.lq;
+    cudaLaunchAttribute pdl[1];
+    pdl[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    pdl[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.blockDim = dim3(256);
+    cfg.stream = s;
+    cfg.attrs = pdl;
+    cfg.numAttrs = 1;
     if (a.d != HD) {
-        delta_bf16_rows_kernel<<<(unsigned)((rows + 15) / 16), 256, 0, s>>>((const uint4 *)a.out, (const uint4 *)a.dout, delta,
-                                                                             rows, a.d / 8, (uint4 *)zero, zero_bytes / 16);
-        EMBER_CUDA_TRY(cudaGetLastError());
+        cfg.gridDim = dim3((unsigned)((rows + 15) / 16));
+        EMBER_CUDA_TRY(cudaLaunchKernelEx(&cfg, delta_bf16_rows_kernel, (const uint4 *)a.out, (const uint4 *)a.dout, delta, rows,
+                                          a.d / 8, (uint4 *)zero, zero_bytes / 16));
         return EMBER_OK;
     }
     constexpr int ROWS_PER_BLOCK = 8 * (32 / (HD / 16));
-    delta_bf16_kernel<HD><<<(unsigned)((rows + ROWS_PER_BLOCK - 1) / ROWS_PER_BLOCK), 256, 0, s>>>(
-        (const uint4 *)a.out, (const uint4 *)a.dout, delta, rows, (uint4 *)zero, zero_bytes / 16);
-    EMBER_CUDA_TRY(cudaGetLastError());
+    cfg.gridDim = dim3((unsigned)((rows + ROWS_PER_BLOCK - 1) / ROWS_PER_BLOCK));
+    EMBER_CUDA_TRY(cudaLaunchKernelEx(&cfg, delta_bf16_kernel<HD>, (const uint4 *)a.out, (const uint4 *)a.dout, delta, rows,
+                                      (uint4 *)zero, zero_bytes / 16));
     return EMBER_OK;
 }
 
@@ -1361,10 +1379,21 @@ int launch_fused(const AttnArgs &a, float *delta, float *dq_acc, DeviceState *st
     EMBER_CUDA_TRY(cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
     const size_t touched = ((size_t)a.lq + a.lk) * HD * 2 * 4 + (size_t)a.lq * HD * 4;  // + the float32 dQ accumulator
     p.order = make_work_order(a.bh, (a.lk + 127) / 128, st->sm_count, touched, a.causal != 0);
-    k1<<<dim3((unsigned)(p.order.units * p.order.blocks)), SP_THREADS, C::SMEM_BYTES, s>>>(tq, tk, tv, tdo, p);
-    EMBER_CUDA_TRY(cudaGetLastError());
-    dq_finish_kernel<HD><<<dim3((unsigned)((size_t)a.bh * nqt), HD / 32), 128, 0, s>>>(dq_acc, (__nv_bfloat16 *)a.dq, a.lq, nqt, a.scale, a.d);
-    EMBER_CUDA_TRY(cudaGetLastError());
+    cudaLaunchAttribute pdl[1];
+    pdl[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    pdl[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(p.order.units * p.order.blocks));
+    cfg.blockDim = dim3(SP_THREADS);
+    cfg.dynamicSmemBytes = C::SMEM_BYTES;
+    cfg.stream = s;
+    cfg.attrs = pdl;
+    cfg.numAttrs = 1;
+    EMBER_CUDA_TRY(cudaLaunchKernelEx(&cfg, k1, tq, tk, tv, tdo, p));
+    cfg.gridDim = dim3((unsigned)((size_t)a.bh * nqt), HD / 32);
+    cfg.blockDim = dim3(128);
+    cfg.dynamicSmemBytes = 0;
+    EMBER_CUDA_TRY(cudaLaunchKernelEx(&cfg, dq_finish_kernel<HD>, (const float *)dq_acc, (__nv_bfloat16 *)a.dq, a.lq, nqt, a.scale, a.d));
     return EMBER_OK;
 }
 

@@ -175,6 +175,9 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    // A kernel launched behind this one with programmatic stream serialization (the backward's delta
+    // kernel) may have its CTAs placed on SMs as they fall idle; it waits for this grid's end itself.
+    pdl_launch_dependents();
     const uint32_t crank = PAIR ? cluster_ctarank() : 0u;  // rank 0 of a pair issues the MMAs
     int bh, rank;
     work_item(p.order, PAIR ? blockIdx.x / 2 : blockIdx.x, bh, rank);

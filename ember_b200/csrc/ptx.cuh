@@ -318,6 +318,14 @@ __device__ __forceinline__ void mma_ts_lo(uint32_t d_tmem, uint32_t a_tmem, uint
 // shared memory, and each CTA's tensor memory receives its 128 rows of the result. Every CTA loads
 // its own operands with its own TMA copies (no multicast); the completion bytes of both CTAs are
 // counted by rank 0's barrier.
+// Programmatic dependent launch. A kernel launched with programmatic stream serialization may have its
+// CTAs placed (and run whatever does not depend on the kernel before it on the stream) as soon as every
+// CTA of that kernel has passed pdl_launch_dependents(); pdl_wait() then blocks until that kernel has
+// completed and its writes are visible. Launched without the attribute, or after something that is
+// not a kernel, both are no-ops. Used along forward -> delta -> single-pass backward -> dQ finish.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 __device__ __forceinline__ uint32_t cluster_ctarank()
 {
     uint32_t r;
