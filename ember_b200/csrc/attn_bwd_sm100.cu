@@ -1322,6 +1322,18 @@ __global__ void __launch_bounds__(256) delta_bf16_rows_kernel(const uint4 *__res
     if (row < rows && c == 0) delta[row] = s;
 }
 
+// EMBER_PDL=0 (read once) launches the backward's kernels without programmatic stream serialization:
+// plain stream order, for comparison or for a tool that cannot follow programmatic edges.
+static int pdl_attr_count()
+{
+    static int v = -1;
+    if (v < 0) {
+        const char *e = getenv("EMBER_PDL");
+        v = (e && e[0] == '0') ? 0 : 1;
+    }
+    return v;
+}
+
 // zero / zero_bytes: the accumulator to clear in the same launch (16-byte aligned, a multiple of 16 bytes), or NULL / 0
 template <int HD>
 int launch_delta_bf16(const AttnArgs &a, float *delta, cudaStream_t s, void *zero = nullptr, size_t zero_bytes = 0)
@@ -1334,7 +1346,7 @@ int launch_delta_bf16(const AttnArgs &a, float *delta, cudaStream_t s, void *zer
     cfg.blockDim = dim3(256);
     cfg.stream = s;
     cfg.attrs = pdl;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = pdl_attr_count();
     if (a.d != HD) {
         cfg.gridDim = dim3((unsigned)((rows + 15) / 16));
         EMBER_CUDA_TRY(cudaLaunchKernelEx(&cfg, delta_bf16_rows_kernel, (const uint4 *)a.out, (const uint4 *)a.dout, delta, rows,
@@ -1388,7 +1400,7 @@ int launch_fused(const AttnArgs &a, float *delta, float *dq_acc, DeviceState *st
     cfg.dynamicSmemBytes = C::SMEM_BYTES;
     cfg.stream = s;
     cfg.attrs = pdl;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = pdl_attr_count();
     EMBER_CUDA_TRY(cudaLaunchKernelEx(&cfg, k1, tq, tk, tv, tdo, p));
     cfg.gridDim = dim3((unsigned)((size_t)a.bh * nqt), HD / 32);
     cfg.blockDim = dim3(128);
