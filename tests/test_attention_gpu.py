@@ -392,3 +392,38 @@ def test_bf16_forward_one_and_two_tile_ctas_give_the_same_bits():
                     assert np.array_equal(got[rows][0], o) and np.array_equal(got[rows][1], lse), (rows, Lq, Lk, D, causal)
     finally:
         L.ember_set_forward_block_rows(before)
+
+
+def test_bf16_backward_plain_stream_order_in_a_subprocess():
+    """EMBER_PDL=0 (read once per process, hence the child) launches the backward's kernels without
+    programmatic dependent launch; the gradients must be those of the default chain: dK and dV bit for
+    bit, dQ to the rounding of its unordered float32 additions."""
+    import os
+    import subprocess
+    import sys
+
+    code = r"""
+import sys, hashlib, numpy as np
+sys.path.insert(0, sys.argv[1]); sys.path.insert(0, sys.argv[1] + "/tests")
+import ember_b200 as em
+from conftest import bf16_round, seeded
+for (B, H, Lq, Lk, D) in [(1, 2, 300, 300, 128), (2, 2, 640, 640, 64), (1, 2, 257, 300, 80)]:
+    q, k, v = (bf16_round(seeded((B, H, L, D), s, 0.5)) for L, s in ((Lq, 1), (Lk, 2), (Lk, 3)))
+    g = bf16_round(seeded((B, H, Lq, D), 4))
+    t = [em.Tensor(x, "bfloat16") for x in (q, k, v, g)]
+    o, lse = em.attention_forward(t[0], t[1], t[2], None, True)
+    dq, dk, dv = (x.to_np() for x in em.attention_backward(t[0], t[1], t[2], o, lse, t[3], None, True))
+    print("grads", Lq, D, hashlib.sha1(dk.tobytes() + dv.tobytes()).hexdigest(), float(np.abs(dq).sum()))
+print("done")
+"""
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    seen = {}
+    for pdl in ("0", "1"):
+        r = subprocess.run([sys.executable, "-c", code, root], env=dict(os.environ, EMBER_PDL=pdl), capture_output=True,
+                           text=True, timeout=600)
+        assert r.returncode == 0 and "done" in r.stdout, r.stdout + r.stderr
+        seen[pdl] = [ln.split() for ln in r.stdout.splitlines() if ln.startswith("grads")]
+    assert len(seen["0"]) == 3
+    for a, b in zip(seen["0"], seen["1"]):
+        assert a[:4] == b[:4], (a, b)                                    # shape and the dK/dV digest
+        assert abs(float(a[4]) - float(b[4])) <= 1e-3 * float(a[4]), (a, b)  # sum |dQ|
